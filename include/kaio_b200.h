@@ -1,0 +1,164 @@
+/*
+ * kaio_b200.h -- C ABI of libkaio_b200.so, the sm_100a (B200) implementation of the
+ * quantized-inference ops of KAIO's `kaio-ops` crate.
+ *
+ * Each entry point below replaces the PTX-JIT launch path inside one `kaio-ops`
+ * function; the Rust function keeps its signature and its host-side contract and
+ * calls the entry point with the raw device pointers, element counts and stream of
+ * its `GpuBuffer` / `KaioDevice` arguments (paths are relative to the KAIO tree).
+ *
+ * Conventions (all entry points):
+ *   - pointers are DEVICE pointers owned by the caller; inputs are never written,
+ *     outputs are written only in [0, m*n) (or the documented extent);
+ *   - `*_len` arguments are element counts of the caller's buffers (GpuBuffer::len());
+ *     they are validated exactly like the reference validates them, and a buffer may
+ *     be longer than the shape needs;
+ *   - `stream` is a CUstream / cudaStream_t (NULL = the legacy default stream).  Work is
+ *     enqueued on it and the call returns without synchronising, like the reference
+ *     (kaio-ops/src/matmul_int8_kernel.rs:1497-1511);
+ *   - the device is the calling thread's current CUDA device;
+ *   - return value: KAIO_B200_OK or an error code; kaio_b200_last_error() returns the
+ *     calling thread's last message.  For KAIO_B200_ERR_INVALID_CONFIG the message is
+ *     the text the reference puts into KaioError::InvalidConfig;
+ *   - there is no CPU fallback: on a machine without an sm_100 GPU every op returns
+ *     KAIO_B200_ERR_UNSUPPORTED_ARCH or KAIO_B200_ERR_CUDA.
+ *
+ * f16 values are IEEE binary16 bit patterns (uint16_t here, `half::f16` / `__half` on
+ * either side).
+ */
+#ifndef KAIO_B200_H
+#define KAIO_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KAIO_B200_OK 0
+#define KAIO_B200_ERR_INVALID_CONFIG 1   /* KaioError::InvalidConfig (kaio-runtime/src/error.rs:4-37) */
+#define KAIO_B200_ERR_CUDA 2             /* KaioError::Cuda */
+#define KAIO_B200_ERR_UNSUPPORTED_ARCH 3 /* analogue of ValidationError::SmTooLow */
+#define KAIO_B200_ERR_TIMEOUT 4          /* a device-side bounded wait gave up (see kaio_b200_device_status) */
+
+typedef uint16_t kaio_f16;
+
+/* ---- W8A8 ------------------------------------------------------------------------ */
+
+/* Replaces kaio_ops::matmul_int8 (kaio-ops/src/matmul_int8_kernel.rs:1468-1512).
+ * c[i,j] = ((sum_k a[i,k]*b[k,j]) as f32) * scale; a s8 [m,k], b s8 [k,n], c f32 [m,n],
+ * all row-major; k % 32 == 0. */
+int32_t kaio_b200_matmul_int8(const int8_t* a, size_t a_len, const int8_t* b, size_t b_len,
+                              float* c, size_t c_len, float scale, uint32_t m, uint32_t n,
+                              uint32_t k, void* stream);
+
+/* Extension (no reference counterpart): per-row activation and per-column weight scales,
+ * c[i,j] = (((acc) as f32) * a_scale[i]) * w_scale[j]. */
+int32_t kaio_b200_matmul_int8_scaled(const int8_t* a, size_t a_len, const int8_t* b, size_t b_len,
+                                     float* c, size_t c_len, const float* a_scale,
+                                     size_t a_scale_len, const float* w_scale, size_t w_scale_len,
+                                     uint32_t m, uint32_t n, uint32_t k, void* stream);
+
+/* Extension: the raw s32 accumulators, acc[i,j] = sum_k a[i,k]*b[k,j] (exact). */
+int32_t kaio_b200_matmul_int8_acc(const int8_t* a, size_t a_len, const int8_t* b, size_t b_len,
+                                  int32_t* acc, size_t acc_len, uint32_t m, uint32_t n, uint32_t k,
+                                  void* stream);
+
+/* ---- W4A16 ----------------------------------------------------------------------- */
+
+/* Replaces kaio_ops::matmul_int4 (kaio-ops/src/matmul_int4_kernel.rs:2126-2171).
+ * a f16 [m,k]; b_packed u32 [(k/8)*n]: word k/8 of column j at (k/8) + j*(k/8), nibble
+ * k%8 at bits [4*(k%8), +4), signed; scales f16 [k/128, n]; c f32 [m,n];
+ * group_size must be 128 and k % 128 == 0. */
+int32_t kaio_b200_matmul_int4(const kaio_f16* a, size_t a_len, const uint32_t* b_packed,
+                              size_t b_len, const kaio_f16* scales, size_t scales_len, float* c,
+                              size_t c_len, uint32_t m, uint32_t n, uint32_t k,
+                              uint32_t group_size, void* stream);
+
+/* Extension: same product with the f32 accumulator narrowed to f16 (round to nearest even). */
+int32_t kaio_b200_matmul_int4_f16out(const kaio_f16* a, size_t a_len, const uint32_t* b_packed,
+                                     size_t b_len, const kaio_f16* scales, size_t scales_len,
+                                     kaio_f16* c, size_t c_len, uint32_t m, uint32_t n, uint32_t k,
+                                     uint32_t group_size, void* stream);
+
+/* ---- fused QKV projection ---------------------------------------------------------- */
+
+/* Replaces kaio_ops::qkv_project_int8 (kaio-ops/src/qkv_project_int8_kernel.rs:2008-2064),
+ * W8A16: out_P[i,j] = f16((sum_k x[i,k] * f16(w_P[k,j])) * scale_P) for P in {q,k,v};
+ * x f16 [m,k]; w_P s8 [k,n] row-major; outputs f16 [m,n]; k % 16 == 0, n even. */
+int32_t kaio_b200_qkv_project_int8(const kaio_f16* x, size_t x_len, const int8_t* w_q,
+                                   size_t w_q_len, const int8_t* w_k, size_t w_k_len,
+                                   const int8_t* w_v, size_t w_v_len, float scale_q, float scale_k,
+                                   float scale_v, kaio_f16* q_out, size_t q_len, kaio_f16* k_out,
+                                   size_t k_len, kaio_f16* v_out, size_t v_len, uint32_t m,
+                                   uint32_t n, uint32_t k, void* stream);
+
+/* Extension: per-column f32 scales (f32 [n] per projection) instead of scalars. */
+int32_t kaio_b200_qkv_project_int8_colscale(const kaio_f16* x, size_t x_len, const int8_t* w_q,
+                                            size_t w_q_len, const int8_t* w_k, size_t w_k_len,
+                                            const int8_t* w_v, size_t w_v_len,
+                                            const float* scale_q, const float* scale_k,
+                                            const float* scale_v, size_t scale_len,
+                                            kaio_f16* q_out, size_t q_len, kaio_f16* k_out,
+                                            size_t k_len, kaio_f16* v_out, size_t v_len,
+                                            uint32_t m, uint32_t n, uint32_t k, void* stream);
+
+/* Replaces kaio_ops::qkv_project_int4 (kaio-ops/src/qkv_project_int4_kernel.rs:1495-1555),
+ * W4A16: three matmul_int4-style products sharing x, outputs f16 = f16(acc), no post-scale;
+ * packed weights and group scales laid out as for kaio_b200_matmul_int4; n even. */
+int32_t kaio_b200_qkv_project_int4(const kaio_f16* x, size_t x_len, const uint32_t* w_q_packed,
+                                   size_t w_q_len, const uint32_t* w_k_packed, size_t w_k_len,
+                                   const uint32_t* w_v_packed, size_t w_v_len,
+                                   const kaio_f16* scales_q, size_t scales_q_len,
+                                   const kaio_f16* scales_k, size_t scales_k_len,
+                                   const kaio_f16* scales_v, size_t scales_v_len, kaio_f16* q_out,
+                                   size_t q_len, kaio_f16* k_out, size_t k_len, kaio_f16* v_out,
+                                   size_t v_len, uint32_t m, uint32_t n, uint32_t k,
+                                   uint32_t group_size, void* stream);
+
+/* ---- attention --------------------------------------------------------------------- */
+
+/* Replaces kaio_ops::attention_tc and attention_tc_causal
+ * (kaio-ops/src/attention_tc_kernel.rs:2240-2333): out = softmax(q k^T / sqrt(d_k) [+ causal
+ * mask j > i]) v; q f16 [seq_q,d_k], k f16 [seq_k,d_k], v f16 [seq_k,d_v], out f32
+ * [seq_q,d_v]; the reference's shape limits apply (multiples of 16/16/16/8, seq_k <= 384,
+ * d_k, d_v <= 128). */
+int32_t kaio_b200_attention_tc(const kaio_f16* q, size_t q_len, const kaio_f16* k, size_t k_len,
+                               const kaio_f16* v, size_t v_len, float* out, size_t out_len,
+                               uint32_t seq_q, uint32_t seq_k, uint32_t d_k, uint32_t d_v,
+                               int32_t causal, void* stream);
+
+/* Extension: batched multi-head attention, f16 output, any seq_k.  q/k/v/out are f16
+ * [batch*seq, heads*head_dim] row-major with row stride `row_stride` elements (the layout the
+ * fused QKV projection writes); head h of batch b starts at row b*seq, column h*head_dim. */
+int32_t kaio_b200_attention_mha_f16(const kaio_f16* q, size_t q_len, const kaio_f16* k,
+                                    size_t k_len, const kaio_f16* v, size_t v_len, kaio_f16* out,
+                                    size_t out_len, uint32_t batch, uint32_t heads, uint32_t seq_q,
+                                    uint32_t seq_k, uint32_t head_dim, uint32_t row_stride,
+                                    int32_t causal, void* stream);
+
+/* ---- library state ------------------------------------------------------------------- */
+
+/* Last error message of the calling thread ("" if none). */
+const char* kaio_b200_last_error(void);
+
+/* Synchronises `stream` and reads the current device's status block: code[0] = 0 when no
+ * kernel reported a problem, else {code, reporting block, site, kernel id}; the block is
+ * cleared.  Returns KAIO_B200_ERR_TIMEOUT when code[0] != 0. */
+int32_t kaio_b200_device_status(void* stream, uint32_t code[4]);
+
+/* Name of the kernel variant the last call on this thread dispatched to (for tests and
+ * traces): e.g. "w8a8_tcgen05", "int8_generic". */
+const char* kaio_b200_last_variant(void);
+
+/* Frees the library's per-device workspaces.  Callers must have synchronised. */
+void kaio_b200_shutdown(void);
+
+/* ABI version: major*1000 + minor. */
+int32_t kaio_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KAIO_B200_H */

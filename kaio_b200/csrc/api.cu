@@ -1,0 +1,741 @@
+// C ABI of libkaio_b200.so: argument validation with the reference's contracts and error
+// texts, per-device state, and dispatch to the sm_100a kernels.
+//
+// The validation functions restate, message for message,
+//   validate_dims_int8          kaio-ops/src/matmul_int8_kernel.rs:108-150
+//   validate_dims_int4          kaio-ops/src/matmul_int4_kernel.rs:112-174
+//   validate_dims_qkv_int8      kaio-ops/src/qkv_project_int8_kernel.rs:1894-1953
+//   validate_dims_qkv_int4      kaio-ops/src/qkv_project_int4_kernel.rs:1344-1433
+//   validate_attention_tc_dims  kaio-ops/src/attention_tc_kernel.rs:139-223
+#include <cstdarg>
+#include <cstdio>
+#include <mutex>
+#include <string>
+
+#include "../../include/kaio_b200.h"
+#include "kernels.h"
+
+#define KAIO_API extern "C" __attribute__((visibility("default")))
+
+namespace kaio {
+
+// ---------------------------------------------------------------- thread-local error state
+static thread_local std::string g_last_error;
+static thread_local const char* g_last_variant = "";
+
+static int32_t fail(int32_t code, const char* fmt, ...)
+{
+    char buf[1024];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+    return code;
+}
+
+static int32_t fail_cuda(cudaError_t err, const char* what)
+{
+    return fail(KAIO_B200_ERR_CUDA, "%s: CUDA error %d (%s)", what, (int)err,
+                cudaGetErrorString(err));
+}
+
+// ---------------------------------------------------------------- tensor maps
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+                cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+cudaError_t encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t elem_bytes,
+                                 const void* base, uint64_t inner, uint64_t outer,
+                                 uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer,
+                                 CUtensorMapSwizzle swizzle)
+{
+    (void)elem_bytes;
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn)
+        return cudaErrorNotSupported;
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {row_stride_bytes};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, dtype, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+// ---------------------------------------------------------------- per-device context
+constexpr int MAX_DEVICES = 64;
+static DeviceCtx g_ctx[MAX_DEVICES];
+static std::mutex g_ctx_mutex;
+
+static int32_t get_ctx(DeviceCtx** out)
+{
+    int dev = -1;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess)
+        return fail_cuda(err, "cudaGetDevice");
+    if (dev < 0 || dev >= MAX_DEVICES)
+        return fail(KAIO_B200_ERR_CUDA, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_ctx_mutex);
+    DeviceCtx& c = g_ctx[dev];
+    if (c.device < 0) {
+        cudaDeviceProp prop;
+        err = cudaGetDeviceProperties(&prop, dev);
+        if (err != cudaSuccess)
+            return fail_cuda(err, "cudaGetDeviceProperties");
+        if (prop.major != 10)
+            return fail(KAIO_B200_ERR_UNSUPPORTED_ARCH,
+                        "kaio_b200 kernels are built for sm_100a only; device %d is sm_%d%d", dev,
+                        prop.major, prop.minor);
+        err = cudaMalloc(&c.status, 4 * sizeof(uint32_t));
+        if (err != cudaSuccess)
+            return fail_cuda(err, "cudaMalloc(status)");
+        err = cudaMemset(c.status, 0, 4 * sizeof(uint32_t));
+        if (err != cudaSuccess)
+            return fail_cuda(err, "cudaMemset(status)");
+        c.num_sms = prop.multiProcessorCount;
+        c.cc_major = prop.major;
+        c.cc_minor = prop.minor;
+        c.device = dev;
+    }
+    *out = &c;
+    return KAIO_B200_OK;
+}
+
+// Grows the split-K workspace / counters of a device.  Growth frees the old block with
+// cudaFree (which synchronises the device), so it is safe against work still in flight.
+static int32_t ensure_workspace(DeviceCtx* c, size_t bytes, size_t counters)
+{
+    std::lock_guard<std::mutex> lock(g_ctx_mutex);
+    if (bytes > c->workspace_bytes) {
+        if (c->workspace)
+            cudaFree(c->workspace);
+        c->workspace = nullptr;
+        c->workspace_bytes = 0;
+        cudaError_t err = cudaMalloc(&c->workspace, bytes);
+        if (err != cudaSuccess)
+            return fail_cuda(err, "cudaMalloc(workspace)");
+        c->workspace_bytes = bytes;
+    }
+    if (counters > c->num_tile_counters) {
+        if (c->tile_counters)
+            cudaFree(c->tile_counters);
+        c->tile_counters = nullptr;
+        c->num_tile_counters = 0;
+        cudaError_t err = cudaMalloc(&c->tile_counters, counters * sizeof(uint32_t));
+        if (err != cudaSuccess)
+            return fail_cuda(err, "cudaMalloc(counters)");
+        err = cudaMemset(c->tile_counters, 0, counters * sizeof(uint32_t));
+        if (err != cudaSuccess)
+            return fail_cuda(err, "cudaMemset(counters)");
+        c->num_tile_counters = counters;
+    }
+    return KAIO_B200_OK;
+}
+
+static int32_t finish(cudaError_t err, const char* op, const char* variant)
+{
+    g_last_variant = variant;
+    if (err != cudaSuccess)
+        return fail_cuda(err, op);
+    return KAIO_B200_OK;
+}
+
+// ---------------------------------------------------------------- validation
+#define INVALID(...) return fail(KAIO_B200_ERR_INVALID_CONFIG, __VA_ARGS__)
+
+static int32_t validate_int8(const char* c_kind, size_t a_len, size_t b_len, size_t c_len,
+                             uint32_t m, uint32_t n, uint32_t k)
+{
+    if (m == 0 || n == 0 || k == 0)
+        INVALID("matmul_int8 dimensions must be non-zero");
+    if (k % 32 != 0)
+        INVALID("matmul_int8: K must be a multiple of 32 (got %u). The "
+                "mma.sync.m16n8k32.s8.s8.s32 instance shape requires K-tile "
+                "size 32; K is not edge-padded inside a K-tile.",
+                k);
+    const size_t mk = (size_t)m * k, kn = (size_t)k * n, mn = (size_t)m * n;
+    if (a_len < mk)
+        INVALID("matmul_int8: A buffer too small: need %zu i8 (%u\xC3\x97%u), got %zu", mk, m, k,
+                a_len);
+    if (b_len < kn)
+        INVALID("matmul_int8: B buffer too small: need %zu i8 (%u\xC3\x97%u), got %zu", kn, k, n,
+                b_len);
+    if (c_len < mn)
+        INVALID("matmul_int8: C buffer too small: need %zu %s (%u\xC3\x97%u), got %zu", mn, c_kind, m,
+                n, c_len);
+    return KAIO_B200_OK;
+}
+
+static int32_t validate_int4(const char* c_kind, size_t a_len, size_t b_len, size_t s_len,
+                             size_t c_len, uint32_t m, uint32_t n, uint32_t k, uint32_t group_size)
+{
+    if (m == 0 || n == 0 || k == 0)
+        INVALID("matmul_int4: M, N, K dimensions must be non-zero");
+    if (group_size != 128)
+        INVALID("matmul_int4: group_size must be 128 (got %u). Non-128 "
+                "group sizes are deferred to a follow-up sprint.",
+                group_size);
+    if (k % 128 != 0)
+        INVALID("matmul_int4: K must be a multiple of group_size=128 (got %u). "
+                "Partial groups are not supported.",
+                k);
+    const size_t mk = (size_t)m * k, words = (size_t)(k / 8) * n, groups = k / group_size,
+                 cells = groups * n, mn = (size_t)m * n;
+    if (a_len < mk)
+        INVALID("matmul_int4: A buffer too small: need %zu f16 (%u\xC3\x97%u), got %zu", mk, m, k,
+                a_len);
+    if (b_len < words)
+        INVALID("matmul_int4: B packed buffer too small: need %zu u32 "
+                "(%u cols \xC3\x97 %u K-words), got %zu",
+                words, n, k / 8, b_len);
+    if (s_len < cells)
+        INVALID("matmul_int4: scales buffer too small: need %zu f16 "
+                "(%zu groups \xC3\x97 %u cols), got %zu",
+                cells, groups, n, s_len);
+    if (c_len < mn)
+        INVALID("matmul_int4: C buffer too small: need %zu %s (%u\xC3\x97%u), got %zu", mn, c_kind, m,
+                n, c_len);
+    return KAIO_B200_OK;
+}
+
+static int32_t validate_qkv_int8(size_t x_len, const size_t w_len[3], const size_t o_len[3],
+                                 uint32_t m, uint32_t n, uint32_t k)
+{
+    if (m == 0 || n == 0 || k == 0)
+        INVALID("qkv_project_int8: M, N, K dimensions must be non-zero");
+    if (k % 16 != 0)
+        INVALID("qkv_project_int8: K must be a multiple of K_TILE_SHARED=16 "
+                "(got %u). The mma.sync.m16n8k16 instance shape requires K-tile size 16; "
+                "K is not edge-padded inside a K-tile.",
+                k);
+    if (n % 2 != 0)
+        INVALID("qkv_project_int8: N must be even (got %u). The store-out path packs "
+                "adjacent f16 output pairs into one .b32; odd N would leave a ragged "
+                "last column that the current store epilogue does not handle.",
+                n);
+    const size_t mk = (size_t)m * k, kn = (size_t)k * n, mn = (size_t)m * n;
+    if (x_len < mk)
+        INVALID("qkv_project_int8: X buffer too small: need %zu f16 (%u\xC3\x97%u), got %zu", mk, m,
+                k, x_len);
+    static const char* wl[3] = {"W_Q", "W_K", "W_V"};
+    static const char* ol[3] = {"Q_out", "K_out", "V_out"};
+    for (int i = 0; i < 3; ++i)
+        if (w_len[i] < kn)
+            INVALID("qkv_project_int8: %s buffer too small: need %zu i8 (%u\xC3\x97%u), got %zu",
+                    wl[i], kn, k, n, w_len[i]);
+    for (int i = 0; i < 3; ++i)
+        if (o_len[i] < mn)
+            INVALID("qkv_project_int8: %s buffer too small: need %zu f16 (%u\xC3\x97%u), got %zu",
+                    ol[i], mn, m, n, o_len[i]);
+    return KAIO_B200_OK;
+}
+
+static int32_t validate_qkv_int4(size_t x_len, const size_t w_len[3], const size_t s_len[3],
+                                 const size_t o_len[3], uint32_t m, uint32_t n, uint32_t k,
+                                 uint32_t group_size)
+{
+    if (m == 0 || n == 0 || k == 0)
+        INVALID("qkv_project_int4: M, N, K dimensions must be non-zero");
+    if (group_size != 128)
+        INVALID("qkv_project_int4: group_size must be 128 (got %u). "
+                "Non-128 group sizes are deferred to a follow-up sprint.",
+                group_size);
+    if (k % 128 != 0)
+        INVALID("qkv_project_int4: K must be a multiple of group_size=128 (got %u). "
+                "Partial groups are not supported.",
+                k);
+    if (n % 2 != 0)
+        INVALID("qkv_project_int4: N must be even (got %u). The store-out path packs "
+                "adjacent f16 output pairs into one .b32; odd N would leave a ragged "
+                "last column that the current store epilogue does not handle.",
+                n);
+    const size_t mk = (size_t)m * k, words = (size_t)(k / 8) * n, groups = k / group_size,
+                 cells = groups * n, mn = (size_t)m * n;
+    if (x_len < mk)
+        INVALID("qkv_project_int4: X buffer too small: need %zu f16 (%u\xC3\x97%u), got %zu", mk, m,
+                k, x_len);
+    static const char* wl[3] = {"W_Q_packed", "W_K_packed", "W_V_packed"};
+    static const char* sl[3] = {"scales_q", "scales_k", "scales_v"};
+    static const char* ol[3] = {"Q_out", "K_out", "V_out"};
+    for (int i = 0; i < 3; ++i)
+        if (w_len[i] < words)
+            INVALID("qkv_project_int4: %s buffer too small: need %zu u32 "
+                    "(%u cols \xC3\x97 %u K-words), got %zu",
+                    wl[i], words, n, k / 8, w_len[i]);
+    for (int i = 0; i < 3; ++i)
+        if (s_len[i] < cells)
+            INVALID("qkv_project_int4: %s buffer too small: need %zu f16 "
+                    "(%zu groups \xC3\x97 %u cols), got %zu",
+                    sl[i], cells, groups, n, s_len[i]);
+    for (int i = 0; i < 3; ++i)
+        if (o_len[i] < mn)
+            INVALID("qkv_project_int4: %s buffer too small: need %zu f16 (%u\xC3\x97%u), got %zu",
+                    ol[i], mn, m, n, o_len[i]);
+    return KAIO_B200_OK;
+}
+
+static const char* WHY_CONSTRAINED =
+    "Either pad inputs to valid shapes, or use the existing f32 `attention` / `attention_flash` "
+    "path instead.";
+
+static int32_t validate_attention_tc(size_t q_len, size_t k_len, size_t v_len, size_t out_len,
+                                     uint32_t seq_q, uint32_t seq_k, uint32_t d_k, uint32_t d_v)
+{
+    if (seq_q == 0 || seq_k == 0 || d_k == 0 || d_v == 0)
+        INVALID("attention_tc dimensions must be non-zero");
+    if (seq_q % 16 != 0)
+        INVALID("attention_tc: seq_q must be a multiple of 16 (got %u). %s", seq_q,
+                WHY_CONSTRAINED);
+    if (seq_k % 16 != 0)
+        INVALID("attention_tc: seq_k must be a multiple of 16 (got %u). %s", seq_k,
+                WHY_CONSTRAINED);
+    if (d_k % 16 != 0)
+        INVALID("attention_tc: d_k must be a multiple of 16 (got %u). %s", d_k, WHY_CONSTRAINED);
+    if (d_v % 8 != 0)
+        INVALID("attention_tc: d_v must be a multiple of 8 (got %u). %s", d_v, WHY_CONSTRAINED);
+    if (seq_k > 384)
+        INVALID("attention_tc: seq_k must be \xE2\x89\xA4 384 (got %u). "
+                "The shared-memory scores buffer caps the sequence length; "
+                "Phase 7's FlashAttention-TC lifts this constraint. %s",
+                seq_k, WHY_CONSTRAINED);
+    if (d_k > 128)
+        INVALID("attention_tc: d_k must be \xE2\x89\xA4 128 (got %u). %s", d_k, WHY_CONSTRAINED);
+    if (d_v > 128)
+        INVALID("attention_tc: d_v must be \xE2\x89\xA4 128 (got %u). %s", d_v, WHY_CONSTRAINED);
+    const size_t qe = (size_t)seq_q * d_k, ke = (size_t)seq_k * d_k, ve = (size_t)seq_k * d_v,
+                 oe = (size_t)seq_q * d_v;
+    if (q_len < qe)
+        INVALID("attention_tc: Q buffer too small: need %zu f16 (%u\xC3\x97%u), got %zu", qe, seq_q,
+                d_k, q_len);
+    if (k_len < ke)
+        INVALID("attention_tc: K buffer too small: need %zu f16 (%u\xC3\x97%u), got %zu", ke, seq_k,
+                d_k, k_len);
+    if (v_len < ve)
+        INVALID("attention_tc: V buffer too small: need %zu f16 (%u\xC3\x97%u), got %zu", ve, seq_k,
+                d_v, v_len);
+    if (out_len < oe)
+        INVALID("attention_tc: out buffer too small: need %zu f32 (%u\xC3\x97%u), got %zu", oe,
+                seq_q, d_v, out_len);
+    return KAIO_B200_OK;
+}
+
+#define REQUIRE_PTR(p, op, name)                                                   \
+    if ((p) == nullptr)                                                            \
+    return fail(KAIO_B200_ERR_INVALID_CONFIG, "%s: %s pointer is null", op, name)
+
+// ---------------------------------------------------------------- op bodies
+static int32_t run_int8(int epi, const int8_t* a, size_t a_len, const int8_t* b, size_t b_len,
+                        void* c, size_t c_len, float scale, const float* a_scale,
+                        const float* w_scale, uint32_t m, uint32_t n, uint32_t k, void* stream)
+{
+    int32_t rc = validate_int8(epi == EPI_S32 ? "i32" : "f32", a_len, b_len, c_len, m, n, k);
+    if (rc)
+        return rc;
+    REQUIRE_PTR(a, "matmul_int8", "A");
+    REQUIRE_PTR(b, "matmul_int8", "B");
+    REQUIRE_PTR(c, "matmul_int8", "C");
+    DeviceCtx* ctx;
+    if ((rc = get_ctx(&ctx)))
+        return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool scales_aligned = epi != EPI_ROWCOL || ((uintptr_t)w_scale % 16 == 0);
+    if (w8a8_fast_path_ok(a, b, c, m, n, k) && scales_aligned)
+        return finish(launch_w8a8_gemm(*ctx, epi, a, b, c, scale, a_scale, w_scale, m, n, k, s),
+                      "matmul_int8", "w8a8_tcgen05");
+    return finish(launch_int8_generic(epi, a, b, c, scale, a_scale, w_scale, m, n, k, s),
+                  "matmul_int8", "int8_generic");
+}
+
+static int32_t run_int4(const kaio_f16* a, size_t a_len, const uint32_t* b, size_t b_len,
+                        const kaio_f16* scales, size_t s_len, void* c, size_t c_len, bool out_f16,
+                        uint32_t m, uint32_t n, uint32_t k, uint32_t group_size, void* stream)
+{
+    int32_t rc =
+        validate_int4(out_f16 ? "f16" : "f32", a_len, b_len, s_len, c_len, m, n, k, group_size);
+    if (rc)
+        return rc;
+    REQUIRE_PTR(a, "matmul_int4", "A");
+    REQUIRE_PTR(b, "matmul_int4", "B packed");
+    REQUIRE_PTR(scales, "matmul_int4", "scales");
+    REQUIRE_PTR(c, "matmul_int4", "C");
+    DeviceCtx* ctx;
+    if ((rc = get_ctx(&ctx)))
+        return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    DqProblem pr;
+    pr.w = b;
+    pr.scales = reinterpret_cast<const __half*>(scales);
+    pr.col_scale = nullptr;
+    pr.scale = 1.0f;
+    pr.out = c;
+    const __half* x = reinterpret_cast<const __half*>(a);
+    if (w4a16_decode_ok(x, &pr, 1, m, n, k)) {
+        const size_t ws = w4a16_decode_workspace_bytes(*ctx, n, k);
+        if ((rc = ensure_workspace(ctx, ws, 4096)))
+            return rc;
+        return finish(launch_w4a16_decode(*ctx, x, pr, out_f16, m, n, k, ctx->workspace,
+                                          ctx->tile_counters, s),
+                      "matmul_int4", "w4a16_decode_splitk");
+    }
+    if (dq_gemm_fast_path_ok(WFMT_S4_PACKED, x, &pr, 1, out_f16, m, n, k))
+        return finish(launch_dq_gemm(*ctx, WFMT_S4_PACKED, x, &pr, 1, out_f16, false, m, n, k, s),
+                      "matmul_int4", "w4a16_tcgen05");
+    return finish(launch_dq_generic(WFMT_S4_PACKED, x, &pr, 1, out_f16, false, m, n, k, s),
+                  "matmul_int4", "w4a16_generic");
+}
+
+static int32_t run_qkv(int wfmt, const char* op, const __half* x, DqProblem probs[3],
+                       bool post_scale, uint32_t m, uint32_t n, uint32_t k, void* stream)
+{
+    for (int i = 0; i < 3; ++i)
+        for (int j = i + 1; j < 3; ++j)
+            if (probs[i].out == probs[j].out)
+                return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                            "%s: the three output buffers must be distinct allocations", op);
+    DeviceCtx* ctx;
+    int32_t rc;
+    if ((rc = get_ctx(&ctx)))
+        return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dq_gemm_fast_path_ok(wfmt, x, probs, 3, true, m, n, k))
+        return finish(launch_dq_gemm(*ctx, wfmt, x, probs, 3, true, post_scale, m, n, k, s), op,
+                      wfmt == WFMT_S8_ROWMAJOR ? "qkv_w8a16_tcgen05" : "qkv_w4a16_tcgen05");
+    return finish(launch_dq_generic(wfmt, x, probs, 3, true, post_scale, m, n, k, s), op,
+                  wfmt == WFMT_S8_ROWMAJOR ? "qkv_w8a16_generic" : "qkv_w4a16_generic");
+}
+
+}  // namespace kaio
+
+using namespace kaio;
+
+// ==================================================================== exported entry points
+
+KAIO_API int32_t kaio_b200_matmul_int8(const int8_t* a, size_t a_len, const int8_t* b, size_t b_len,
+                                       float* c, size_t c_len, float scale, uint32_t m, uint32_t n,
+                                       uint32_t k, void* stream)
+{
+    return run_int8(EPI_SCALAR, a, a_len, b, b_len, c, c_len, scale, nullptr, nullptr, m, n, k,
+                    stream);
+}
+
+KAIO_API int32_t kaio_b200_matmul_int8_scaled(const int8_t* a, size_t a_len, const int8_t* b,
+                                              size_t b_len, float* c, size_t c_len,
+                                              const float* a_scale, size_t a_scale_len,
+                                              const float* w_scale, size_t w_scale_len, uint32_t m,
+                                              uint32_t n, uint32_t k, void* stream)
+{
+    if (a_scale == nullptr || w_scale == nullptr)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG, "matmul_int8_scaled: scale pointer is null");
+    if (a_scale_len < m)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "matmul_int8_scaled: a_scale buffer too small: need %u f32, got %zu", m,
+                    a_scale_len);
+    if (w_scale_len < n)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "matmul_int8_scaled: w_scale buffer too small: need %u f32, got %zu", n,
+                    w_scale_len);
+    return run_int8(EPI_ROWCOL, a, a_len, b, b_len, c, c_len, 1.0f, a_scale, w_scale, m, n, k,
+                    stream);
+}
+
+KAIO_API int32_t kaio_b200_matmul_int8_acc(const int8_t* a, size_t a_len, const int8_t* b,
+                                           size_t b_len, int32_t* acc, size_t acc_len, uint32_t m,
+                                           uint32_t n, uint32_t k, void* stream)
+{
+    return run_int8(EPI_S32, a, a_len, b, b_len, acc, acc_len, 1.0f, nullptr, nullptr, m, n, k,
+                    stream);
+}
+
+KAIO_API int32_t kaio_b200_matmul_int4(const kaio_f16* a, size_t a_len, const uint32_t* b_packed,
+                                       size_t b_len, const kaio_f16* scales, size_t scales_len,
+                                       float* c, size_t c_len, uint32_t m, uint32_t n, uint32_t k,
+                                       uint32_t group_size, void* stream)
+{
+    return run_int4(a, a_len, b_packed, b_len, scales, scales_len, c, c_len, false, m, n, k,
+                    group_size, stream);
+}
+
+KAIO_API int32_t kaio_b200_matmul_int4_f16out(const kaio_f16* a, size_t a_len,
+                                              const uint32_t* b_packed, size_t b_len,
+                                              const kaio_f16* scales, size_t scales_len,
+                                              kaio_f16* c, size_t c_len, uint32_t m, uint32_t n,
+                                              uint32_t k, uint32_t group_size, void* stream)
+{
+    return run_int4(a, a_len, b_packed, b_len, scales, scales_len, c, c_len, true, m, n, k,
+                    group_size, stream);
+}
+
+static int32_t qkv_int8_common(const kaio_f16* x, size_t x_len, const int8_t* const w[3],
+                               const size_t w_len[3], const float scalar[3],
+                               const float* const col[3], kaio_f16* const out[3],
+                               const size_t o_len[3], uint32_t m, uint32_t n, uint32_t k,
+                               void* stream)
+{
+    int32_t rc = validate_qkv_int8(x_len, w_len, o_len, m, n, k);
+    if (rc)
+        return rc;
+    REQUIRE_PTR(x, "qkv_project_int8", "X");
+    DqProblem probs[3];
+    for (int i = 0; i < 3; ++i) {
+        REQUIRE_PTR(w[i], "qkv_project_int8", "W");
+        REQUIRE_PTR(out[i], "qkv_project_int8", "output");
+        probs[i].w = w[i];
+        probs[i].scales = nullptr;
+        probs[i].col_scale = col ? col[i] : nullptr;
+        probs[i].scale = scalar ? scalar[i] : 1.0f;
+        probs[i].out = out[i];
+    }
+    return run_qkv(WFMT_S8_ROWMAJOR, "qkv_project_int8", reinterpret_cast<const __half*>(x), probs,
+                   true, m, n, k, stream);
+}
+
+KAIO_API int32_t kaio_b200_qkv_project_int8(const kaio_f16* x, size_t x_len, const int8_t* w_q,
+                                            size_t w_q_len, const int8_t* w_k, size_t w_k_len,
+                                            const int8_t* w_v, size_t w_v_len, float scale_q,
+                                            float scale_k, float scale_v, kaio_f16* q_out,
+                                            size_t q_len, kaio_f16* k_out, size_t k_len,
+                                            kaio_f16* v_out, size_t v_len, uint32_t m, uint32_t n,
+                                            uint32_t k, void* stream)
+{
+    const int8_t* w[3] = {w_q, w_k, w_v};
+    const size_t wl[3] = {w_q_len, w_k_len, w_v_len};
+    const float sc[3] = {scale_q, scale_k, scale_v};
+    kaio_f16* out[3] = {q_out, k_out, v_out};
+    const size_t ol[3] = {q_len, k_len, v_len};
+    return qkv_int8_common(x, x_len, w, wl, sc, nullptr, out, ol, m, n, k, stream);
+}
+
+KAIO_API int32_t kaio_b200_qkv_project_int8_colscale(
+    const kaio_f16* x, size_t x_len, const int8_t* w_q, size_t w_q_len, const int8_t* w_k,
+    size_t w_k_len, const int8_t* w_v, size_t w_v_len, const float* scale_q, const float* scale_k,
+    const float* scale_v, size_t scale_len, kaio_f16* q_out, size_t q_len, kaio_f16* k_out,
+    size_t k_len, kaio_f16* v_out, size_t v_len, uint32_t m, uint32_t n, uint32_t k, void* stream)
+{
+    if (scale_q == nullptr || scale_k == nullptr || scale_v == nullptr)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "qkv_project_int8_colscale: scale pointer is null");
+    if (scale_len < n)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "qkv_project_int8_colscale: scale buffers too small: need %u f32, got %zu", n,
+                    scale_len);
+    const int8_t* w[3] = {w_q, w_k, w_v};
+    const size_t wl[3] = {w_q_len, w_k_len, w_v_len};
+    const float* col[3] = {scale_q, scale_k, scale_v};
+    kaio_f16* out[3] = {q_out, k_out, v_out};
+    const size_t ol[3] = {q_len, k_len, v_len};
+    return qkv_int8_common(x, x_len, w, wl, nullptr, col, out, ol, m, n, k, stream);
+}
+
+KAIO_API int32_t kaio_b200_qkv_project_int4(
+    const kaio_f16* x, size_t x_len, const uint32_t* w_q_packed, size_t w_q_len,
+    const uint32_t* w_k_packed, size_t w_k_len, const uint32_t* w_v_packed, size_t w_v_len,
+    const kaio_f16* scales_q, size_t scales_q_len, const kaio_f16* scales_k, size_t scales_k_len,
+    const kaio_f16* scales_v, size_t scales_v_len, kaio_f16* q_out, size_t q_len, kaio_f16* k_out,
+    size_t k_len, kaio_f16* v_out, size_t v_len, uint32_t m, uint32_t n, uint32_t k,
+    uint32_t group_size, void* stream)
+{
+    const size_t wl[3] = {w_q_len, w_k_len, w_v_len};
+    const size_t sl[3] = {scales_q_len, scales_k_len, scales_v_len};
+    const size_t ol[3] = {q_len, k_len, v_len};
+    int32_t rc = validate_qkv_int4(x_len, wl, sl, ol, m, n, k, group_size);
+    if (rc)
+        return rc;
+    const uint32_t* w[3] = {w_q_packed, w_k_packed, w_v_packed};
+    const kaio_f16* sc[3] = {scales_q, scales_k, scales_v};
+    kaio_f16* out[3] = {q_out, k_out, v_out};
+    REQUIRE_PTR(x, "qkv_project_int4", "X");
+    DqProblem probs[3];
+    for (int i = 0; i < 3; ++i) {
+        REQUIRE_PTR(w[i], "qkv_project_int4", "W packed");
+        REQUIRE_PTR(sc[i], "qkv_project_int4", "scales");
+        REQUIRE_PTR(out[i], "qkv_project_int4", "output");
+        probs[i].w = w[i];
+        probs[i].scales = reinterpret_cast<const __half*>(sc[i]);
+        probs[i].col_scale = nullptr;
+        probs[i].scale = 1.0f;
+        probs[i].out = out[i];
+    }
+    return run_qkv(WFMT_S4_PACKED, "qkv_project_int4", reinterpret_cast<const __half*>(x), probs,
+                   false, m, n, k, stream);
+}
+
+KAIO_API int32_t kaio_b200_attention_tc(const kaio_f16* q, size_t q_len, const kaio_f16* k,
+                                        size_t k_len, const kaio_f16* v, size_t v_len, float* out,
+                                        size_t out_len, uint32_t seq_q, uint32_t seq_k,
+                                        uint32_t d_k, uint32_t d_v, int32_t causal, void* stream)
+{
+    int32_t rc = validate_attention_tc(q_len, k_len, v_len, out_len, seq_q, seq_k, d_k, d_v);
+    if (rc)
+        return rc;
+    REQUIRE_PTR(q, "attention_tc", "Q");
+    REQUIRE_PTR(k, "attention_tc", "K");
+    REQUIRE_PTR(v, "attention_tc", "V");
+    REQUIRE_PTR(out, "attention_tc", "out");
+    DeviceCtx* ctx;
+    if ((rc = get_ctx(&ctx)))
+        return rc;
+    AttnParams p = {};
+    p.q = reinterpret_cast<const __half*>(q);
+    p.k = reinterpret_cast<const __half*>(k);
+    p.v = reinterpret_cast<const __half*>(v);
+    p.out = out;
+    p.batch = 1;
+    p.heads = 1;
+    p.seq_q = seq_q;
+    p.seq_k = seq_k;
+    p.d_k = d_k;
+    p.d_v = d_v;
+    p.q_row = d_k;
+    p.k_row = d_k;
+    p.v_row = d_v;
+    p.o_row = d_v;
+    p.causal = causal ? 1 : 0;
+    p.out_f16 = 0;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (flash_attention_ok(p))
+        return finish(launch_flash_attention(*ctx, p, s), "attention_tc", "flash_tcgen05");
+    return finish(launch_attention_generic(p, s), "attention_tc", "attention_generic");
+}
+
+KAIO_API int32_t kaio_b200_attention_mha_f16(const kaio_f16* q, size_t q_len, const kaio_f16* k,
+                                             size_t k_len, const kaio_f16* v, size_t v_len,
+                                             kaio_f16* out, size_t out_len, uint32_t batch,
+                                             uint32_t heads, uint32_t seq_q, uint32_t seq_k,
+                                             uint32_t head_dim, uint32_t row_stride,
+                                             int32_t causal, void* stream)
+{
+    const char* op = "attention_mha_f16";
+    if (batch == 0 || heads == 0 || seq_q == 0 || seq_k == 0 || head_dim == 0)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG, "%s dimensions must be non-zero", op);
+    if ((uint64_t)heads * head_dim > row_stride)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: row_stride (%u) must be at least heads*head_dim (%llu)", op, row_stride,
+                    (unsigned long long)heads * head_dim);
+    if (head_dim > 256)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG, "%s: head_dim must be \xE2\x89\xA4 256 (got %u)",
+                    op, head_dim);
+    const size_t need_q = ((size_t)batch * seq_q - 1) * row_stride + (size_t)heads * head_dim;
+    const size_t need_k = ((size_t)batch * seq_k - 1) * row_stride + (size_t)heads * head_dim;
+    if (q_len < need_q)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: Q buffer too small: need %zu f16, got %zu", op, need_q, q_len);
+    if (k_len < need_k)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: K buffer too small: need %zu f16, got %zu", op, need_k, k_len);
+    if (v_len < need_k)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: V buffer too small: need %zu f16, got %zu", op, need_k, v_len);
+    if (out_len < need_q)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: out buffer too small: need %zu f16, got %zu", op, need_q, out_len);
+    REQUIRE_PTR(q, op, "Q");
+    REQUIRE_PTR(k, op, "K");
+    REQUIRE_PTR(v, op, "V");
+    REQUIRE_PTR(out, op, "out");
+    DeviceCtx* ctx;
+    int32_t rc;
+    if ((rc = get_ctx(&ctx)))
+        return rc;
+    AttnParams p = {};
+    p.q = reinterpret_cast<const __half*>(q);
+    p.k = reinterpret_cast<const __half*>(k);
+    p.v = reinterpret_cast<const __half*>(v);
+    p.out = out;
+    p.batch = batch;
+    p.heads = heads;
+    p.seq_q = seq_q;
+    p.seq_k = seq_k;
+    p.d_k = head_dim;
+    p.d_v = head_dim;
+    p.q_row = p.k_row = p.v_row = p.o_row = row_stride;
+    p.q_head = p.k_head = p.v_head = p.o_head = head_dim;
+    p.q_batch = p.o_batch = (uint64_t)seq_q * row_stride;
+    p.k_batch = p.v_batch = (uint64_t)seq_k * row_stride;
+    p.causal = causal ? 1 : 0;
+    p.out_f16 = 1;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (flash_attention_ok(p))
+        return finish(launch_flash_attention(*ctx, p, s), op, "flash_tcgen05");
+    return finish(launch_attention_generic(p, s), op, "attention_generic");
+}
+
+KAIO_API const char* kaio_b200_last_error(void)
+{
+    return g_last_error.c_str();
+}
+
+KAIO_API const char* kaio_b200_last_variant(void)
+{
+    return g_last_variant;
+}
+
+KAIO_API int32_t kaio_b200_device_status(void* stream, uint32_t code[4])
+{
+    DeviceCtx* ctx;
+    int32_t rc;
+    if ((rc = get_ctx(&ctx)))
+        return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t err = cudaStreamSynchronize(s);
+    if (err != cudaSuccess)
+        return fail_cuda(err, "cudaStreamSynchronize");
+    uint32_t host[4] = {0, 0, 0, 0};
+    err = cudaMemcpy(host, ctx->status, sizeof(host), cudaMemcpyDeviceToHost);
+    if (err != cudaSuccess)
+        return fail_cuda(err, "cudaMemcpy(status)");
+    if (code)
+        for (int i = 0; i < 4; ++i)
+            code[i] = host[i];
+    if (host[0] != 0) {
+        cudaMemset(ctx->status, 0, sizeof(host));
+        return fail(KAIO_B200_ERR_TIMEOUT,
+                    "device-side bounded wait gave up: code %u, block %u, site %u, kernel %u",
+                    host[0], host[1], host[2], host[3]);
+    }
+    return KAIO_B200_OK;
+}
+
+KAIO_API void kaio_b200_shutdown(void)
+{
+    std::lock_guard<std::mutex> lock(g_ctx_mutex);
+    int cur = -1;
+    cudaGetDevice(&cur);
+    for (int d = 0; d < MAX_DEVICES; ++d) {
+        DeviceCtx& c = g_ctx[d];
+        if (c.device < 0)
+            continue;
+        cudaSetDevice(d);
+        if (c.status)
+            cudaFree(c.status);
+        if (c.workspace)
+            cudaFree(c.workspace);
+        if (c.tile_counters)
+            cudaFree(c.tile_counters);
+        c = DeviceCtx();
+    }
+    if (cur >= 0)
+        cudaSetDevice(cur);
+}
+
+KAIO_API int32_t kaio_b200_version(void)
+{
+    return 1000;
+}

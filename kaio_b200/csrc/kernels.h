@@ -1,0 +1,97 @@
+// Internal interface between the C-ABI layer (api.cu) and the kernel translation units.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace kaio {
+
+// Epilogue selectors of the W8A8 GEMM.
+enum : int {
+    EPI_SCALAR = 0,  // f32 out = (acc as f32) * scale
+    EPI_ROWCOL = 1,  // f32 out = ((acc as f32) * a_scale[i]) * w_scale[j]
+    EPI_S32 = 2,     // s32 out = acc
+};
+
+// Weight encodings of the dequantising GEMM (f16 activations).
+enum : int {
+    WFMT_S8_ROWMAJOR = 0,  // s8 [K,N] row-major (fused QKV W8A16)
+    WFMT_S4_PACKED = 1,    // s4, 8 per u32 along K, words column-major, group-128 f16 scales
+};
+
+// Per-device state owned by the library.
+struct DeviceCtx {
+    int device = -1;
+    int num_sms = 0;
+    int cc_major = 0, cc_minor = 0;
+    uint32_t* status = nullptr;       // uint32[4] status block, zero = no error
+    void* workspace = nullptr;        // split-K partial sums
+    size_t workspace_bytes = 0;
+    uint32_t* tile_counters = nullptr;  // split-K arrival counters (self-resetting)
+    size_t num_tile_counters = 0;
+};
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time libcuda).
+cudaError_t encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t elem_bytes,
+                                 const void* base, uint64_t inner, uint64_t outer,
+                                 uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer,
+                                 CUtensorMapSwizzle swizzle);
+
+// ---------------------------------------------------------------- W8A8
+bool w8a8_fast_path_ok(const void* a, const void* b, const void* out, uint32_t m, uint32_t n,
+                       uint32_t k);
+cudaError_t launch_w8a8_gemm(const DeviceCtx& ctx, int epi, const int8_t* a, const int8_t* b,
+                             void* out, float scale, const float* a_scale, const float* w_scale,
+                             uint32_t m, uint32_t n, uint32_t k, cudaStream_t stream);
+cudaError_t launch_int8_generic(int epi, const int8_t* a, const int8_t* b, void* out, float scale,
+                                const float* a_scale, const float* w_scale, uint32_t m, uint32_t n,
+                                uint32_t k, cudaStream_t stream);
+
+// ---------------------------------------------------------------- dequantising GEMMs
+// One "problem" = one weight matrix + one output; the fused QKV ops pass three.
+struct DqProblem {
+    const void* w;          // s8 [K,N] or packed u32 [(K/8)*N]
+    const __half* scales;   // group scales f16 [K/128, N] (WFMT_S4_PACKED) or nullptr
+    const float* col_scale; // per-column f32 post-scale or nullptr
+    float scale;            // scalar f32 post-scale (used when col_scale == nullptr)
+    void* out;              // f32 or f16 [M,N]
+};
+
+cudaError_t launch_dq_generic(int wfmt, const __half* x, const DqProblem* probs, int num_probs,
+                              bool out_f16, bool post_scale, uint32_t m, uint32_t n, uint32_t k,
+                              cudaStream_t stream);
+
+bool w4a16_decode_ok(const void* x, const DqProblem* probs, int num_probs, uint32_t m, uint32_t n,
+                     uint32_t k);
+size_t w4a16_decode_workspace_bytes(const DeviceCtx& ctx, uint32_t n, uint32_t k);
+cudaError_t launch_w4a16_decode(const DeviceCtx& ctx, const __half* x, const DqProblem& prob,
+                                bool out_f16, uint32_t m, uint32_t n, uint32_t k, void* workspace,
+                                uint32_t* counters, cudaStream_t stream);
+
+bool dq_gemm_fast_path_ok(int wfmt, const void* x, const DqProblem* probs, int num_probs,
+                          bool out_f16, uint32_t m, uint32_t n, uint32_t k);
+cudaError_t launch_dq_gemm(const DeviceCtx& ctx, int wfmt, const __half* x, const DqProblem* probs,
+                           int num_probs, bool out_f16, bool post_scale, uint32_t m, uint32_t n,
+                           uint32_t k, cudaStream_t stream);
+
+// ---------------------------------------------------------------- attention
+struct AttnParams {
+    const __half *q, *k, *v;
+    void* out;  // f32 or f16
+    uint32_t batch, heads, seq_q, seq_k, d_k, d_v;
+    // element strides: row stride and per-head / per-batch offsets
+    uint64_t q_row, k_row, v_row, o_row;
+    uint64_t q_head, k_head, v_head, o_head;
+    uint64_t q_batch, k_batch, v_batch, o_batch;
+    int causal;
+    int out_f16;
+};
+
+cudaError_t launch_attention_generic(const AttnParams& p, cudaStream_t stream);
+bool flash_attention_ok(const AttnParams& p);
+cudaError_t launch_flash_attention(const DeviceCtx& ctx, const AttnParams& p, cudaStream_t stream);
+
+}  // namespace kaio

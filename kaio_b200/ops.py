@@ -1,0 +1,172 @@
+"""Host-side mirror of the ``kaio-ops`` quantized entry points over the C ABI.
+
+Names, argument order and meaning follow the Rust functions
+(``kaio-ops/src/lib.rs:92-123``); a ``torch.Tensor`` on a CUDA device plays the role of
+``GpuBuffer<T>`` (``numel()`` is ``GpuBuffer::len()``), :class:`KaioDevice` the role of
+``kaio_runtime::KaioDevice`` (an ordinal plus the stream work is enqueued on).  Like the
+reference, every call enqueues asynchronously and returns ``None``; errors raise
+:class:`kaio_b200.errors.KaioError` subclasses carrying the reference's message text.
+
+PyTorch is used for device memory and streams only; all arithmetic happens in the CUDA
+library.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+from .errors import from_code
+
+GROUP_SIZE = 128
+
+
+class KaioDevice:
+    """``KaioDevice::new(ordinal)`` (kaio-runtime/src/device.rs:59-115)."""
+
+    def __init__(self, ordinal: int = 0, stream: "torch.cuda.Stream | None" = None):
+        self.ordinal = int(ordinal)
+        self._stream = stream
+
+    def stream_handle(self) -> int:
+        s = self._stream if self._stream is not None else torch.cuda.current_stream(self.ordinal)
+        return int(s.cuda_stream)
+
+    def info(self):
+        p = torch.cuda.get_device_properties(self.ordinal)
+        return {"name": p.name, "compute_capability": (p.major, p.minor), "total_memory": p.total_memory}
+
+    def synchronize(self):
+        torch.cuda.synchronize(self.ordinal)
+
+
+def _buf(t: torch.Tensor, dtype: torch.dtype, what: str):
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{what}: expected a torch.Tensor, got {type(t).__name__}")
+    if t.dtype != dtype:
+        raise TypeError(f"{what}: expected dtype {dtype}, got {t.dtype}")
+    if not t.is_cuda:
+        raise TypeError(f"{what}: expected a CUDA tensor (there is no CPU fallback)")
+    if not t.is_contiguous():
+        raise TypeError(f"{what}: expected a contiguous tensor")
+    return C.c_void_p(t.data_ptr()), C.c_size_t(t.numel())
+
+
+def _check(code: int):
+    if code != 0:
+        raise from_code(code, _lib.load().kaio_b200_last_error().decode("utf-8", "replace"))
+
+
+def _call(device: KaioDevice, name: str, *args):
+    lib = _lib.load()
+    with torch.cuda.device(device.ordinal):
+        _check(getattr(lib, name)(*args, C.c_void_p(device.stream_handle())))
+
+
+def last_variant() -> str:
+    """Kernel variant the last call on this thread dispatched to."""
+    return _lib.load().kaio_b200_last_variant().decode()
+
+
+def device_status(device: KaioDevice):
+    """Synchronise and read the device status block; raises ``DeviceTimeout`` if set."""
+    lib = _lib.load()
+    code = (C.c_uint32 * 4)()
+    with torch.cuda.device(device.ordinal):
+        rc = lib.kaio_b200_device_status(C.c_void_p(device.stream_handle()), code)
+    _check(rc)
+    return list(code)
+
+
+# ------------------------------------------------------------------ W8A8
+
+def matmul_int8(device, a, b, c, scale, m, n, k):
+    """``kaio_ops::matmul_int8`` (kaio-ops/src/matmul_int8_kernel.rs:1468-1512)."""
+    _call(device, "kaio_b200_matmul_int8", *_buf(a, torch.int8, "a"), *_buf(b, torch.int8, "b"),
+          *_buf(c, torch.float32, "c"), C.c_float(scale), m, n, k)
+
+
+def matmul_int8_scaled(device, a, b, c, a_scale, w_scale, m, n, k):
+    """Extension: per-row x per-column scales."""
+    _call(device, "kaio_b200_matmul_int8_scaled", *_buf(a, torch.int8, "a"), *_buf(b, torch.int8, "b"),
+          *_buf(c, torch.float32, "c"), *_buf(a_scale, torch.float32, "a_scale"),
+          *_buf(w_scale, torch.float32, "w_scale"), m, n, k)
+
+
+def matmul_int8_acc(device, a, b, acc, m, n, k):
+    """Extension: raw s32 accumulators."""
+    _call(device, "kaio_b200_matmul_int8_acc", *_buf(a, torch.int8, "a"), *_buf(b, torch.int8, "b"),
+          *_buf(acc, torch.int32, "acc"), m, n, k)
+
+
+# ------------------------------------------------------------------ W4A16
+
+def matmul_int4(device, a, b_packed, scales, c, m, n, k, group_size):
+    """``kaio_ops::matmul_int4`` (kaio-ops/src/matmul_int4_kernel.rs:2126-2171).
+
+    ``b_packed`` is an int32 tensor holding the u32 words (torch has no uint32 arithmetic; the
+    bits are what matters).  ``c`` float32 selects the reference form, float16 the extension.
+    """
+    name = "kaio_b200_matmul_int4" if c.dtype == torch.float32 else "kaio_b200_matmul_int4_f16out"
+    _call(device, name, *_buf(a, torch.float16, "a"), *_buf(b_packed, torch.int32, "b_packed"),
+          *_buf(scales, torch.float16, "scales"), *_buf(c, c.dtype if c.dtype in (torch.float32, torch.float16)
+                                                        else torch.float32, "c"),
+          m, n, k, group_size)
+
+
+# ------------------------------------------------------------------ fused QKV
+
+def qkv_project_int8(device, x, w_q, w_k, w_v, scale_q, scale_k, scale_v, q_out, k_out, v_out, m, n, k):
+    """``kaio_ops::qkv_project_int8`` (kaio-ops/src/qkv_project_int8_kernel.rs:2008-2064).
+
+    Scalar scales select the reference form; float32 tensors of length ``n`` the per-column
+    extension.
+    """
+    if isinstance(scale_q, torch.Tensor):
+        sq, sl = _buf(scale_q, torch.float32, "scale_q")
+        sk, _ = _buf(scale_k, torch.float32, "scale_k")
+        sv, _ = _buf(scale_v, torch.float32, "scale_v")
+        sl = C.c_size_t(min(scale_q.numel(), scale_k.numel(), scale_v.numel()))
+        _call(device, "kaio_b200_qkv_project_int8_colscale", *_buf(x, torch.float16, "x"),
+              *_buf(w_q, torch.int8, "w_q"), *_buf(w_k, torch.int8, "w_k"), *_buf(w_v, torch.int8, "w_v"),
+              sq, sk, sv, sl, *_buf(q_out, torch.float16, "q_out"), *_buf(k_out, torch.float16, "k_out"),
+              *_buf(v_out, torch.float16, "v_out"), m, n, k)
+        return
+    _call(device, "kaio_b200_qkv_project_int8", *_buf(x, torch.float16, "x"),
+          *_buf(w_q, torch.int8, "w_q"), *_buf(w_k, torch.int8, "w_k"), *_buf(w_v, torch.int8, "w_v"),
+          C.c_float(scale_q), C.c_float(scale_k), C.c_float(scale_v),
+          *_buf(q_out, torch.float16, "q_out"), *_buf(k_out, torch.float16, "k_out"),
+          *_buf(v_out, torch.float16, "v_out"), m, n, k)
+
+
+def qkv_project_int4(device, x, w_q_packed, w_k_packed, w_v_packed, scales_q, scales_k, scales_v,
+                     q_out, k_out, v_out, m, n, k, group_size):
+    """``kaio_ops::qkv_project_int4`` (kaio-ops/src/qkv_project_int4_kernel.rs:1495-1555)."""
+    _call(device, "kaio_b200_qkv_project_int4", *_buf(x, torch.float16, "x"),
+          *_buf(w_q_packed, torch.int32, "w_q_packed"), *_buf(w_k_packed, torch.int32, "w_k_packed"),
+          *_buf(w_v_packed, torch.int32, "w_v_packed"), *_buf(scales_q, torch.float16, "scales_q"),
+          *_buf(scales_k, torch.float16, "scales_k"), *_buf(scales_v, torch.float16, "scales_v"),
+          *_buf(q_out, torch.float16, "q_out"), *_buf(k_out, torch.float16, "k_out"),
+          *_buf(v_out, torch.float16, "v_out"), m, n, k, group_size)
+
+
+# ------------------------------------------------------------------ attention
+
+def attention_tc(device, q, k, v, out, seq_q, seq_k, d_k, d_v):
+    """``kaio_ops::attention_tc`` (kaio-ops/src/attention_tc_kernel.rs:2240-2254)."""
+    _call(device, "kaio_b200_attention_tc", *_buf(q, torch.float16, "q"), *_buf(k, torch.float16, "k"),
+          *_buf(v, torch.float16, "v"), *_buf(out, torch.float32, "out"), seq_q, seq_k, d_k, d_v, 0)
+
+
+def attention_tc_causal(device, q, k, v, out, seq_q, seq_k, d_k, d_v):
+    """``kaio_ops::attention_tc_causal`` (kaio-ops/src/attention_tc_kernel.rs:2257-2271)."""
+    _call(device, "kaio_b200_attention_tc", *_buf(q, torch.float16, "q"), *_buf(k, torch.float16, "k"),
+          *_buf(v, torch.float16, "v"), *_buf(out, torch.float32, "out"), seq_q, seq_k, d_k, d_v, 1)
+
+
+def attention_mha_f16(device, q, k, v, out, batch, heads, seq_q, seq_k, head_dim, row_stride, causal):
+    """Extension: batched multi-head attention on ``[batch*seq, heads*head_dim]`` f16 buffers."""
+    _call(device, "kaio_b200_attention_mha_f16", *_buf(q, torch.float16, "q"), *_buf(k, torch.float16, "k"),
+          *_buf(v, torch.float16, "v"), *_buf(out, torch.float16, "out"), batch, heads, seq_q, seq_k,
+          head_dim, row_stride, 1 if causal else 0)

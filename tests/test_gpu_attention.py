@@ -1,0 +1,70 @@
+"""GPU parity of attention_tc / attention_tc_causal and the multi-head extension.
+
+Cases restate kaio-ops/tests/attention_tc_api.rs; tolerance abs < 5e-3 OR rel < 2e-2
+(kaio-ops/tests/common/mod.rs:249-284).
+"""
+import numpy as np
+import pytest
+import torch
+
+from kaio_b200 import InvalidConfig, ops
+from helpers import assert_attention_close, dev, device, host
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(16, 16, 16, 8), (32, 32, 32, 32), (64, 128, 64, 64), (64, 384, 64, 64), (16, 32, 16, 8),
+          (128, 384, 128, 128), (256, 256, 128, 128)]
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("sq,sk,dk,dv", SHAPES)
+def test_attention_tc(oracle, sq, sk, dk, dv, causal):
+    q, k, v = oracle.patterned_f16(sq * dk), oracle.patterned_f16(sk * dk), oracle.patterned_f16(sk * dv)
+    want = oracle.attention(q, k, v, sq, sk, dk, dv, causal=causal)
+    out = torch.full((sq * dv,), float("nan"), device="cuda", dtype=torch.float32)
+    fn = ops.attention_tc_causal if causal else ops.attention_tc
+    fn(device(), dev(q), dev(k), dev(v), out, sq, sk, dk, dv)
+    assert ops.device_status(device())[0] == 0
+    assert_attention_close(host(out, (sq, dv)), want)
+
+
+def test_causal_row0_self_only(oracle):
+    """attention_tc_api.rs:153-201."""
+    sq = sk = 16
+    dk, dv = 16, 8
+    q, k = oracle.patterned_f16(sq * dk), oracle.patterned_f16(sk * dk)
+    v = np.repeat(((np.arange(sk, dtype=np.float32) + 1.0) * np.float32(0.1))[:, None], dv, 1).astype(np.float16)
+    out = torch.zeros(sq * dv, device="cuda", dtype=torch.float32)
+    ops.attention_tc_causal(device(), dev(q), dev(k), dev(v), out, sq, sk, dk, dv)
+    assert np.all(np.abs(host(out, (sq, dv))[0] - 0.1) < 5e-3)
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("b,h,s,d", [(2, 3, 64, 32), (1, 2, 256, 128), (2, 4, 512, 128), (1, 2, 1152, 128),
+                                     (1, 1, 200, 64)])
+def test_mha_f16(oracle, b, h, s, d, causal):
+    rng = np.random.default_rng(b * 1000 + h * 100 + s + d)
+    stride = h * d
+    q, k, v = [rng.standard_normal((b * s, stride)).astype(np.float16) for _ in range(3)]
+    want = np.zeros((b * s, stride), np.float16)
+    for bi in range(b):
+        for hi in range(h):
+            off = bi * s * stride + hi * d
+            oracle.attention(q.reshape(-1)[off:], k.reshape(-1)[off:], v.reshape(-1)[off:], s, s, d, d,
+                             causal=causal, strides=(stride,) * 4, f16_out=True, out=want.reshape(-1)[off:])
+    out = torch.full((b * s * stride,), float("nan"), device="cuda", dtype=torch.float16)
+    ops.attention_mha_f16(device(), dev(q), dev(k), dev(v), out, b, h, s, s, d, stride, causal)
+    assert ops.device_status(device())[0] == 0
+    assert_attention_close(host(out, (b * s, stride)).astype(np.float32), want.astype(np.float32))
+
+
+def test_rejects_bad_arguments():
+    d = device()
+    t = torch.zeros(16 * 16, device="cuda", dtype=torch.float16)
+    o = torch.zeros(16 * 8, device="cuda", dtype=torch.float32)
+    with pytest.raises(InvalidConfig, match="seq_q must be a multiple of 16"):
+        ops.attention_tc(d, t, t, t, o, 17, 16, 16, 8)
+    with pytest.raises(InvalidConfig, match="seq_k must be"):
+        ops.attention_tc(d, t, t, t, o, 16, 400, 16, 8)
+    with pytest.raises(InvalidConfig, match="K buffer too small"):
+        ops.attention_tc(d, t, t[:100], t, o, 16, 16, 16, 8)
