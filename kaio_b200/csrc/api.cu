@@ -389,7 +389,7 @@ static int32_t run_int4(const kaio_f16* a, size_t a_len, const uint32_t* b, size
     const __half* x = reinterpret_cast<const __half*>(a);
     if (w4a16_decode_ok(x, &pr, 1, m, n, k)) {
         const size_t ws = w4a16_decode_workspace_bytes(*ctx, n, k);
-        if ((rc = ensure_workspace(ctx, ws, 4096)))
+        if ((rc = ensure_workspace(ctx, ws, w4a16_decode_num_counters(n))))
             return rc;
         return finish(launch_w4a16_decode(*ctx, x, pr, out_f16, m, n, k, ctx->workspace,
                                           ctx->tile_counters, s),

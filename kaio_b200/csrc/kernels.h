@@ -67,6 +67,7 @@ cudaError_t launch_dq_generic(int wfmt, const __half* x, const DqProblem* probs,
 bool w4a16_decode_ok(const void* x, const DqProblem* probs, int num_probs, uint32_t m, uint32_t n,
                      uint32_t k);
 size_t w4a16_decode_workspace_bytes(const DeviceCtx& ctx, uint32_t n, uint32_t k);
+size_t w4a16_decode_num_counters(uint32_t n);
 cudaError_t launch_w4a16_decode(const DeviceCtx& ctx, const __half* x, const DqProblem& prob,
                                 bool out_f16, uint32_t m, uint32_t n, uint32_t k, void* workspace,
                                 uint32_t* counters, cudaStream_t stream);
