@@ -82,6 +82,22 @@ int32_t kaio_b200_matmul_int4_f16out(const kaio_f16* a, size_t a_len, const uint
                                      kaio_f16* c, size_t c_len, uint32_t m, uint32_t n, uint32_t k,
                                      uint32_t group_size, void* stream);
 
+/* No counterpart in the reference.  kaio_b200_matmul_int4 for decode shapes (m <= 16) that
+ * allocates nothing: same arguments, same result, but the split-K scratch (partial tiles,
+ * arrival counters, status words) lives in a fixed ~2.6 MB array inside the library instead of a
+ * cudaMalloc'd workspace.  It is for callers that cannot allocate at call time: a host runtime
+ * whose memory pool already owns all device memory (a later cudaMalloc would fail), or a
+ * latency-critical loop that must not hit the device-wide synchronisation an allocation implies.
+ * Limits (rejected with KAIO_B200_ERR_INVALID_CONFIG): m <= 16, n <= 524288, a device with at
+ * most 160 SMs, 16-byte aligned a / b_packed.  The first call on each device looks up the
+ * array's device address; make that call before any stream capture.  Every call on a device
+ * shares the one array, so calls that may overlap on the GPU (different streams) race: order
+ * them.  The call clears the counters and status words it needs on `stream` before launching. */
+int32_t kaio_b200_matmul_int4_noalloc(const kaio_f16* a, size_t a_len, const uint32_t* b_packed,
+                                      size_t b_len, const kaio_f16* scales, size_t scales_len,
+                                      float* c, size_t c_len, uint32_t m, uint32_t n, uint32_t k,
+                                      uint32_t group_size, void* stream);
+
 /* ---- fused QKV projection ---------------------------------------------------------- */
 
 /* Replaces kaio_ops::qkv_project_int8 (kaio-ops/src/qkv_project_int8_kernel.rs:2008-2064),

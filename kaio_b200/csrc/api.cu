@@ -677,6 +677,111 @@ KAIO_API int32_t kaio_b200_attention_mha_f16(const kaio_f16* q, size_t q_len, co
     return finish(launch_attention_generic(p, s), op, "attention_generic");
 }
 
+// ---------------------------------------------------------------- allocation-free decode entry
+// Scratch of kaio_b200_matmul_int4_noalloc: split-K partial tiles, tile arrival counters and a
+// status block, in a fixed array that is part of the loaded module (every GPU that loads the
+// library holds these ~2.6 MB until the process exits).
+namespace kaio {
+constexpr size_t NOALLOC_MAX_CTAS = 160;         // one CTA per SM; B200 has 148
+constexpr size_t NOALLOC_MAX_TILES = 4096;       // column tiles of 128 -> N <= 524288
+constexpr size_t NOALLOC_PARTIAL_BYTES = NOALLOC_MAX_CTAS * 2 * 16 * 128 * sizeof(float);
+constexpr size_t NOALLOC_COUNTER_BYTES = NOALLOC_MAX_TILES * sizeof(uint32_t);
+constexpr size_t NOALLOC_STATUS_BYTES = 256;
+constexpr size_t NOALLOC_SCRATCH_BYTES =
+    NOALLOC_PARTIAL_BYTES + NOALLOC_COUNTER_BYTES + NOALLOC_STATUS_BYTES;
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+
+// Device address of g_noalloc_scratch per device.  In host code the array's name is only a
+// handle for the runtime; the address a kernel can use comes from cudaGetSymbolAddress, asked
+// once per device with that device current.
+static unsigned char* g_noalloc_ptr[MAX_DEVICES] = {};
+static int g_noalloc_sms[MAX_DEVICES] = {};
+static std::mutex g_noalloc_mutex;
+}  // namespace kaio
+
+KAIO_API int32_t kaio_b200_matmul_int4_noalloc(const kaio_f16* a, size_t a_len,
+                                               const uint32_t* b_packed, size_t b_len,
+                                               const kaio_f16* scales, size_t scales_len, float* c,
+                                               size_t c_len, uint32_t m, uint32_t n, uint32_t k,
+                                               uint32_t group_size, void* stream)
+{
+    const char* op = "matmul_int4_noalloc";
+    int32_t rc = validate_int4("f32", a_len, b_len, scales_len, c_len, m, n, k, group_size);
+    if (rc)
+        return rc;
+    REQUIRE_PTR(a, op, "A");
+    REQUIRE_PTR(b_packed, op, "B packed");
+    REQUIRE_PTR(scales, op, "scales");
+    REQUIRE_PTR(c, op, "C");
+    if (m > 16)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: M must be at most 16 (got %u); larger M has no allocation-free variant",
+                    op, m);
+    if (w4a16_decode_num_counters(n) > NOALLOC_MAX_TILES)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: N must be at most %zu (got %u): the fixed scratch holds %zu tile counters",
+                    op, NOALLOC_MAX_TILES * 128, n, NOALLOC_MAX_TILES);
+    DqProblem pr;
+    pr.w = b_packed;
+    pr.scales = reinterpret_cast<const __half*>(scales);
+    pr.col_scale = nullptr;
+    pr.scale = 1.0f;
+    pr.out = c;
+    const __half* x = reinterpret_cast<const __half*>(a);
+    if (!w4a16_decode_ok(x, &pr, 1, m, n, k))
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: A and B packed must be 16-byte aligned device pointers", op);
+
+    int dev = -1;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess)
+        return fail_cuda(err, "cudaGetDevice");
+    if (dev < 0 || dev >= MAX_DEVICES)
+        return fail(KAIO_B200_ERR_CUDA, "device ordinal %d out of range", dev);
+    {
+        // One-time set-up for this device (first call on it; do it before any stream capture).
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        if (g_noalloc_ptr[dev] == nullptr) {
+            int major = 0, sms = 0;
+            err = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+            if (err != cudaSuccess)
+                return fail_cuda(err, "cudaDeviceGetAttribute");
+            if (major != 10)
+                return fail(KAIO_B200_ERR_UNSUPPORTED_ARCH,
+                            "kaio_b200 kernels are built for sm_100a only; device %d is sm_%dx", dev,
+                            major);
+            err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            if (err != cudaSuccess)
+                return fail_cuda(err, "cudaDeviceGetAttribute");
+            unsigned char* ptr = nullptr;
+            err = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch);
+            if (err != cudaSuccess || ptr == nullptr)
+                return fail_cuda(err, "cudaGetSymbolAddress(noalloc scratch)");
+            g_noalloc_sms[dev] = sms;
+            g_noalloc_ptr[dev] = ptr;
+        }
+    }
+    DeviceCtx ctx;
+    ctx.device = dev;
+    ctx.num_sms = g_noalloc_sms[dev];
+    unsigned char* base = g_noalloc_ptr[dev];
+    ctx.status = reinterpret_cast<uint32_t*>(base + NOALLOC_PARTIAL_BYTES + NOALLOC_COUNTER_BYTES);
+    if (w4a16_decode_workspace_bytes(ctx, n, k) > NOALLOC_PARTIAL_BYTES)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: this device needs %zu bytes of split-K scratch, the fixed array holds %zu",
+                    op, w4a16_decode_workspace_bytes(ctx, n, k), NOALLOC_PARTIAL_BYTES);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // The array keeps whatever the previous call left: counters and status must start at zero.
+    err = cudaMemsetAsync(base + NOALLOC_PARTIAL_BYTES, 0,
+                          NOALLOC_COUNTER_BYTES + NOALLOC_STATUS_BYTES, s);
+    if (err != cudaSuccess)
+        return fail_cuda(err, "cudaMemsetAsync(noalloc scratch)");
+    return finish(launch_w4a16_decode(ctx, x, pr, false, m, n, k, base,
+                                      reinterpret_cast<uint32_t*>(base + NOALLOC_PARTIAL_BYTES), s),
+                  op, "w4a16_decode_splitk_noalloc");
+}
+
 KAIO_API const char* kaio_b200_last_error(void)
 {
     return g_last_error.c_str();

@@ -1,0 +1,66 @@
+"""The allocation-free decode entry point, through the C ABI.
+
+kaio_b200_matmul_int4_noalloc serves callers that cannot call cudaMalloc when the op runs (a
+runtime whose pool already owns the whole device, a loop that must not synchronise the device).
+It keeps its split-K scratch in a fixed array inside the library, which every call shares and
+which keeps the previous call's contents -- so the check is: two calls in a row, on different
+inputs, each equal to what the regular entry point returns for the same inputs.
+
+This file sorts last on purpose: a run that stops at the first failure has then already run
+every other test.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from kaio_b200 import _lib
+from helpers import dev, host, max_rel
+
+pytestmark = pytest.mark.gpu
+G = 128
+
+
+def call(name, a, packed, scales, c, m, n, k):
+    lib = _lib.load()
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    rc = getattr(lib, name)(C.c_void_p(a.data_ptr()), a.numel(), C.c_void_p(packed.data_ptr()), packed.numel(),
+                            C.c_void_p(scales.data_ptr()), scales.numel(), C.c_void_p(c.data_ptr()), c.numel(),
+                            m, n, k, G, stream)
+    assert rc == 0, lib.kaio_b200_last_error().decode()
+    return lib.kaio_b200_last_variant().decode()
+
+
+def test_two_calls_in_a_row_match_the_regular_entry_point(oracle):
+    torch.cuda.set_device(0)
+    rng = np.random.default_rng(2024)
+    # two different shapes, both split across CTAs (partial tiles go through the shared scratch)
+    for (m, n, k) in [(16, 11008, 4096), (3, 1000, 2048)]:
+        w = rng.integers(-8, 8, k * n, dtype=np.int8)
+        a = dev(rng.standard_normal(m * k).astype(np.float16))
+        s = dev(rng.uniform(0.005, 0.02, (k // G) * n).astype(np.float16))
+        packed = dev(oracle.pack_s4(w, k, n))
+        want = torch.full((m * n,), float("nan"), device="cuda", dtype=torch.float32)
+        call("kaio_b200_matmul_int4", a, packed, s, want, m, n, k)
+        got = torch.full((m * n,), float("nan"), device="cuda", dtype=torch.float32)
+        variant = call("kaio_b200_matmul_int4_noalloc", a, packed, s, got, m, n, k)
+        torch.cuda.synchronize()
+        assert variant == "w4a16_decode_splitk_noalloc"
+        g, w_ = host(got, (m, n)), host(want, (m, n))
+        assert np.all(np.isfinite(g))
+        assert max_rel(g, w_) < 1e-3  # the tolerance of the f32-output parity tests
+
+
+def test_rejects_sizes_beyond_the_fixed_scratch():
+    torch.cuda.set_device(0)
+    lib = _lib.load()
+    m, n, k = 17, 256, 128
+    a = torch.zeros(m * k, device="cuda", dtype=torch.float16)
+    b = torch.zeros((k // 8) * n, device="cuda", dtype=torch.int32)
+    s = torch.zeros(n, device="cuda", dtype=torch.float16)
+    c = torch.zeros(m * n, device="cuda", dtype=torch.float32)
+    rc = lib.kaio_b200_matmul_int4_noalloc(C.c_void_p(a.data_ptr()), a.numel(), C.c_void_p(b.data_ptr()), b.numel(),
+                                           C.c_void_p(s.data_ptr()), s.numel(), C.c_void_p(c.data_ptr()), c.numel(),
+                                           m, n, k, G, None)
+    assert rc == 1 and "M must be at most 16" in lib.kaio_b200_last_error().decode()
