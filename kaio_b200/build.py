@@ -57,7 +57,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
         src, obj, stale = job
         if not stale:
             return src, ""
-        r = subprocess.run([nvcc, *NVCC_FLAGS, "-c", src, "-o", obj], capture_output=True, text=True)
+        extra = os.environ.get("KAIO_B200_NVCC_EXTRA", "").split()
+        r = subprocess.run([nvcc, *NVCC_FLAGS, *extra, "-c", src, "-o", obj], capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"nvcc failed on {src}:\n{r.stdout}\n{r.stderr}")
         return src, r.stderr

@@ -104,9 +104,29 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
     return ok != 0;
 }
 
-// Poll limit: the first polls are back to back, later ones sleep up to 256 ns,
-// so the limit corresponds to roughly one second before a wait gives up.
-constexpr uint32_t WAIT_POLL_LIMIT = 4u << 20;
+// try_wait with a suspend-time hint: the hardware parks the thread until the phase completes
+// or `hint_ns` elapse, so a waiting warp does not compete for issue slots with the warps that
+// do the work (a spinning waiter on the same scheduler slows a single-thread MMA issuer or TMA
+// producer several-fold).
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred P;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n"
+        "selp.u32 %0, 1, 0, P;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
+
+// Each poll may park for up to WAIT_HINT_NS; WAIT_POLL_LIMIT polls bound a wait to about one
+// second (the hint is an upper bound, so the limit also counts polls that return early).
+constexpr uint32_t WAIT_HINT_NS = 20000;
+constexpr uint32_t WAIT_POLL_LIMIT = 1u << 20;
 
 // Returns true when the phase completed; false when this wait (or another
 // thread of the CTA, through *abort_flag) gave up.
@@ -114,14 +134,18 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
                                                   volatile uint32_t* abort_flag, uint32_t* status,
                                                   uint32_t site, uint32_t kernel_id)
 {
+    if (mbar_try_wait(bar, parity))
+        return true;
+    const unsigned long long t_start = clock64();
     for (uint32_t it = 0; it < WAIT_POLL_LIMIT; ++it) {
-        if (mbar_try_wait(bar, parity))
+        if (mbar_try_wait_hint(bar, parity, WAIT_HINT_NS))
             return true;
-        if (it >= 128) {
-            if (*abort_flag)
-                return false;
-            __nanosleep(it >= 8192 ? 256 : 32);
-        }
+        if (*abort_flag)
+            return false;
+        // ~1 s at 2 GHz: polls that return early (hint not honoured) must not shorten or
+        // lengthen the bound by orders of magnitude
+        if (clock64() - t_start > 2000000000ull)
+            break;
     }
     *abort_flag = 1;
     report_status(status, DEV_TIMEOUT, site, kernel_id);

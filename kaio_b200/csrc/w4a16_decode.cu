@@ -7,6 +7,13 @@
 // every mma at these M.  Arithmetic kept from the reference: w = f16(q) * f16(scale) rounded to
 // f16 (mul.f16, :693-699), products accumulated in f32.
 //
+// The product is computed transposed on the 5th-generation tensor cores:
+//     D^T[128 weight columns, 16 activation rows] += W^T[128, k] * A^T[k, 16]
+// with the dequantised weights as the 128-row operand in TENSOR MEMORY (tcgen05.st from the
+// dequantising threads, no shared-memory round trip) and the activations as the K-major
+// shared-memory operand.  (mma.sync runs at 256 FMA/clk/SM on this part and was the bound of
+// an earlier version of this kernel.)
+//
 // Work decomposition (stream-K, deterministic):
 //   unit  = (column tile of 128, K block of 256); units are numbered tile-major and cut into
 //           gridDim.x contiguous ranges, so every SM streams the same number of bytes (+-1 unit).
@@ -15,44 +22,59 @@
 //   the last one to arrive sums the partials in ascending CTA order -- a fixed order, so the
 //   result does not depend on timing -- and writes the output.
 //
-// CTA = 15 warps:
-//   warps 0-7  consumers: (k-half h, column quarter nq).  Per stage each lane takes one 16-byte
-//              chunk (32 nibbles of one column) per 8-column group, dequantises in registers
-//              with the 0x6400 magic-number trick (exact), multiplies by the group scale with
-//              hmul2 (the reference's rounding) and feeds mma.sync.m16n8k16.  The k order inside
-//              an MMA is a fixed permutation of the memory order; the activations are staged in
-//              the same permutation, so no nibble shuffling is needed.
-//   warp 8     TMA producer: one 2-D box [128 columns][128 B = 256 k] per stage, 128-byte swizzle
-//              (conflict-free 16-byte reads), L2 evict-first.
-//   warps 9-14 activation/scale loaders, one per ring slot: A[:, k-block] permuted into the
-//              fragment order and the 2x128 group scales of the stage, through plain loads.
+// CTA = 26 warps:
+//   warp 0       TMA producer: one box [128 columns][128 B = 256 k] of packed weights per stage,
+//                128-byte swizzle, L2 evict-first, 6-stage ring.
+//   warp 1       MMA issuer: 16 x tcgen05.mma kind::f16 (M128 N16 K16) per stage, A from tensor
+//                memory, B (activations) from shared memory; D double-buffered in tensor memory.
+//   warps 2,3,24,25  loaders: the stage's activation slice, written in the UMMA K-major
+//                128-byte-swizzle layout with each group of 8 k permuted to the order the
+//                dequantiser emits, and the stage's 2 x 128 group scales.
+//   warps 4-19   dequantisers: thread = weight column = tensor-memory lane (four warps per
+//                lane quarter, each taking 64 of the stage's 256 k).  16-byte
+//                conflict-free reads of the packed nibbles, 0x6400 magic-number conversion
+//                (exact), hmul2 by the group scale (the reference's rounding), tcgen05.st.
+//   warps 20-23  epilogue: tcgen05.ld of D^T (thread = column, 16 rows), split-K fix-up,
+//                coalesced stores.
 #include "common.cuh"
 #include "kernels.h"
 
 namespace kaio {
 namespace w4dec {
 
-constexpr int BN = 128;          // columns per tile
-constexpr int BKK = 256;         // k per stage (128 bytes of nibbles per column)
+constexpr int BN = 128;   // weight columns per tile = UMMA M
+constexpr int BKK = 256;  // k per stage (128 bytes of nibbles per column)
+constexpr int NROWS = 16; // activation rows = UMMA N
 constexpr int STAGES = 6;
-constexpr int W_BYTES = BN * 128;       // 16 KiB
-constexpr int A_BYTES = 16 * BKK * 2;   // 8 KiB: 16 rows x 256 k f16, fragment-permuted
+constexpr int A_SLOTS = 3;              // tensor-memory ring of dequantised weight blocks
+constexpr int W_BYTES = BN * 128;       // 16 KiB packed weights
+constexpr int X_BYTES = NROWS * BKK * 2;  // 8 KiB activations, 4 sub-tiles [16 rows][128 B]
 constexpr int S_BYTES = 2 * BN * 2;     // 512 B: 2 groups x 128 columns f16
-constexpr int STAGE_BYTES = 25 * 1024;  // W | A | scales, padded to keep W 1024-aligned
-constexpr int RED_BYTES = 4 * 32 * 16 * 4;  // 8 KiB cross-warp reduction buffer
-constexpr int NUM_CONSUMER_WARPS = 8;
-constexpr int NUM_LOADER_WARPS = STAGES;  // loader warp w fills stage w
-constexpr int NUM_THREADS = (NUM_CONSUMER_WARPS + 1 + NUM_LOADER_WARPS) * 32;  // 480
-constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + RED_BYTES + 256;
-constexpr int PARTIAL_FLOATS = 16 * BN;  // one partial tile
+constexpr int STAGE_BYTES = 25 * 1024;  // W | X | scales, padded to keep W and X 1024-aligned
+constexpr int NUM_LOADER_WARPS = 4;
+constexpr int NUM_DEQUANT_WARPS = 16;
+constexpr int NUM_WARPS = 26;
+constexpr int NUM_THREADS = NUM_WARPS * 32;
+constexpr int NUM_BARRIERS = 3 * STAGES + A_SLOTS + 4;
+constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + NUM_BARRIERS * 8 + 64;
+constexpr int PARTIAL_FLOATS = NROWS * BN;  // one partial tile, [column][row]
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t TMEM_D_COL = 0;      // 2 x 16 columns
+constexpr uint32_t TMEM_A_COL = 128;    // A_SLOTS x 128 columns (256 k of f16 pairs)
 
-enum : uint32_t { SITE_EMPTY_P = 1, SITE_EMPTY_L = 2, SITE_FULL = 3 };
+constexpr uint32_t IDESC = make_idesc(/*d=f32*/ 1, /*a=f16*/ 0, /*b=f16*/ 0, /*a K-major*/ 0,
+                                      /*b K-major*/ 0, BN, NROWS);
+
+enum : uint32_t {
+    SITE_W_EMPTY = 1, SITE_W_FULL = 2, SITE_X_EMPTY = 3, SITE_A_EMPTY = 5,
+    SITE_A_FULL = 6, SITE_D_EMPTY = 7, SITE_D_FULL = 8
+};
 
 struct Params {
     const __half* a;       // [M,K]
     const __half* scales;  // [K/128, N]
     void* out;             // f32 or f16 [M,N]
-    float* partials;       // [grid][2][16*128]
+    float* partials;       // [grid][2][128*16]
     uint32_t* counters;    // [tiles]
     uint32_t m, n, k;
     uint32_t num_kb;       // ceil(K / 256)
@@ -63,16 +85,6 @@ struct Params {
 __device__ __forceinline__ void named_barrier(uint32_t id, uint32_t count)
 {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
-}
-
-__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
-                                          uint32_t a3, uint32_t b0, uint32_t b1)
-{
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
-        "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 __device__ __forceinline__ uint32_t h2_as_u32(__half2 h)
@@ -110,12 +122,46 @@ __device__ __forceinline__ void dequant8(uint32_t w, __half2 s2, uint32_t& pa, u
     pd = h2_as_u32(__hmul2(qd, s2));
 }
 
-// 16-byte slot of (row r, 8-k group cj) in a stage's activation tile [16 rows][32 groups].  The
-// XOR terms make both access patterns bank-conflict free: the loader writes 32 consecutive cj of
-// one row, a consumer quarter-warp reads rows {2q, 2q+1} x groups {8t + const}.
-__device__ __forceinline__ uint32_t a_slot(uint32_t r, uint32_t cj)
+__device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_t (&r)[16])
 {
-    return r * 32 + (cj & 0x18u) + (((cj & 7u) ^ (2u * ((cj >> 3) & 3u)) ^ (r & 1u)));
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
+        "r"(r[15])
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_st_wait()
+{
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+
+// D[tmem] (+)= A[tmem] * B[smem], f16 x f16 -> f32.
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                            uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
 }
 
 // First unit of CTA c when `units` units are cut into `grid` contiguous ranges.
@@ -130,23 +176,45 @@ __device__ __forceinline__ uint32_t owner_of(uint32_t u, uint32_t units, uint32_
     return (uint32_t)((((uint64_t)u + 1) * grid - 1) / units);
 }
 
-template <bool OUT_F16, bool M_LE_8>
+#ifdef KAIO_TRACE
+// Development aid (never compiled into the shipped library): per-CTA cycle stamps of the
+// pipeline hand-offs, [cta][unit][8].
+__device__ unsigned long long* g_trace = nullptr;
+#define KAIO_STAMP(it, slot)                                                            \
+    do {                                                                                \
+        if (trace_ptr && (it) < 16)                                                     \
+            trace_ptr[((it)) * 8 + (slot)] = clock64();                                 \
+    } while (0)
+#else
+#define KAIO_STAMP(it, slot) do { } while (0)
+#endif
+
+template <bool OUT_F16>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const Params p)
 {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    float* red = reinterpret_cast<float*>(smem_gen + STAGES * STAGE_BYTES);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + STAGES * STAGE_BYTES + RED_BYTES);
-    const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES + RED_BYTES;
-    auto full_bar = [&](uint32_t s) { return bar_base + 8u * s; };
-    auto empty_bar = [&](uint32_t s) { return bar_base + 8u * (STAGES + s); };
-    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 2 * STAGES);
-    volatile uint32_t* last_flag = abort_flag + 1;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + STAGES * STAGE_BYTES);
+    const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+    auto w_full = [&](uint32_t s) { return bar_base + 8u * s; };
+    auto w_empty = [&](uint32_t s) { return bar_base + 8u * (STAGES + s); };
+    // mma_done[s]: the MMAs of the unit that used ring slot s have retired (one commit per unit
+    // frees both the unit's activation slot and its tensor-memory block)
+    auto mma_done = [&](uint32_t s) { return bar_base + 8u * (2 * STAGES + s); };
+    auto a_full = [&](uint32_t t) { return bar_base + 8u * (3 * STAGES + t); };
+    auto d_full = [&](uint32_t b) { return bar_base + 8u * (3 * STAGES + A_SLOTS + b); };
+    auto d_empty = [&](uint32_t b) { return bar_base + 8u * (3 * STAGES + A_SLOTS + 2 + b); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + NUM_BARRIERS);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+    volatile uint32_t* last_flag = tmem_slot + 2;
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
+#ifdef KAIO_TRACE
+    unsigned long long* const trace_ptr = g_trace ? g_trace + (size_t)blockIdx.x * 128 : nullptr;
+#endif
 
     const uint32_t units = p.num_tiles * p.num_kb;
     const uint32_t u_begin = range_begin(blockIdx.x, units, gridDim.x);
@@ -154,63 +222,148 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const Params p)
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < STAGES; ++s) {
-            mbar_init(full_bar(s), 2);  // TMA producer's expect_tx + the stage's loader warp
-            mbar_init(empty_bar(s), NUM_CONSUMER_WARPS);
+            mbar_init(w_full(s), 2);  // TMA (expect_tx) + the stage's loader warp
+            mbar_init(w_empty(s), NUM_DEQUANT_WARPS);
+            mbar_init(mma_done(s), 1);
+        }
+        for (uint32_t t = 0; t < A_SLOTS; ++t) {
+            mbar_init(a_full(t), NUM_DEQUANT_WARPS);
+        }
+        for (uint32_t b = 0; b < 2; ++b) {
+            mbar_init(d_full(b), 1);
+            mbar_init(d_empty(b), 4);
         }
         *abort_flag = 0;
         *last_flag = 0;
         fence_barrier_init();
         tma_prefetch_desc(&tmap_w);
     }
+    if (warp == 1) {
+        tmem_alloc<TMEM_COLS>(smem_u32(const_cast<uint32_t*>(tmem_slot)));
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
     __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0)
+        KAIO_STAMP(15, 7);
 
-    if (warp == NUM_CONSUMER_WARPS) {
-        // ------------------------------------------------------------ TMA producer
-        if (lane == 0) {
-            const uint64_t policy = l2_policy_evict_first();
-            uint32_t it = 0;
-            for (uint32_t u = u_begin; u < u_end; ++u, ++it) {
-                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-                if (!mbar_wait_bounded(empty_bar(s), ph ^ 1u, abort_flag, p.status, SITE_EMPTY_P,
-                                       KERNEL_W4A16_DECODE))
-                    break;
-                const uint32_t tile = u / p.num_kb, kb = u % p.num_kb;
-                mbar_expect_tx(full_bar(s), W_BYTES);
-                tma_load_2d_hint(smem_base + s * STAGE_BYTES, &tmap_w, full_bar(s),
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer (weights)
+        // The whole warp runs the loop so that its control flow and address arithmetic stay
+        // warp-uniform (uniform registers feed the TMA instruction directly); one elected lane
+        // issues.
+        const uint64_t policy = l2_policy_evict_first();
+        uint32_t tile = u_begin / p.num_kb, kb = u_begin % p.num_kb;
+        uint32_t s = 0, ph = 0;
+        for (uint32_t u = u_begin; u < u_end; ++u) {
+            if (!mbar_wait_bounded(w_empty(s), ph ^ 1u, abort_flag, p.status, SITE_W_EMPTY,
+                                   KERNEL_W4A16_DECODE))
+                break;
+            if (elect_one()) {
+                mbar_expect_tx(w_full(s), W_BYTES);
+                tma_load_2d_hint(smem_base + s * STAGE_BYTES, &tmap_w, w_full(s),
                                  (int32_t)(kb * (BKK / 8)), (int32_t)(tile * BN), policy);
+                KAIO_STAMP(u - u_begin, 0);
             }
-            if (*abort_flag)
-                for (uint32_t spin = 0; spin < 2000; ++spin)
-                    __nanosleep(100);
+            __syncwarp();
+            if (++kb == p.num_kb) {
+                kb = 0;
+                ++tile;
+            }
+            if (++s == STAGES) {
+                s = 0;
+                ph ^= 1u;
+            }
         }
-    } else if (warp > NUM_CONSUMER_WARPS) {
+        if (*abort_flag)
+            for (uint32_t spin = 0; spin < 2000; ++spin)
+                __nanosleep(100);
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        // Converged warp, one elected lane issues: descriptors and addresses are then computed
+        // in the uniform datapath instead of being moved there per instruction, which is what
+        // bounds the issue rate of these short (N = 16) MMAs.
+        uint32_t seg = 0, s = 0, ph = 0, t = 0, aph = 0;
+        uint32_t kb = u_begin % p.num_kb;
+        bool seg_first = true;
+        for (uint32_t u = u_begin; u < u_end; ++u) {
+            const bool seg_last = (kb + 1 == p.num_kb) || (u + 1 == u_end);
+            const uint32_t buf = seg & 1u;
+            if (lane == 0)
+                KAIO_STAMP(u - u_begin, 7);
+            if (seg_first &&
+                !mbar_wait_bounded(d_empty(buf), ((seg >> 1) & 1u) ^ 1u, abort_flag, p.status,
+                                   SITE_D_EMPTY, KERNEL_W4A16_DECODE))
+                break;
+            // a_full implies the stage's activations are in place: the dequantisers waited for
+            // the loader's arrival on w_full before they produced this block
+            if (!mbar_wait_bounded(a_full(t), aph, abort_flag, p.status, SITE_A_FULL,
+                                   KERNEL_W4A16_DECODE))
+                break;
+            tc_fence_after_sync();
+            if (lane == 0)
+                KAIO_STAMP(u - u_begin, 5);
+            const uint32_t d_tmem = tmem_base + TMEM_D_COL + buf * NROWS;
+            const uint32_t a_tmem = tmem_base + TMEM_A_COL + t * (BKK / 2);
+            const uint64_t b_desc0 =
+                make_smem_desc_sw128(smem_base + s * STAGE_BYTES + W_BYTES, 16, 1024);
+            if (elect_one()) {
+                umma_f16_ts(d_tmem, a_tmem, b_desc0, IDESC, seg_first ? 0u : 1u);
+#pragma unroll
+                for (uint32_t kk = 1; kk < BKK / 16; ++kk) {
+                    // activations: sub-tile kk/4 (64 k, 2 KiB apart), 32 bytes per MMA inside
+                    // the row; the descriptor's address field counts 16-byte units
+                    umma_f16_ts(d_tmem, a_tmem + kk * 8,
+                                b_desc0 + (uint64_t)((kk >> 2) * 128 + (kk & 3u) * 2), IDESC, 1u);
+                }
+                umma_commit(mma_done(s));
+                if (seg_last)
+                    umma_commit(d_full(buf));
+            }
+            __syncwarp();
+            if (lane == 0)
+                KAIO_STAMP(u - u_begin, 6);
+            seg_first = false;
+            if (seg_last) {
+                ++seg;
+                seg_first = true;
+            }
+            if (++kb == p.num_kb)
+                kb = 0;
+            if (++s == STAGES) {
+                s = 0;
+                ph ^= 1u;
+            }
+            if (++t == A_SLOTS) {
+                t = 0;
+                aph ^= 1u;
+            }
+        }
+        (void)ph;
+    } else if (warp == 2 || warp == 3 || warp == 24 || warp == 25) {
         // ------------------------------------------------------------ activation / scale loaders
-        // Loader warp lw owns ring slot lw, so up to STAGES activation slices are in flight at
-        // once and the L2 latency of one slice is hidden behind the others.
-        const uint32_t lw = warp - (NUM_CONSUMER_WARPS + 1);
+        const uint32_t lw = warp < 4 ? warp - 2 : warp - 22;
         const uint32_t groups = p.k >> 7;
         for (uint32_t it = lw; u_begin + it < u_end; it += NUM_LOADER_WARPS) {
             const uint32_t u = u_begin + it;
             const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-            if (!mbar_wait_bounded(empty_bar(s), ph ^ 1u, abort_flag, p.status, SITE_EMPTY_L,
+            // the slot is free when the MMAs that read the activations and the dequantisers
+            // that read the scales have both finished with it
+            if (!mbar_wait_bounded(mma_done(s), ph ^ 1u, abort_flag, p.status, SITE_X_EMPTY,
+                                   KERNEL_W4A16_DECODE) ||
+                !mbar_wait_bounded(w_empty(s), ph ^ 1u, abort_flag, p.status, SITE_W_EMPTY,
                                    KERNEL_W4A16_DECODE))
                 break;
             const uint32_t tile = u / p.num_kb, kb = u % p.num_kb;
             uint8_t* stage = smem_gen + s * STAGE_BYTES;
-            uint4* a_s = reinterpret_cast<uint4*>(stage + W_BYTES);
-            __half* s_s = reinterpret_cast<__half*>(stage + W_BYTES + A_BYTES);
+            uint8_t* x_s = stage + W_BYTES;
+            __half* s_s = reinterpret_cast<__half*>(stage + W_BYTES + X_BYTES);
             const uint32_t k0 = kb * BKK;
-            constexpr uint32_t ROWS = M_LE_8 ? 8 : 16;
-            // lane = 8-k group cj of the stage; one row per step: A[r][k0 + 8 cj .. +8)
+            // lane = 8-k group cj of the stage (32 groups); one activation row per step
             const uint32_t cj = lane;
             const uint32_t kk = k0 + cj * 8;
-            uint4 v[ROWS];
-#pragma unroll
-            for (uint32_t r = 0; r < ROWS; ++r) {
-                v[r] = make_uint4(0, 0, 0, 0);
-                if (r < p.m && kk < p.k)
-                    v[r] = __ldg(reinterpret_cast<const uint4*>(p.a + (size_t)r * p.k + kk));
-            }
             __half sv[8];
 #pragma unroll
             for (uint32_t x = 0; x < 8; ++x) {
@@ -221,202 +374,208 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const Params p)
                     sv[x] = __ldg(p.scales + (size_t)grp * p.n + col);
             }
 #pragma unroll
-            for (uint32_t r = 0; r < ROWS; ++r) {
-                uint4 o;  // memory order [0..7] -> fragment order [0,4,1,5,2,6,3,7]
-                o.x = __byte_perm(v[r].x, v[r].z, 0x5410);  // (h0, h4)
-                o.y = __byte_perm(v[r].x, v[r].z, 0x7632);  // (h1, h5)
-                o.z = __byte_perm(v[r].y, v[r].w, 0x5410);  // (h2, h6)
-                o.w = __byte_perm(v[r].y, v[r].w, 0x7632);  // (h3, h7)
-                a_s[a_slot(r, cj)] = o;
+            for (uint32_t r0 = 0; r0 < NROWS; r0 += 8) {
+                if (r0 >= p.m)
+                    break;  // rows >= M feed output rows that are never stored
+                uint4 v[8];
+#pragma unroll
+                for (uint32_t r = 0; r < 8; ++r) {
+                    v[r] = make_uint4(0, 0, 0, 0);
+                    if (r0 + r < p.m && kk < p.k)
+                        v[r] = __ldg(
+                            reinterpret_cast<const uint4*>(p.a + (size_t)(r0 + r) * p.k + kk));
+                }
+#pragma unroll
+                for (uint32_t r = 0; r < 8; ++r) {
+                    if (r0 + r < p.m) {
+                        uint4 o;  // memory order [0..7] -> dequantiser order [0,4,1,5,2,6,3,7]
+                        o.x = __byte_perm(v[r].x, v[r].z, 0x5410);  // (h0, h4)
+                        o.y = __byte_perm(v[r].x, v[r].z, 0x7632);  // (h1, h5)
+                        o.z = __byte_perm(v[r].y, v[r].w, 0x5410);  // (h2, h6)
+                        o.w = __byte_perm(v[r].y, v[r].w, 0x7632);  // (h3, h7)
+                        // K-major 128-byte-swizzle tile: sub-tile cj/8, row, 16-byte chunk cj%8
+                        *reinterpret_cast<uint4*>(x_s + (cj >> 3) * 2048 +
+                                                  sw128_offset(r0 + r, cj & 7u)) = o;
+                    }
+                }
             }
 #pragma unroll
             for (uint32_t x = 0; x < 8; ++x)
                 s_s[lane + 32 * x] = sv[x];
+            fence_proxy_async_smem();  // the activations are read by the tensor core (async proxy)
             __syncwarp();
-            if (lane == 0)
-                mbar_arrive(full_bar(s));  // release: the stores above are visible to waiters
+            if (lane == 0) {
+                mbar_arrive(w_full(s));
+                KAIO_STAMP(it, 1);
+            }
         }
-    } else {
-        // ------------------------------------------------------------ consumers
-        const uint32_t h = warp >> 2;   // which 32-k chunks of the stage: chunk = 2t + h
-        const uint32_t nq = warp & 3u;  // column quarter of the tile
-        const uint32_t g = lane >> 2, t = lane & 3u;
-        const uint32_t chunk = 2 * t + h;
-        float acc[4][4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-                acc[i][j] = 0.0f;
-
+    } else if (warp >= 4 && warp < 20) {
+        // ------------------------------------------------------------ dequantisers
+        const uint32_t q = warp & 3u;          // tensor-memory lane quarter of this warp
+        const uint32_t wg = (warp - 4) >> 2;   // which 64-k quarter of the stage (2 chunks of 32 k)
+        const uint32_t row = q * 32 + lane;    // weight column inside the tile = TMEM lane
         uint32_t it = 0;
-        uint32_t seg_kb_lo = u_begin % p.num_kb;  // first K block of the current segment
-        bool ok = true;
         for (uint32_t u = u_begin; u < u_end; ++u, ++it) {
             const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-            const uint32_t tile = u / p.num_kb, kb = u % p.num_kb;
-            if (!mbar_wait_bounded(full_bar(s), ph, abort_flag, p.status, SITE_FULL,
-                                   KERNEL_W4A16_DECODE)) {
-                ok = false;
+            const uint32_t t = it % A_SLOTS;
+            // w_full completes when both the TMA box and the loader's activations/scales landed
+            if (!mbar_wait_bounded(w_full(s), ph, abort_flag, p.status, SITE_W_FULL,
+                                   KERNEL_W4A16_DECODE))
                 break;
-            }
+            if (warp == 4 && lane == 0)
+                KAIO_STAMP(it, 2);
             const uint8_t* stage = smem_gen + s * STAGE_BYTES;
-            const uint8_t* a_s = stage + W_BYTES;
-            const __half* s_s = reinterpret_cast<const __half*>(stage + W_BYTES + A_BYTES);
-
-            uint4 wv[4];
-            __half2 sc[4];
+            const __half* s_s = reinterpret_cast<const __half*>(stage + W_BYTES + X_BYTES);
+            uint4 wv[2];
 #pragma unroll
-            for (int ng = 0; ng < 4; ++ng) {
-                const uint32_t col = nq * 32 + ng * 8 + g;  // col & 7 == g
-                wv[ng] = *reinterpret_cast<const uint4*>(stage + col * 128 + ((chunk ^ g) << 4));
-                sc[ng] = __half2half2(s_s[(t >> 1) * BN + col]);
-            }
-            uint4 alo[4], ahi[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const uint32_t slot = a_slot(g, chunk * 4 + j);
-                alo[j] = *reinterpret_cast<const uint4*>(a_s + slot * 16);
-                if (!M_LE_8)
-                    ahi[j] = *reinterpret_cast<const uint4*>(a_s + (slot + 8 * 32) * 16);
-                else
-                    ahi[j] = make_uint4(0, 0, 0, 0);
-            }
+            for (uint32_t c = 0; c < 2; ++c)
+                wv[c] = *reinterpret_cast<const uint4*>(stage + sw128_offset(row, wg * 2 + c));
+            const __half2 sc = __half2half2(s_s[(wg >> 1) * BN + row]);
             __syncwarp();
             if (lane == 0)
-                mbar_arrive(empty_bar(s));  // all shared-memory reads of this stage are done
-
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-#pragma unroll
-                for (int ng = 0; ng < 4; ++ng) {
-                    const uint32_t w = j == 0 ? wv[ng].x : j == 1 ? wv[ng].y : j == 2 ? wv[ng].z
-                                                                                      : wv[ng].w;
-                    uint32_t pa, pb, pc, pd;
-                    dequant8(w, sc[ng], pa, pb, pc, pd);
-                    mma_16816(acc[ng], alo[j].x, ahi[j].x, alo[j].y, ahi[j].y, pa, pb);
-                    mma_16816(acc[ng], alo[j].z, ahi[j].z, alo[j].w, ahi[j].w, pc, pd);
-                }
+                mbar_arrive(w_empty(s));  // packed weights and scales of this stage are in registers
+            // the tensor-memory block is free once the MMAs of unit it - A_SLOTS have retired
+            if (it >= A_SLOTS) {
+                const uint32_t pit = it - A_SLOTS;
+                if (!mbar_wait_bounded(mma_done(pit % STAGES), (pit / STAGES) & 1u, abort_flag,
+                                       p.status, SITE_A_EMPTY, KERNEL_W4A16_DECODE))
+                    break;
             }
-
-            // ---------------------------------------------------------- end of a segment?
-            if (kb + 1 == p.num_kb || u + 1 == u_end) {
-                float* myred = red + (nq * 32 + lane) * 16;
-                if (h == 1) {
+            tc_fence_after_sync();
+            if (warp == 4 && lane == 0)
+                KAIO_STAMP(it, 3);
+            const uint32_t a_tmem =
+                tmem_base + ((q * 32u) << 16) + TMEM_A_COL + t * (BKK / 2) + wg * 32;
 #pragma unroll
-                    for (int ng = 0; ng < 4; ++ng)
-                        *reinterpret_cast<float4*>(myred + ng * 4) =
-                            make_float4(acc[ng][0], acc[ng][1], acc[ng][2], acc[ng][3]);
-                }
-                named_barrier(1, NUM_CONSUMER_WARPS * 32);
-                if (h == 0) {
-#pragma unroll
-                    for (int ng = 0; ng < 4; ++ng) {
-                        const float4 r4 = *reinterpret_cast<const float4*>(myred + ng * 4);
-                        acc[ng][0] += r4.x;
-                        acc[ng][1] += r4.y;
-                        acc[ng][2] += r4.z;
-                        acc[ng][3] += r4.w;
-                    }
-                }
-                named_barrier(1, NUM_CONSUMER_WARPS * 32);
-
-                if (h == 0) {
-                    const bool complete = (seg_kb_lo == 0) && (kb + 1 == p.num_kb);
-                    bool write_out = complete;
-                    if (!complete) {
-                        // slot 0: the segment that opens this CTA's range; slot 1: the one that closes it
-                        const uint32_t first_tile = u_begin / p.num_kb;
-                        const uint32_t slot = (tile == first_tile) ? 0u : 1u;
-                        float* mine = p.partials +
-                                      ((size_t)(blockIdx.x * 2 + slot) * PARTIAL_FLOATS) +
-                                      (nq * 32 + lane) * 16;
-#pragma unroll
-                        for (int ng = 0; ng < 4; ++ng)
-                            __stcg(reinterpret_cast<float4*>(mine + ng * 4),
-                                   make_float4(acc[ng][0], acc[ng][1], acc[ng][2], acc[ng][3]));
-                        __threadfence();
-                        named_barrier(2, 128);
-                        const uint32_t c_first = owner_of(tile * p.num_kb, units, gridDim.x);
-                        const uint32_t c_last =
-                            owner_of(tile * p.num_kb + p.num_kb - 1, units, gridDim.x);
-                        if (threadIdx.x == 0) {
-                            const uint32_t prev = atomicAdd(p.counters + tile, 1u);
-                            const bool last = (prev == c_last - c_first);
-                            if (last)
-                                p.counters[tile] = 0;  // self-resetting for the next launch
-                            *last_flag = last ? 1u : 0u;
-                        }
-                        named_barrier(2, 128);
-                        write_out = (*last_flag != 0);
-                        if (write_out) {
-                            __threadfence();
-#pragma unroll
-                            for (int ng = 0; ng < 4; ++ng)
-#pragma unroll
-                                for (int e = 0; e < 4; ++e)
-                                    acc[ng][e] = 0.0f;
-                            for (uint32_t c = c_first; c <= c_last; ++c) {
-                                const uint32_t c_tile0 = range_begin(c, units, gridDim.x) / p.num_kb;
-                                const uint32_t cslot = (tile == c_tile0) ? 0u : 1u;
-                                const float* src = p.partials +
-                                                   ((size_t)(c * 2 + cslot) * PARTIAL_FLOATS) +
-                                                   (nq * 32 + lane) * 16;
-#pragma unroll
-                                for (int ng = 0; ng < 4; ++ng) {
-                                    const float4 v =
-                                        __ldcg(reinterpret_cast<const float4*>(src + ng * 4));
-                                    acc[ng][0] += v.x;
-                                    acc[ng][1] += v.y;
-                                    acc[ng][2] += v.z;
-                                    acc[ng][3] += v.w;
-                                }
-                            }
-                        }
-                        named_barrier(2, 128);  // last_flag may be rewritten after this point
-                    }
-                    if (write_out) {
-                        // C fragment: (row g, cols 2t,2t+1) and (row g+8, cols 2t,2t+1)
-#pragma unroll
-                        for (int ng = 0; ng < 4; ++ng) {
-                            const uint32_t col = tile * BN + nq * 32 + ng * 8 + 2 * t;
-#pragma unroll
-                            for (int half = 0; half < 2; ++half) {
-                                const uint32_t row = g + 8 * half;
-                                if (row >= p.m)
-                                    continue;
-                                const float v0 = acc[ng][2 * half], v1 = acc[ng][2 * half + 1];
-                                const size_t idx = (size_t)row * p.n + col;
-                                if (OUT_F16) {
-                                    __half* o = reinterpret_cast<__half*>(p.out);
-                                    if (col < p.n)
-                                        o[idx] = __float2half_rn(v0);
-                                    if (col + 1 < p.n)
-                                        o[idx + 1] = __float2half_rn(v1);
-                                } else {
-                                    float* o = reinterpret_cast<float*>(p.out);
-                                    if (col < p.n)
-                                        o[idx] = v0;
-                                    if (col + 1 < p.n)
-                                        o[idx + 1] = v1;
-                                }
-                            }
-                        }
-                    }
-                }
-#pragma unroll
-                for (int ng = 0; ng < 4; ++ng)
-#pragma unroll
-                    for (int e = 0; e < 4; ++e)
-                        acc[ng][e] = 0.0f;
-                seg_kb_lo = 0;  // the next segment starts a new tile
+            for (uint32_t c = 0; c < 2; ++c) {
+                uint32_t r[16];
+                dequant8(wv[c].x, sc, r[0], r[1], r[2], r[3]);
+                dequant8(wv[c].y, sc, r[4], r[5], r[6], r[7]);
+                dequant8(wv[c].z, sc, r[8], r[9], r[10], r[11]);
+                dequant8(wv[c].w, sc, r[12], r[13], r[14], r[15]);
+                tmem_st_32x32b_x16(a_tmem + c * 16, r);
             }
+            tmem_st_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(a_full(t));
+#ifdef KAIO_TRACE
+            if (lane == 0 && trace_ptr && it < 16)
+                atomicMax(&trace_ptr[it * 8 + 4], (unsigned long long)clock64());
+#endif
         }
-        (void)ok;
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 20..23)
+        const uint32_t q = warp & 3u;
+        const uint32_t tid = q * 32 + lane;  // weight column inside the tile = TMEM lane
+        uint32_t seg = 0;
+        uint32_t seg_kb_lo = u_begin % p.num_kb;
+        for (uint32_t u = u_begin; u < u_end; ++u) {
+            const uint32_t tile = u / p.num_kb, kb = u % p.num_kb;
+            if (!((kb + 1 == p.num_kb) || (u + 1 == u_end)))
+                continue;
+            const uint32_t buf = seg & 1u;
+            if (!mbar_wait_bounded(d_full(buf), (seg >> 1) & 1u, abort_flag, p.status, SITE_D_FULL,
+                                   KERNEL_W4A16_DECODE))
+                break;
+            tc_fence_after_sync();
+            uint32_t raw[16];
+            tmem_ld_32x32b_x16(tmem_base + ((q * 32u) << 16) + TMEM_D_COL + buf * NROWS, raw);
+            tmem_ld_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(d_empty(buf));
+            float acc[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                acc[i] = __uint_as_float(raw[i]);
+
+            const bool complete = (seg_kb_lo == 0) && (kb + 1 == p.num_kb);
+            bool write_out = complete;
+            if (!complete) {
+                // slot 0: the segment that opens this CTA's range; slot 1: the one that closes it
+                const uint32_t first_tile = u_begin / p.num_kb;
+                const uint32_t slot = (tile == first_tile) ? 0u : 1u;
+                float* mine =
+                    p.partials + ((size_t)(blockIdx.x * 2 + slot) * PARTIAL_FLOATS) + tid * 16;
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    __stcg(reinterpret_cast<float4*>(mine + i * 4),
+                           make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]));
+                __threadfence();
+                named_barrier(2, 128);
+                const uint32_t c_first = owner_of(tile * p.num_kb, units, gridDim.x);
+                const uint32_t c_last = owner_of(tile * p.num_kb + p.num_kb - 1, units, gridDim.x);
+                if (tid == 0) {
+                    const uint32_t prev = atomicAdd(p.counters + tile, 1u);
+                    const bool last = (prev == c_last - c_first);
+                    if (last)
+                        p.counters[tile] = 0;  // self-resetting for the next launch
+                    *last_flag = last ? 1u : 0u;
+                }
+                named_barrier(2, 128);
+                write_out = (*last_flag != 0);
+                if (write_out) {
+                    __threadfence();
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        acc[i] = 0.0f;
+                    for (uint32_t c = c_first; c <= c_last; ++c) {
+                        const uint32_t c_tile0 = range_begin(c, units, gridDim.x) / p.num_kb;
+                        const uint32_t cslot = (tile == c_tile0) ? 0u : 1u;
+                        const float* src =
+                            p.partials + ((size_t)(c * 2 + cslot) * PARTIAL_FLOATS) + tid * 16;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float4 v4 = __ldcg(reinterpret_cast<const float4*>(src + i * 4));
+                            acc[4 * i] += v4.x;
+                            acc[4 * i + 1] += v4.y;
+                            acc[4 * i + 2] += v4.z;
+                            acc[4 * i + 3] += v4.w;
+                        }
+                    }
+                }
+                named_barrier(2, 128);  // last_flag may be rewritten after this point
+            }
+            if (write_out) {
+                const uint32_t col = tile * BN + tid;
+                if (col < p.n) {
+#pragma unroll
+                    for (uint32_t r = 0; r < NROWS; ++r) {
+                        if (r < p.m) {
+                            const size_t idx = (size_t)r * p.n + col;
+                            if (OUT_F16)
+                                reinterpret_cast<__half*>(p.out)[idx] = __float2half_rn(acc[r]);
+                            else
+                                reinterpret_cast<float*>(p.out)[idx] = acc[r];
+                        }
+                    }
+                }
+            }
+            ++seg;
+            seg_kb_lo = 0;  // the next segment starts a new tile
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc<TMEM_COLS>(tmem_base);
     }
 }
 
 }  // namespace w4dec
+
+#ifdef KAIO_TRACE
+extern "C" __attribute__((visibility("default"))) int kaio_b200_debug_set_trace(void* ptr)
+{
+    return (int)cudaMemcpyToSymbol(w4dec::g_trace, &ptr, sizeof(ptr));
+}
+#endif
 
 bool w4a16_decode_ok(const void* x, const DqProblem* probs, int num_probs, uint32_t m, uint32_t n,
                      uint32_t k)
@@ -469,32 +628,23 @@ cudaError_t launch_w4a16_decode(const DeviceCtx& ctx, const __half* x, const DqP
     p.status = ctx.status;
     const uint32_t grid = decode_grid(ctx, n, k);
 
-    static bool attr_set[4][64] = {};
-#define KAIO_LAUNCH_W4DEC(F16, M8)                                                                \
+    static bool attr_set[2][64] = {};
+#define KAIO_LAUNCH_W4DEC(F16)                                                                    \
     do {                                                                                          \
-        const int slot = (F16 ? 2 : 0) + (M8 ? 1 : 0);                                            \
-        if (!attr_set[slot][ctx.device]) {                                                        \
-            err = cudaFuncSetAttribute(w4a16_decode_kernel<F16, M8>,                              \
+        if (!attr_set[F16 ? 1 : 0][ctx.device]) {                                                 \
+            err = cudaFuncSetAttribute(w4a16_decode_kernel<F16>,                                  \
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);  \
             if (err != cudaSuccess)                                                               \
                 return err;                                                                       \
-            attr_set[slot][ctx.device] = true;                                                    \
+            attr_set[F16 ? 1 : 0][ctx.device] = true;                                             \
         }                                                                                         \
-        w4a16_decode_kernel<F16, M8><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmap_w, p);       \
+        w4a16_decode_kernel<F16><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmap_w, p);           \
     } while (0)
 
-    const bool m8 = m <= 8;
-    if (out_f16) {
-        if (m8)
-            KAIO_LAUNCH_W4DEC(true, true);
-        else
-            KAIO_LAUNCH_W4DEC(true, false);
-    } else {
-        if (m8)
-            KAIO_LAUNCH_W4DEC(false, true);
-        else
-            KAIO_LAUNCH_W4DEC(false, false);
-    }
+    if (out_f16)
+        KAIO_LAUNCH_W4DEC(true);
+    else
+        KAIO_LAUNCH_W4DEC(false);
 #undef KAIO_LAUNCH_W4DEC
     return cudaGetLastError();
 }
