@@ -150,6 +150,24 @@ static int32_t ensure_workspace(DeviceCtx* c, size_t bytes, size_t counters)
     return KAIO_B200_OK;
 }
 
+// The dequantised-weight workspace is written and read by every dequantising GEMM call on the
+// device, in stream order.  Growth frees the old block with cudaFree, which synchronises.
+static int32_t ensure_dq_workspace(DeviceCtx* c, size_t bytes)
+{
+    std::lock_guard<std::mutex> lock(g_ctx_mutex);
+    if (bytes > c->dq_workspace_bytes) {
+        if (c->dq_workspace)
+            cudaFree(c->dq_workspace);
+        c->dq_workspace = nullptr;
+        c->dq_workspace_bytes = 0;
+        cudaError_t err = cudaMalloc(&c->dq_workspace, bytes);
+        if (err != cudaSuccess)
+            return fail_cuda(err, "cudaMalloc(dequantised weights)");
+        c->dq_workspace_bytes = bytes;
+    }
+    return KAIO_B200_OK;
+}
+
 static int32_t finish(cudaError_t err, const char* op, const char* variant)
 {
     g_last_variant = variant;
@@ -395,9 +413,13 @@ static int32_t run_int4(const kaio_f16* a, size_t a_len, const uint32_t* b, size
                                           ctx->tile_counters, s),
                       "matmul_int4", "w4a16_decode_splitk");
     }
-    if (dq_gemm_fast_path_ok(WFMT_S4_PACKED, x, &pr, 1, out_f16, m, n, k))
-        return finish(launch_dq_gemm(*ctx, WFMT_S4_PACKED, x, &pr, 1, out_f16, false, m, n, k, s),
+    if (dq_gemm_fast_path_ok(WFMT_S4_PACKED, x, &pr, 1, out_f16, m, n, k)) {
+        if ((rc = ensure_dq_workspace(ctx, dq_gemm_workspace_bytes(1, n, k))))
+            return rc;
+        return finish(launch_dq_gemm(*ctx, WFMT_S4_PACKED, x, &pr, 1, out_f16, false, m, n, k,
+                                     ctx->dq_workspace, s),
                       "matmul_int4", "w4a16_tcgen05");
+    }
     return finish(launch_dq_generic(WFMT_S4_PACKED, x, &pr, 1, out_f16, false, m, n, k, s),
                   "matmul_int4", "w4a16_generic");
 }
@@ -415,9 +437,13 @@ static int32_t run_qkv(int wfmt, const char* op, const __half* x, DqProblem prob
     if ((rc = get_ctx(&ctx)))
         return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (dq_gemm_fast_path_ok(wfmt, x, probs, 3, true, m, n, k))
-        return finish(launch_dq_gemm(*ctx, wfmt, x, probs, 3, true, post_scale, m, n, k, s), op,
-                      wfmt == WFMT_S8_ROWMAJOR ? "qkv_w8a16_tcgen05" : "qkv_w4a16_tcgen05");
+    if (dq_gemm_fast_path_ok(wfmt, x, probs, 3, true, m, n, k)) {
+        if ((rc = ensure_dq_workspace(ctx, dq_gemm_workspace_bytes(3, n, k))))
+            return rc;
+        return finish(launch_dq_gemm(*ctx, wfmt, x, probs, 3, true, post_scale, m, n, k,
+                                     ctx->dq_workspace, s),
+                      op, wfmt == WFMT_S8_ROWMAJOR ? "qkv_w8a16_tcgen05" : "qkv_w4a16_tcgen05");
+    }
     return finish(launch_dq_generic(wfmt, x, probs, 3, true, post_scale, m, n, k, s), op,
                   wfmt == WFMT_S8_ROWMAJOR ? "qkv_w8a16_generic" : "qkv_w4a16_generic");
 }
@@ -834,6 +860,8 @@ KAIO_API void kaio_b200_shutdown(void)
             cudaFree(c.workspace);
         if (c.tile_counters)
             cudaFree(c.tile_counters);
+        if (c.dq_workspace)
+            cudaFree(c.dq_workspace);
         c = DeviceCtx();
     }
     if (cur >= 0)

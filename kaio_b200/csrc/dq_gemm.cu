@@ -1,5 +1,452 @@
+// Dequantising GEMMs for M > 16 on the tensor cores: W4A16 (`matmul_int4`, `qkv_project_int4`)
+// and W8A16 (`qkv_project_int8`).
+//
+// Replaces KAIO's kernels `matmul_int4` (kaio-ops/src/matmul_int4_kernel.rs:1492-2070),
+// `qkv_project_int4` (qkv_project_int4_kernel.rs:714-1314) and `qkv_project_int8`
+// (qkv_project_int8_kernel.rs:1093-1861), which dequantise per lane in front of mma.sync.
+//
+// Two launches per call:
+//   1. dequant_*_kernel: the weights, exactly as the reference dequantises them
+//      (s4: f16(q) * f16(group scale) rounded to f16, matmul_int4_kernel.rs:655-713;
+//       s8: cvt.rn.f16.s8, qkv_project_int8_kernel.rs:631-638), written once as f16 [K,N]
+//      row-major into a library-owned workspace.  HBM-bound, 2.5 bytes (s4) / 3 bytes (s8) of
+//      traffic per weight; for the prefill shapes this is a few percent of the GEMM.
+//   2. f16_gemm_kernel: one persistent launch over all (up to three) weight matrices -- the
+//      tile scheduler walks (projection, m-tile, n-tile), so the fused QKV ops stay one GEMM
+//      launch with three outputs.  Per CTA: warp 0 TMA producer (x tile [128 rows][64 k] and
+//      weight tile [64 k][256 n], 128-byte swizzle, 4-stage ring), warp 1 issues
+//      tcgen05.mma kind::f16 M128 N256 K16 (x K-major, weights MN-major straight from the
+//      row-major [K,N] layout), f32 accumulators double-buffered in tensor memory, warps 2-5
+//      epilogue (post-scale, f16/f32 narrow, predicated stores).
+//
+// Shapes: N % 8 == 0 and 16-byte aligned bases (TMA).  Everything else takes the generic kernel.
+#include "common.cuh"
 #include "kernels.h"
+
 namespace kaio {
-bool dq_gemm_fast_path_ok(int, const void*, const DqProblem*, int, bool, uint32_t, uint32_t, uint32_t) { return false; }
-cudaError_t launch_dq_gemm(const DeviceCtx&, int, const __half*, const DqProblem*, int, bool, bool, uint32_t, uint32_t, uint32_t, cudaStream_t) { return cudaErrorNotSupported; }
+namespace f16g {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;     // f16 elements per stage along K (128 bytes of x per row)
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * 128;           // 16 KiB: [128 rows][64 k f16]
+constexpr int B_CHUNK_BYTES = BK * 128;     // 8 KiB: [64 k][64 n f16]
+constexpr int B_CHUNKS = BN * 2 / 128;      // 4 chunks of 64 columns
+constexpr int B_BYTES = B_CHUNKS * B_CHUNK_BYTES;  // 32 KiB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;     // 48 KiB
+constexpr int TMEM_COLS = 512;
+constexpr int NUM_THREADS = 192;
+constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 256;
+constexpr int MAX_PROBS = 3;
+
+constexpr uint32_t IDESC = make_idesc(/*d=f32*/ 1, /*a=f16*/ 0, /*b=f16*/ 0, /*a K-major*/ 0,
+                                      /*b MN-major*/ 1, BM, BN);
+
+enum : uint32_t { SITE_EMPTY = 1, SITE_FULL = 2, SITE_TMEM_EMPTY = 3, SITE_TMEM_FULL = 4 };
+
+struct Problem {
+    void* out;               // f32 or f16 [M,N]
+    const float* col_scale;  // per-column post-scale or nullptr
+    float scale;             // scalar post-scale
+};
+
+struct Params {
+    Problem probs[MAX_PROBS];
+    uint32_t num_probs;
+    uint32_t m, n, k;
+    int out_f16;
+    int post_scale;
+    uint32_t* status;
+};
+
+struct TensorMaps {
+    CUtensorMap x;
+    CUtensorMap w[MAX_PROBS];
+};
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+f16_gemm_kernel(const __grid_constant__ TensorMaps maps, const Params p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + STAGES * STAGE_BYTES);
+    const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+    auto full_bar = [&](uint32_t s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](uint32_t s) { return bar_base + 8u * (STAGES + s); };
+    auto tmem_full_bar = [&](uint32_t b) { return bar_base + 8u * (2 * STAGES + b); };
+    auto tmem_empty_bar = [&](uint32_t b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * STAGES + 4);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+
+    const uint32_t tiles_m = (p.m + BM - 1) / BM;
+    const uint32_t tiles_n = (p.n + BN - 1) / BN;
+    const uint32_t tiles_per_prob = tiles_m * tiles_n;
+    const uint32_t num_tiles = tiles_per_prob * p.num_probs;
+    const uint32_t num_kb = (p.k + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (uint32_t b = 0; b < 2; ++b) {
+            mbar_init(tmem_full_bar(b), 1);
+            mbar_init(tmem_empty_bar(b), 4);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        tma_prefetch_desc(&maps.x);
+        for (uint32_t i = 0; i < p.num_probs; ++i)
+            tma_prefetch_desc(&maps.w[i]);
+    }
+    if (warp == 1) {
+        tmem_alloc<TMEM_COLS>(smem_u32(const_cast<uint32_t*>(tmem_slot)));
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    // tile -> (projection, m-tile, n-tile); m fastest so CTAs running side by side share a
+    // weight panel in L2
+    auto decode_tile = [&](uint32_t tile, uint32_t& prob, uint32_t& m0, uint32_t& n0) {
+        prob = tile / tiles_per_prob;
+        const uint32_t r = tile - prob * tiles_per_prob;
+        m0 = (r % tiles_m) * BM;
+        n0 = (r / tiles_m) * BN;
+    };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer (converged warp)
+        uint32_t s = 0, ph = 0;
+        for (uint32_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+            uint32_t prob, m0, n0;
+            decode_tile(tile, prob, m0, n0);
+            const CUtensorMap* wmap = &maps.w[prob];
+            bool ok = true;
+            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                if (!mbar_wait_bounded(empty_bar(s), ph ^ 1u, abort_flag, p.status, SITE_EMPTY,
+                                       KERNEL_DQ_GEMM)) {
+                    ok = false;
+                    break;
+                }
+                if (elect_one()) {
+                    const uint32_t stage = smem_base + s * STAGE_BYTES;
+                    const int32_t k0 = kb * BK;
+                    mbar_expect_tx(full_bar(s), STAGE_BYTES);
+                    tma_load_2d(stage, &maps.x, full_bar(s), k0, (int32_t)m0);
+#pragma unroll
+                    for (int c = 0; c < B_CHUNKS; ++c)
+                        tma_load_2d(stage + A_BYTES + c * B_CHUNK_BYTES, wmap, full_bar(s),
+                                    (int32_t)n0 + c * 64, k0);
+                }
+                __syncwarp();
+                if (++s == STAGES) {
+                    s = 0;
+                    ph ^= 1u;
+                }
+            }
+            if (!ok)
+                break;
+        }
+        if (*abort_flag)
+            for (uint32_t spin = 0; spin < 2000; ++spin)
+                __nanosleep(100);
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer (converged warp)
+        uint32_t s = 0, ph = 0, local_tile = 0;
+        for (uint32_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local_tile) {
+            const uint32_t buf = local_tile & 1u;
+            const uint32_t acc_ph = (local_tile >> 1) & 1u;
+            if (!mbar_wait_bounded(tmem_empty_bar(buf), acc_ph ^ 1u, abort_flag, p.status,
+                                   SITE_TMEM_EMPTY, KERNEL_DQ_GEMM))
+                break;
+            tc_fence_after_sync();
+            const uint32_t d_tmem = tmem_base + buf * BN;
+            bool ok = true;
+            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                if (!mbar_wait_bounded(full_bar(s), ph, abort_flag, p.status, SITE_FULL,
+                                       KERNEL_DQ_GEMM)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t stage = smem_base + s * STAGE_BYTES;
+                // x: K-major, 8-row groups 1024 B apart.  weights: MN-major, 8-k groups 1024 B
+                // apart, the 64-column chunks B_CHUNK_BYTES apart.
+                const uint64_t a_desc = make_smem_desc_sw128(stage, 16, 1024);
+                const uint64_t b_desc =
+                    make_smem_desc_sw128(stage + A_BYTES, B_CHUNK_BYTES, 1024);
+                if (elect_one()) {
+#pragma unroll
+                    for (uint32_t kk = 0; kk < BK / UMMA_K; ++kk) {
+                        // x advances 32 bytes inside its swizzled row, weights 16 k-rows of 128 B
+                        umma_f16(d_tmem, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 128),
+                                 IDESC, (kb | kk) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(empty_bar(s));
+                    if (kb + 1 == num_kb)
+                        umma_commit(tmem_full_bar(buf));
+                }
+                __syncwarp();
+                if (++s == STAGES) {
+                    s = 0;
+                    ph ^= 1u;
+                }
+            }
+            if (!ok)
+                break;
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..5)
+        const uint32_t quarter = warp & 3u;
+        uint32_t local_tile = 0;
+        for (uint32_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local_tile) {
+            const uint32_t buf = local_tile & 1u;
+            const uint32_t acc_ph = (local_tile >> 1) & 1u;
+            uint32_t prob, m0, n0;
+            decode_tile(tile, prob, m0, n0);
+            const Problem& pr = p.probs[prob];
+            if (!mbar_wait_bounded(tmem_full_bar(buf), acc_ph, abort_flag, p.status, SITE_TMEM_FULL,
+                                   KERNEL_DQ_GEMM))
+                break;
+            tc_fence_after_sync();
+            const uint32_t row = m0 + quarter * 32 + lane;
+            const bool row_ok = row < p.m;
+            const uint32_t taddr = tmem_base + buf * BN + ((quarter * 32u) << 16);
+#pragma unroll 1
+            for (uint32_t c = 0; c < BN / 32; ++c) {
+                const uint32_t col0 = n0 + c * 32;
+                if (col0 >= p.n)
+                    break;  // warp-uniform
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(taddr + c * 32, r);
+                tmem_ld_wait();
+                if (!row_ok)
+                    continue;
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    v[j] = __uint_as_float(r[j]);
+                if (p.post_scale) {
+                    if (pr.col_scale != nullptr) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            if (col0 + j < p.n) {  // N % 8 == 0: whole vector in or out
+                                const float4 cs =
+                                    __ldg(reinterpret_cast<const float4*>(pr.col_scale + col0 + j));
+                                v[j] = __fmul_rn(v[j], cs.x);
+                                v[j + 1] = __fmul_rn(v[j + 1], cs.y);
+                                v[j + 2] = __fmul_rn(v[j + 2], cs.z);
+                                v[j + 3] = __fmul_rn(v[j + 3], cs.w);
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            v[j] = __fmul_rn(v[j], pr.scale);
+                    }
+                }
+                if (p.out_f16) {
+                    __half* dst = reinterpret_cast<__half*>(pr.out) + (size_t)row * p.n + col0;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        if (col0 + j < p.n) {
+                            uint4 pk;
+                            __half2 h0 = __floats2half2_rn(v[j], v[j + 1]);
+                            __half2 h1 = __floats2half2_rn(v[j + 2], v[j + 3]);
+                            __half2 h2 = __floats2half2_rn(v[j + 4], v[j + 5]);
+                            __half2 h3 = __floats2half2_rn(v[j + 6], v[j + 7]);
+                            pk.x = *reinterpret_cast<uint32_t*>(&h0);
+                            pk.y = *reinterpret_cast<uint32_t*>(&h1);
+                            pk.z = *reinterpret_cast<uint32_t*>(&h2);
+                            pk.w = *reinterpret_cast<uint32_t*>(&h3);
+                            *reinterpret_cast<uint4*>(dst + j) = pk;
+                        }
+                    }
+                } else {
+                    float* dst = reinterpret_cast<float*>(pr.out) + (size_t)row * p.n + col0;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4)
+                        if (col0 + j < p.n)
+                            *reinterpret_cast<float4*>(dst + j) =
+                                make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(tmem_empty_bar(buf));
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc<TMEM_COLS>(tmem_base);
+    }
 }
+
+}  // namespace f16g
+
+// ---------------------------------------------------------------- dequantisation pre-pass
+struct DequantArgs {
+    const void* w[3];
+    const __half* scales[3];
+    __half* out[3];
+};
+
+// s4 packed (word k/8 of column j at (k/8) + j*(K/8)) -> f16 [K,N] row-major.  Block = 64 columns
+// x 64 k through a shared-memory transpose so that both the packed reads (K-contiguous per column)
+// and the f16 writes (N-contiguous per k) are coalesced.
+__global__ void __launch_bounds__(256)
+dequant_s4_kernel(const DequantArgs args, uint32_t n, uint32_t k)
+{
+    __shared__ __half tile[64][64 + 2];
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(args.w[blockIdx.z]);
+    const __half* scales = args.scales[blockIdx.z];
+    __half* out = args.out[blockIdx.z];
+    const uint32_t n0 = blockIdx.x * 64, k0 = blockIdx.y * 64;
+    const uint32_t k_words = k >> 3;
+    // 64 columns x 8 words: thread -> (column, word)
+    for (uint32_t i = threadIdx.x; i < 64 * 8; i += 256) {
+        const uint32_t col = i >> 3, wi = i & 7u;
+        const uint32_t gc = n0 + col, gk = k0 + wi * 8;
+        if (gc < n && gk < k) {
+            const uint32_t word = w[(gk >> 3) + (size_t)gc * k_words];
+            const __half sc = scales[(size_t)(gk >> 7) * n + gc];
+#pragma unroll
+            for (int nib = 0; nib < 8; ++nib) {
+                const int32_t q = ((int32_t)(word << (28 - 4 * nib))) >> 28;
+                tile[wi * 8 + nib][col] = __hmul(__int2half_rn(q), sc);
+            }
+        }
+    }
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < 64 * 32; i += 256) {
+        const uint32_t kk = i >> 5, c2 = (i & 31u) * 2;
+        const uint32_t gk = k0 + kk, gc = n0 + c2;
+        if (gk < k && gc < n) {  // N is even on this path
+            const __half2 v = __halves2half2(tile[kk][c2], tile[kk][c2 + 1]);
+            *reinterpret_cast<__half2*>(out + (size_t)gk * n + gc) = v;
+        }
+    }
+}
+
+// s8 [K,N] -> f16 [K,N] (exact).
+__global__ void __launch_bounds__(256)
+dequant_s8_kernel(const DequantArgs args, size_t count)
+{
+    const int8_t* w = reinterpret_cast<const int8_t*>(args.w[blockIdx.y]);
+    __half* out = args.out[blockIdx.y];
+    const size_t stride = (size_t)gridDim.x * blockDim.x * 8;
+    for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < count; i += stride) {
+        // count % 8 == 0 and 8-byte aligned bases on this path
+        const int2 raw = *reinterpret_cast<const int2*>(w + i);
+        const int8_t* b = reinterpret_cast<const int8_t*>(&raw);
+        __half2 h[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            h[j] = __halves2half2(__int2half_rn((int)b[2 * j]), __int2half_rn((int)b[2 * j + 1]));
+        *reinterpret_cast<uint4*>(out + i) = *reinterpret_cast<uint4*>(h);
+    }
+}
+
+bool dq_gemm_fast_path_ok(int wfmt, const void* x, const DqProblem* probs, int num_probs,
+                          bool out_f16, uint32_t m, uint32_t n, uint32_t k)
+{
+    (void)m;
+    if (num_probs < 1 || num_probs > f16g::MAX_PROBS)
+        return false;
+    if (n % 8 != 0 || k % 8 != 0 || (uintptr_t)x % 16 != 0)
+        return false;
+    for (int i = 0; i < num_probs; ++i) {
+        if ((uintptr_t)probs[i].w % 16 != 0 || (uintptr_t)probs[i].out % 16 != 0)
+            return false;
+        if (probs[i].col_scale != nullptr && (uintptr_t)probs[i].col_scale % 16 != 0)
+            return false;
+        if (wfmt == WFMT_S4_PACKED && (k % 128 != 0 || probs[i].scales == nullptr))
+            return false;
+    }
+    (void)out_f16;
+    return true;
+}
+
+size_t dq_gemm_workspace_bytes(int num_probs, uint32_t n, uint32_t k)
+{
+    return (size_t)num_probs * (((size_t)k * n * sizeof(__half) + 255) & ~(size_t)255);
+}
+
+cudaError_t launch_dq_gemm(const DeviceCtx& ctx, int wfmt, const __half* x, const DqProblem* probs,
+                           int num_probs, bool out_f16, bool post_scale, uint32_t m, uint32_t n,
+                           uint32_t k, void* dq_workspace, cudaStream_t stream)
+{
+    using namespace f16g;
+    const size_t per = dq_gemm_workspace_bytes(1, n, k);
+    DequantArgs da = {};
+    for (int i = 0; i < num_probs; ++i) {
+        da.w[i] = probs[i].w;
+        da.scales[i] = probs[i].scales;
+        da.out[i] = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(dq_workspace) + per * i);
+    }
+    if (wfmt == WFMT_S4_PACKED) {
+        dim3 grid((n + 63) / 64, (k + 63) / 64, num_probs);
+        dequant_s4_kernel<<<grid, 256, 0, stream>>>(da, n, k);
+    } else {
+        const size_t count = (size_t)k * n;
+        dim3 grid((unsigned)((count / 8 + 255) / 256 < 4096 ? (count / 8 + 255) / 256 : 4096), num_probs);
+        dequant_s8_kernel<<<grid, 256, 0, stream>>>(da, count);
+    }
+    cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess)
+        return err;
+
+    TensorMaps maps;
+    err = encode_tensor_map_2d(&maps.x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x, k, m,
+                               (uint64_t)k * 2, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (err != cudaSuccess)
+        return err;
+    for (int i = 0; i < MAX_PROBS; ++i) {
+        const int j = i < num_probs ? i : 0;
+        err = encode_tensor_map_2d(&maps.w[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, da.out[j], n, k,
+                                   (uint64_t)n * 2, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (err != cudaSuccess)
+            return err;
+    }
+    Params p = {};
+    for (int i = 0; i < num_probs; ++i) {
+        p.probs[i].out = probs[i].out;
+        p.probs[i].col_scale = probs[i].col_scale;
+        p.probs[i].scale = probs[i].scale;
+    }
+    p.num_probs = (uint32_t)num_probs;
+    p.m = m;
+    p.n = n;
+    p.k = k;
+    p.out_f16 = out_f16 ? 1 : 0;
+    p.post_scale = post_scale ? 1 : 0;
+    p.status = ctx.status;
+    const uint32_t tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN) * (uint32_t)num_probs;
+    const uint32_t grid = tiles < (uint32_t)ctx.num_sms ? tiles : (uint32_t)ctx.num_sms;
+    static bool attr_set[64] = {};
+    if (!attr_set[ctx.device]) {
+        err = cudaFuncSetAttribute(f16_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   SMEM_BYTES);
+        if (err != cudaSuccess)
+            return err;
+        attr_set[ctx.device] = true;
+    }
+    f16_gemm_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(maps, p);
+    return cudaGetLastError();
+}
+
+}  // namespace kaio

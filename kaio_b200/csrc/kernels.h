@@ -32,6 +32,8 @@ struct DeviceCtx {
     size_t workspace_bytes = 0;
     uint32_t* tile_counters = nullptr;  // split-K arrival counters (self-resetting)
     size_t num_tile_counters = 0;
+    void* dq_workspace = nullptr;     // dequantised f16 weights of the call in flight
+    size_t dq_workspace_bytes = 0;
 };
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time libcuda).
@@ -74,9 +76,10 @@ cudaError_t launch_w4a16_decode(const DeviceCtx& ctx, const __half* x, const DqP
 
 bool dq_gemm_fast_path_ok(int wfmt, const void* x, const DqProblem* probs, int num_probs,
                           bool out_f16, uint32_t m, uint32_t n, uint32_t k);
+size_t dq_gemm_workspace_bytes(int num_probs, uint32_t n, uint32_t k);
 cudaError_t launch_dq_gemm(const DeviceCtx& ctx, int wfmt, const __half* x, const DqProblem* probs,
                            int num_probs, bool out_f16, bool post_scale, uint32_t m, uint32_t n,
-                           uint32_t k, cudaStream_t stream);
+                           uint32_t k, void* dq_workspace, cudaStream_t stream);
 
 // ---------------------------------------------------------------- attention
 struct AttnParams {
