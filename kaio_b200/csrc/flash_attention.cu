@@ -1,5 +1,508 @@
+// Flash attention forward for head_dim 128 on the 5th-generation tensor cores:
+//   out = softmax(Q K^T / sqrt(d) [+ causal mask j > i]) V,  f16 in, f32 accumulation,
+//   f32 or f16 out, any seq_k (online softmax over 128-row KV blocks).
+//
+// Replaces KAIO's `attention_tc` / `attention_tc_causal` kernel
+// (kaio-ops/src/attention_tc_kernel.rs:1454-2233: one warp per 16 query rows, the whole score row
+// in shared memory, seq_k <= 384) and adds the batched multi-head form that reads Q/K/V in place
+// from [batch*seq, heads*128] projection outputs.
+//
+// One CTA per (batch, head, 128 query rows), 192 threads:
+//   warp 0     TMA producer: Q once (two [128][64] boxes), then K and V blocks ([128 kv][128 d] as
+//              two 64-column boxes each) through a 2-stage ring; 128-byte swizzle.
+//   warp 1     MMA issuer (converged warp, elected lane):
+//                S_j  = Q K_j^T     tcgen05.mma kind::f16 M128 N128 K16 x8, Q and K from shared
+//                                   memory (both K-major), S in tensor memory (double buffered)
+//                O   += P_j V_j     M128 N128 K16 x8, P (f16) from TENSOR MEMORY, V from shared
+//                                   memory read MN-major (d contiguous), O in tensor memory
+//              QK^T of block j+1 is issued before P V of block j, so the tensor pipe works on the
+//              next scores while the softmax warps process the current ones.
+//   warps 2-5  softmax: thread = query row.  tcgen05.ld of the score row, scale by
+//              log2(e)/sqrt(d), causal / tail mask, running max with lazy rescale (O and the row
+//              sum are rescaled only when the max grows by more than 2^8), ex2, row sum, P packed
+//              to f16 and stored to tensor memory; at the end O / sum -> global.
+#include "common.cuh"
 #include "kernels.h"
+
 namespace kaio {
-bool flash_attention_ok(const AttnParams&) { return false; }
-cudaError_t launch_flash_attention(const DeviceCtx&, const AttnParams&, cudaStream_t) { return cudaErrorNotSupported; }
+namespace fa {
+
+constexpr int BQ = 128;   // query rows per CTA
+constexpr int BKV = 128;  // key/value rows per block
+constexpr int D = 128;    // head dim
+constexpr int KV_STAGES = 2;
+constexpr int Q_BYTES = BQ * D * 2;           // 32 KiB: two [128][64] sub-tiles
+constexpr int KV_TILE_BYTES = BKV * D * 2;    // 32 KiB each for K and V
+constexpr int STAGE_BYTES = 2 * KV_TILE_BYTES;  // K | V
+constexpr int SUB_BYTES = 128 * 128;          // one [128 rows][64 f16] sub-tile
+constexpr int NUM_THREADS = 192;
+constexpr int SMEM_BYTES = 1024 + Q_BYTES + KV_STAGES * STAGE_BYTES + 256;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t TMEM_S = 0;      // 2 x 128 columns (f32 scores)
+constexpr uint32_t TMEM_O = 256;    // 128 columns (f32 output accumulator)
+constexpr uint32_t TMEM_P = 384;    // 2 x 64 columns (f16 probabilities, 2 per column)
+
+constexpr uint32_t IDESC_QK = make_idesc(1, 0, 0, /*a K-major*/ 0, /*b K-major*/ 0, BQ, BKV);
+constexpr uint32_t IDESC_PV = make_idesc(1, 0, 0, /*a K-major*/ 0, /*b MN-major*/ 1, BQ, D);
+
+enum : uint32_t {
+    SITE_Q_FULL = 1, SITE_KV_FULL = 2, SITE_KV_EMPTY = 3, SITE_S_FULL = 4, SITE_P_FULL = 5,
+    SITE_PV_DONE = 6
+};
+
+struct Params {
+    void* out;
+    uint32_t batch, heads, seq_q, seq_k;
+    uint64_t o_row, o_head, o_batch;  // element strides of the output
+    float scale_log2;                 // log2(e) / sqrt(d)
+    int causal;
+    int out_f16;
+    uint32_t* status;
+};
+
+struct TensorMaps {
+    CUtensorMap q, k, v;
+};
+
+__device__ __forceinline__ float ex2_approx(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
+
+__device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_t (&r)[16])
+{
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
+        "r"(r[15])
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(
+            taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
+        "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]),
+        "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]),
+        "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_st_wait()
+{
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// D[tmem] (+)= A[tmem] * B[smem], f16 x f16 -> f32.
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                            uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t q_smem = smem_base;
+    const uint32_t kv_smem = smem_base + Q_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + Q_BYTES + KV_STAGES * STAGE_BYTES);
+    const uint32_t bar_base = smem_base + Q_BYTES + KV_STAGES * STAGE_BYTES;
+    const uint32_t q_full = bar_base;
+    auto kv_full = [&](uint32_t s) { return bar_base + 8u * (1 + s); };
+    auto kv_empty = [&](uint32_t s) { return bar_base + 8u * (3 + s); };
+    auto s_full = [&](uint32_t b) { return bar_base + 8u * (5 + b); };
+    auto p_full = [&](uint32_t b) { return bar_base + 8u * (7 + b); };
+    auto pv_done = [&](uint32_t b) { return bar_base + 8u * (9 + b); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 11);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+
+    // heavy (late, causal) query blocks first
+    const uint32_t num_qb = (p.seq_q + BQ - 1) / BQ;
+    const uint32_t qb = num_qb - 1 - blockIdx.x;
+    const uint32_t bh = blockIdx.y;
+    const uint32_t b = bh / p.heads, h = bh % p.heads;
+    const uint32_t q0 = qb * BQ;
+    // KV blocks this query block attends to
+    uint32_t kv_end = p.seq_k;
+    if (p.causal) {
+        const uint32_t lim = q0 + BQ;  // columns j <= i < q0 + BQ
+        kv_end = lim < kv_end ? lim : kv_end;
+    }
+    const uint32_t num_kv = (kv_end + BKV - 1) / BKV;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (uint32_t s = 0; s < KV_STAGES; ++s) {
+            mbar_init(kv_full(s), 1);
+            mbar_init(kv_empty(s), 1);
+        }
+        for (uint32_t i = 0; i < 2; ++i) {
+            mbar_init(s_full(i), 1);
+            mbar_init(p_full(i), 4);  // one arrive per softmax warp
+            mbar_init(pv_done(i), 1);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        tma_prefetch_desc(&maps.q);
+        tma_prefetch_desc(&maps.k);
+        tma_prefetch_desc(&maps.v);
+    }
+    if (warp == 1) {
+        tmem_alloc<TMEM_COLS>(smem_u32(const_cast<uint32_t*>(tmem_slot)));
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        const int32_t col0 = (int32_t)(h * D);
+        const int32_t q_row = (int32_t)(b * p.seq_q + q0);
+        if (elect_one()) {
+            mbar_expect_tx(q_full, Q_BYTES);
+            tma_load_2d(q_smem, &maps.q, q_full, col0, q_row);
+            tma_load_2d(q_smem + SUB_BYTES, &maps.q, q_full, col0 + 64, q_row);
+        }
+        __syncwarp();
+        for (uint32_t j = 0; j < num_kv; ++j) {
+            const uint32_t s = j & 1u, ph = (j >> 1) & 1u;
+            if (!mbar_wait_bounded(kv_empty(s), ph ^ 1u, abort_flag, p.status, SITE_KV_EMPTY,
+                                   KERNEL_FLASH_ATTN))
+                break;
+            if (elect_one()) {
+                const uint32_t stage = kv_smem + s * STAGE_BYTES;
+                const int32_t kv_row = (int32_t)(b * p.seq_k + j * BKV);
+                mbar_expect_tx(kv_full(s), STAGE_BYTES);
+                tma_load_2d(stage, &maps.k, kv_full(s), col0, kv_row);
+                tma_load_2d(stage + SUB_BYTES, &maps.k, kv_full(s), col0 + 64, kv_row);
+                tma_load_2d(stage + KV_TILE_BYTES, &maps.v, kv_full(s), col0, kv_row);
+                tma_load_2d(stage + KV_TILE_BYTES + SUB_BYTES, &maps.v, kv_full(s), col0 + 64,
+                            kv_row);
+            }
+            __syncwarp();
+        }
+        if (*abort_flag)
+            for (uint32_t spin = 0; spin < 2000; ++spin)
+                __nanosleep(100);
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        auto issue_qk = [&](uint32_t j) {
+            // S[j&1] = Q K_j^T : 8 steps of 16 along d; sub-tile d/64, 32 bytes inside the row
+            const uint32_t stage = kv_smem + (j & 1u) * STAGE_BYTES;
+            const uint32_t d_tmem = tmem_base + TMEM_S + (j & 1u) * BKV;
+            if (elect_one()) {
+#pragma unroll
+                for (uint32_t kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t off = (kk >> 2) * SUB_BYTES + (kk & 3u) * 32;
+                    umma_f16(d_tmem, make_smem_desc_sw128(q_smem + off, 16, 1024),
+                             make_smem_desc_sw128(stage + off, 16, 1024), IDESC_QK,
+                             kk != 0 ? 1u : 0u);
+                }
+                umma_commit(s_full(j & 1u));
+            }
+            __syncwarp();
+        };
+        bool ok = mbar_wait_bounded(q_full, 0, abort_flag, p.status, SITE_Q_FULL, KERNEL_FLASH_ATTN);
+        if (ok && num_kv > 0) {
+            ok = mbar_wait_bounded(kv_full(0), 0, abort_flag, p.status, SITE_KV_FULL,
+                                   KERNEL_FLASH_ATTN);
+            if (ok) {
+                tc_fence_after_sync();
+                issue_qk(0);
+            }
+        }
+        for (uint32_t j = 0; ok && j < num_kv; ++j) {
+            if (j + 1 < num_kv) {
+                // scores of the next block while the softmax warps work on this one
+                if (!mbar_wait_bounded(kv_full((j + 1) & 1u), ((j + 1) >> 1) & 1u, abort_flag,
+                                       p.status, SITE_KV_FULL, KERNEL_FLASH_ATTN))
+                    break;
+                tc_fence_after_sync();
+                issue_qk(j + 1);
+            }
+            if (!mbar_wait_bounded(p_full(j & 1u), (j >> 1) & 1u, abort_flag, p.status, SITE_P_FULL,
+                                   KERNEL_FLASH_ATTN))
+                break;
+            tc_fence_after_sync();
+            // O += P_j V_j : 8 steps of 16 along kv; P in tensor memory (8 columns per step),
+            // V MN-major: 16 kv rows of 128 bytes per step, the two 64-column halves SUB_BYTES apart
+            const uint32_t v_smem = kv_smem + (j & 1u) * STAGE_BYTES + KV_TILE_BYTES;
+            const uint32_t p_tmem = tmem_base + TMEM_P + (j & 1u) * (BKV / 2);
+            if (elect_one()) {
+#pragma unroll
+                for (uint32_t kk = 0; kk < BKV / 16; ++kk) {
+                    umma_f16_ts(tmem_base + TMEM_O, p_tmem + kk * 8,
+                                make_smem_desc_sw128(v_smem + kk * 2048, SUB_BYTES, 1024), IDESC_PV,
+                                (j | kk) != 0 ? 1u : 0u);
+                }
+                umma_commit(kv_empty(j & 1u));
+                umma_commit(pv_done(j & 1u));
+            }
+            __syncwarp();
+        }
+    } else {
+        // ------------------------------------------------------------ softmax + epilogue (warps 2..5)
+        const uint32_t quarter = warp & 3u;
+        const uint32_t lane_sel = (quarter * 32u) << 16;
+        const uint32_t row_local = quarter * 32 + lane;
+        const uint32_t row = q0 + row_local;  // query index inside this (batch, head)
+        float m_ref = 0.0f;                   // max used in the exponent (log2 units)
+        float l_sum = 0.0f;
+        bool ok = true;
+        for (uint32_t j = 0; j < num_kv; ++j) {
+            if (!mbar_wait_bounded(s_full(j & 1u), (j >> 1) & 1u, abort_flag, p.status, SITE_S_FULL,
+                                   KERNEL_FLASH_ATTN)) {
+                ok = false;
+                break;
+            }
+            tc_fence_after_sync();
+            const uint32_t s_tmem = tmem_base + TMEM_S + (j & 1u) * BKV + lane_sel;
+            const uint32_t col_base = j * BKV;
+            // columns allowed for this row: j_abs < seq_k and (causal) j_abs <= row
+            uint32_t col_lim = p.seq_k;
+            if (p.causal && row + 1 < col_lim)
+                col_lim = row + 1;
+            const bool need_mask = col_base + BKV > col_lim;
+
+            // ---- pass 1: block maximum of the scaled scores
+            float m_blk = -INFINITY;
+#pragma unroll 1
+            for (uint32_t c = 0; c < BKV / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(s_tmem + c * 32, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    float x = __uint_as_float(r[i]) * p.scale_log2;
+                    if (need_mask && col_base + c * 32 + i >= col_lim)
+                        x = -INFINITY;
+                    m_blk = fmaxf(m_blk, x);
+                }
+            }
+            // ---- lazy rescale: keep the old reference unless the max grew by more than 2^8
+            float alpha = 1.0f;
+            if (j == 0) {
+                m_ref = (m_blk == -INFINITY) ? 0.0f : m_blk;
+            } else if (m_blk > m_ref + 8.0f) {
+                alpha = ex2_approx(m_ref - m_blk);
+                m_ref = m_blk;
+            }
+            const bool any_rescale = __any_sync(0xffffffffu, alpha != 1.0f);
+            // P[j&1] was last read by the P V MMAs of block j-2; O by those of block j-1
+            if (j >= 2 && !mbar_wait_bounded(pv_done(j & 1u), ((j - 2) >> 1) & 1u, abort_flag,
+                                             p.status, SITE_PV_DONE, KERNEL_FLASH_ATTN)) {
+                ok = false;
+                break;
+            }
+            if (any_rescale) {
+                if (!mbar_wait_bounded(pv_done((j - 1) & 1u), ((j - 1) >> 1) & 1u, abort_flag,
+                                       p.status, SITE_PV_DONE, KERNEL_FLASH_ATTN)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                l_sum *= alpha;
+#pragma unroll 1
+                for (uint32_t c = 0; c < D / 32; ++c) {
+                    uint32_t r[32];
+                    tmem_ld_32x32b_x32(tmem_base + TMEM_O + lane_sel + c * 32, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                    tmem_st_32x32b_x32(tmem_base + TMEM_O + lane_sel + c * 32, r);
+                }
+                tmem_st_wait();
+            }
+            // ---- pass 2: p = 2^(x - m_ref), row sum, f16 pairs into tensor memory
+            const uint32_t p_tmem = tmem_base + TMEM_P + (j & 1u) * (BKV / 2) + lane_sel;
+#pragma unroll 1
+            for (uint32_t c = 0; c < BKV / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(s_tmem + c * 32, r);
+                tmem_ld_wait();
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float x0 = __uint_as_float(r[i]) * p.scale_log2 - m_ref;
+                    float x1 = __uint_as_float(r[i + 1]) * p.scale_log2 - m_ref;
+                    if (need_mask) {
+                        if (col_base + c * 32 + i >= col_lim)
+                            x0 = -INFINITY;
+                        if (col_base + c * 32 + i + 1 >= col_lim)
+                            x1 = -INFINITY;
+                    }
+                    const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+                    l_sum += p0 + p1;
+                    const __half2 hp = __floats2half2_rn(p0, p1);
+                    pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&hp);
+                }
+                tmem_st_32x32b_x16(p_tmem + c * 16, pk);
+            }
+            tmem_st_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(p_full(j & 1u));
+        }
+        // ---- epilogue: O / l -> global
+        if (ok && num_kv > 0) {
+            const uint32_t last = num_kv - 1;
+            ok = mbar_wait_bounded(pv_done(last & 1u), (last >> 1) & 1u, abort_flag, p.status,
+                                   SITE_PV_DONE, KERNEL_FLASH_ATTN);
+        }
+        if (ok) {
+            tc_fence_after_sync();
+            const float inv = l_sum > 0.0f ? 1.0f / l_sum : 0.0f;
+            const size_t obase = (size_t)b * p.o_batch + (size_t)h * p.o_head + (size_t)row * p.o_row;
+#pragma unroll 1
+            for (uint32_t c = 0; c < D / 32; ++c) {
+                uint32_t r[32];
+                if (num_kv > 0) {
+                    tmem_ld_32x32b_x32(tmem_base + TMEM_O + lane_sel + c * 32, r);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        r[i] = 0;
+                }
+                if (row < p.seq_q) {
+                    if (p.out_f16) {
+                        __half* dst = reinterpret_cast<__half*>(p.out) + obase + c * 32;
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            uint4 pk;
+                            __half2 h0 = __floats2half2_rn(__uint_as_float(r[i]) * inv,
+                                                           __uint_as_float(r[i + 1]) * inv);
+                            __half2 h1 = __floats2half2_rn(__uint_as_float(r[i + 2]) * inv,
+                                                           __uint_as_float(r[i + 3]) * inv);
+                            __half2 h2 = __floats2half2_rn(__uint_as_float(r[i + 4]) * inv,
+                                                           __uint_as_float(r[i + 5]) * inv);
+                            __half2 h3 = __floats2half2_rn(__uint_as_float(r[i + 6]) * inv,
+                                                           __uint_as_float(r[i + 7]) * inv);
+                            pk.x = *reinterpret_cast<uint32_t*>(&h0);
+                            pk.y = *reinterpret_cast<uint32_t*>(&h1);
+                            pk.z = *reinterpret_cast<uint32_t*>(&h2);
+                            pk.w = *reinterpret_cast<uint32_t*>(&h3);
+                            *reinterpret_cast<uint4*>(dst + i) = pk;
+                        }
+                    } else {
+                        float* dst = reinterpret_cast<float*>(p.out) + obase + c * 32;
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4)
+                            *reinterpret_cast<float4*>(dst + i) = make_float4(
+                                __uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv,
+                                __uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+                    }
+                }
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc<TMEM_COLS>(tmem_base);
+    }
+}
+
+}  // namespace fa
+
+bool flash_attention_ok(const AttnParams& p)
+{
+    if (p.d_k != 128 || p.d_v != 128)
+        return false;
+    const uint64_t strides[] = {p.q_row, p.k_row, p.v_row, p.o_row, p.q_head, p.k_head, p.v_head,
+                                p.o_head, p.q_batch, p.k_batch, p.v_batch, p.o_batch};
+    for (uint64_t s : strides)
+        if (s % 8 != 0)
+            return false;
+    if ((uintptr_t)p.q % 16 || (uintptr_t)p.k % 16 || (uintptr_t)p.v % 16 || (uintptr_t)p.out % 16)
+        return false;
+    // the TMA view is [batch*seq rows, heads*128 columns] with one row stride: batch b starts at
+    // row b*seq and head h at column h*128
+    if (p.heads > 1 && (p.q_head != 128 || p.k_head != 128 || p.v_head != 128))
+        return false;
+    if (p.batch > 1 &&
+        (p.q_batch != (uint64_t)p.seq_q * p.q_row || p.k_batch != (uint64_t)p.seq_k * p.k_row ||
+         p.v_batch != (uint64_t)p.seq_k * p.v_row))
+        return false;
+    if (p.q_row < (uint64_t)p.heads * 128 || p.k_row < (uint64_t)p.heads * 128 ||
+        p.v_row < (uint64_t)p.heads * 128)
+        return false;
+    return true;
+}
+
+cudaError_t launch_flash_attention(const DeviceCtx& ctx, const AttnParams& ap, cudaStream_t stream)
+{
+    using namespace fa;
+    TensorMaps maps;
+    const uint64_t width = (uint64_t)ap.heads * D;
+    cudaError_t err = encode_tensor_map_2d(&maps.q, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, ap.q, width,
+                                           (uint64_t)ap.batch * ap.seq_q, ap.q_row * 2, 64, BQ,
+                                           CU_TENSOR_MAP_SWIZZLE_128B);
+    if (err != cudaSuccess)
+        return err;
+    err = encode_tensor_map_2d(&maps.k, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, ap.k, width,
+                               (uint64_t)ap.batch * ap.seq_k, ap.k_row * 2, 64, BKV,
+                               CU_TENSOR_MAP_SWIZZLE_128B);
+    if (err != cudaSuccess)
+        return err;
+    err = encode_tensor_map_2d(&maps.v, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, ap.v, width,
+                               (uint64_t)ap.batch * ap.seq_k, ap.v_row * 2, 64, BKV,
+                               CU_TENSOR_MAP_SWIZZLE_128B);
+    if (err != cudaSuccess)
+        return err;
+    Params p = {};
+    p.out = ap.out;
+    p.batch = ap.batch;
+    p.heads = ap.heads;
+    p.seq_q = ap.seq_q;
+    p.seq_k = ap.seq_k;
+    p.o_row = ap.o_row;
+    p.o_head = ap.o_head;
+    p.o_batch = ap.o_batch;
+    p.scale_log2 = 1.4426950408889634f / sqrtf((float)D);
+    p.causal = ap.causal;
+    p.out_f16 = ap.out_f16;
+    p.status = ctx.status;
+    static bool attr_set[64] = {};
+    if (!attr_set[ctx.device]) {
+        err = cudaFuncSetAttribute(flash_attention_kernel,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (err != cudaSuccess)
+            return err;
+        attr_set[ctx.device] = true;
+    }
+    dim3 grid((ap.seq_q + BQ - 1) / BQ, ap.batch * ap.heads);
+    flash_attention_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(maps, p);
+    return cudaGetLastError();
+}
+
+}  // namespace kaio
