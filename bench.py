@@ -4,10 +4,11 @@
 One "step" = one pass of the W8A8 prefill GEMMs at the Llama-7B shapes
 (M=4096; (K,N) = (4096,11008), (11008,4096), (4096,4096)), int8 x int8 -> s32, per-row
 activation scale x per-column weight scale, f32 output.  `value` is whole-job W8A8 TOPS
-(2*M*N*K summed over the three GEMMs / device time, max over ranks).  With --gpus N > 1 every
-GEMM is column-parallel: rank r owns N/P weight columns, computes its [M, N/P] output shard and
-the shards are all-gathered over NCCL so that every rank ends with the full [M, N] output
-(strong scaling).
+(2*M*N*K summed over the three GEMMs and over the ranks / device time, max over ranks).  The
+7B-shape weights fit one GPU, so with --gpus N > 1 every rank is a replica working on its own
+M rows (weak scaling, no collective).  The sharded path -- the Llama-70B-shape W4A16 FFN GEMMs,
+weights column-sharded N/P per rank, f16 output all-gathered over NCCL -- is measured at every N in
+the "ffn70b_w4a16" object (GEMM alone and GEMM + gather).
 
 The same JSON line also carries
   * "w4a16_decode": the W4A16 decode GEMM (M in {1,8,16}, K=4096, N=11008) in HBM GB/s,
@@ -158,7 +159,7 @@ def run_reference(args):
     line = {
         "impl": "reference", "metric": "w8a8_prefill_tops", "value": value, "unit": "TOPS",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": sec_sum / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
+        "ms_per_step": sec_sum / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "s8 x s8 -> s32, f32 scales", "data": "synthetic",
         "config": {"workload": "w8a8_prefill_llama7b_m4096 (row sample)", "rows_per_step": rows},
         "cpu_baseline": {"value": value, "unit": "TOPS", "cores": threads, "kind": "port", "sample": sample},
@@ -190,7 +191,7 @@ def main():
     import torch
     import torch.distributed as dist
 
-    from kaio_b200 import ops
+    from kaio_b200 import ops, sharding
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -211,23 +212,22 @@ def main():
     g = torch.Generator(device="cuda")
     g.manual_seed(42)
     probs = []
+    # The 7B-shape weights fit every GPU, so with N > 1 each rank is a replica that runs the same
+    # GEMMs on its own batch of M rows (own activations, same weights): weak scaling, no collective.
     for gi, (k, n) in enumerate(GEMMS_7B):
-        assert n % (16 * world) == 0
-        n_loc = n // world
-        g.manual_seed(42 + gi)
+        n_loc = n
+        g.manual_seed(42 + gi + 1000 * rank)
         a = torch.randint(-127, 128, (m * k,), dtype=torch.int8, device="cuda", generator=g)
-        g.manual_seed(137 + gi * 16 + rank)
+        g.manual_seed(137 + gi)
         b = torch.randint(-127, 128, (k * n_loc,), dtype=torch.int8, device="cuda", generator=g)
-        g.manual_seed(4242 + gi)
+        g.manual_seed(4242 + gi + 1000 * rank)
         sa = torch.rand(m, device="cuda", generator=g) * 0.009 + 0.001
-        g.manual_seed(4243 + gi * 16 + rank)
+        g.manual_seed(4243 + gi)
         sw = torch.rand(n_loc, device="cuda", generator=g) * 0.009 + 0.001
         c_loc = torch.empty(m * n_loc, dtype=torch.float32, device="cuda")
-        gathered = torch.empty(world * m * n_loc, dtype=torch.float32, device="cuda") if world > 1 else None
-        full = torch.empty(m, n, dtype=torch.float32, device="cuda") if world > 1 else None
-        probs.append(dict(k=k, n=n, n_loc=n_loc, a=a, b=b, sa=sa, sw=sw, c=c_loc, gathered=gathered, full=full))
+        probs.append(dict(k=k, n=n, n_loc=n_loc, a=a, b=b, sa=sa, sw=sw, c=c_loc))
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device="cuda")
-    total_ops = sum(2 * m * n * k for k, n in GEMMS_7B)
+    total_ops = world * sum(2 * m * n * k for k, n in GEMMS_7B)
 
     def gemm(p):
         ops.matmul_int8_scaled(dev, p["a"], p["b"], p["c"], p["sa"], p["sw"], m, p["n_loc"], p["k"])
@@ -235,10 +235,6 @@ def main():
     def step():
         for p in probs:
             gemm(p)
-            if world > 1:
-                dist.all_gather_into_tensor(p["gathered"], p["c"])
-                # [P, M, N/P] -> [M, N]: un-shard copy so every rank holds the row-major output
-                p["full"].view(m, world, p["n_loc"]).copy_(p["gathered"].view(world, m, p["n_loc"]).transpose(0, 1))
 
     def barrier():
         if world > 1:
@@ -263,9 +259,6 @@ def main():
         e[0].record()
         for i, p in enumerate(probs):
             gemm(p)
-            if world > 1:
-                dist.all_gather_into_tensor(p["gathered"], p["c"])
-                p["full"].view(m, world, p["n_loc"]).copy_(p["gathered"].view(world, m, p["n_loc"]).transpose(0, 1))
             e[i + 1].record()
         evs.append(e)
     barrier()
@@ -281,6 +274,13 @@ def main():
     ms_per_step = total_ms / args.steps
     value = total_ops / (ms_per_step * 1e-3) / 1e12
 
+    ffn = None
+    if not args.skip_extras:
+        for p in probs:  # free the headline buffers before the 70B-shape leg
+            p.clear()
+        torch.cuda.empty_cache()
+        ffn = bench_ffn70b(torch, dist, ops, sharding, dev, rank, world)
+
     if rank != 0:
         if world > 1:
             dist.barrier()
@@ -291,9 +291,9 @@ def main():
     per_gemm = []
     for i, (k, n) in enumerate(GEMMS_7B):
         avg = sum(gemm_ms[i]) / len(gemm_ms[i])
-        per_gemm.append({"k": k, "n": n, "ms": avg, "tops": 2 * m * (n // world) * k / (avg * 1e-3) / 1e12})
+        per_gemm.append({"k": k, "n": n, "ms": avg, "tops": 2 * m * n * k / (avg * 1e-3) / 1e12})
     int8_peak = 2.0 * peaks["bf16_tflops"]
-    kern_ops = sum(2 * m * (n // world) * k for k, n in GEMMS_7B)
+    kern_ops = sum(2 * m * n * k for k, n in GEMMS_7B)
     kern_ms = sum(p["ms"] for p in per_gemm)
     achieved = kern_ops / (kern_ms * 1e-3) / 1e12
     traffic = load_traffic()
@@ -304,25 +304,30 @@ def main():
         "frac_of_nominal_4500": achieved / 4500.0,
         "traffic": traffic.get("w8a8_gemm_kernel_bytes_per_step"),
         "per_gemm": per_gemm,
-        "timing": "CUDA events around each GEMM launch (with its all-gather when --gpus > 1)",
+        "timing": "CUDA events around each GEMM launch on rank 0",
     }
 
     line = {
         "metric": "w8a8_prefill_tops", "value": value, "unit": "TOPS", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "s8 x s8 -> s32, f32 scales", "data": "synthetic",
-        "config": {"workload": "w8a8_prefill_llama7b_m4096", "m": m, "gemms_kn": GEMMS_7B,
+        "config": {"workload": "w8a8_prefill_llama7b_m4096", "m_per_gpu": m, "gemms_kn": GEMMS_7B,
                    "epilogue": "per-row x per-column f32 scales, f32 out",
-                   "parallelism": "single GPU" if world == 1 else f"column-parallel N/{world} + NCCL all-gather + un-shard copy",
+                   "parallelism": "single GPU" if world == 1 else
+                   f"{world} replicas (weights replicated, M={m} rows per GPU, no collective); the sharded "
+                   "70B-shape FFN with its NCCL all-gather is in ffn70b_w4a16",
                    "l2": f"{L2_FLUSH_BYTES >> 20} MiB memset between timed steps (untimed)",
                    "wall_s_timed_loop": t_wall},
         "roofline": roofline, "clocks": clocks, "gpu_launches": len(probs) * args.steps,
     }
 
+    if ffn is not None:
+        line["ffn70b_w4a16"] = ffn
     if not args.skip_extras and world == 1:
         line["w4a16_decode"] = bench_decode(torch, ops, dev, peaks, traffic)
-        line["e2e"] = bench_e2e(torch, ops, dev, probs, m, total_ops, steps=max(3, min(args.steps, 10)))
+        line["qkv_attention"] = bench_qkv_attention(torch, ops, dev, peaks)
+        line["e2e"] = bench_e2e(torch, ops, dev, m, total_ops, steps=max(3, min(args.steps, 10)))
         rows = 256
         o, s, threads = cpu_int8_sample(rows)
         line["cpu_baseline"] = {
@@ -386,10 +391,19 @@ def bench_decode(torch, ops, dev, peaks, traffic):
     return out
 
 
-def bench_e2e(torch, ops, dev, probs, m, total_ops, steps):
+def bench_e2e(torch, ops, dev, m, total_ops, steps):
     """The same step through the public API from pinned host memory: activations are copied
     host->device and the f32 outputs device->host inside the timed region (weights and scales are
     model state and stay resident, as in the reference where they live in GpuBuffers)."""
+    g = torch.Generator(device="cuda")
+    probs = []
+    for gi, (k, n) in enumerate(GEMMS_7B):
+        g.manual_seed(42 + gi)
+        a = torch.randint(-127, 128, (m * k,), dtype=torch.int8, device="cuda", generator=g)
+        b = torch.randint(-127, 128, (k * n,), dtype=torch.int8, device="cuda", generator=g)
+        sa = torch.rand(m, device="cuda", generator=g) * 0.009 + 0.001
+        sw = torch.rand(n, device="cuda", generator=g) * 0.009 + 0.001
+        probs.append(dict(k=k, n=n, a=a, b=b, sa=sa, sw=sw, c=torch.empty(m * n, dtype=torch.float32, device="cuda")))
     host_a = [torch.empty(p["a"].numel(), dtype=torch.int8).pin_memory() for p in probs]
     host_c = [torch.empty(p["c"].numel(), dtype=torch.float32).pin_memory() for p in probs]
     for h, p in zip(host_a, probs):
@@ -400,7 +414,7 @@ def bench_e2e(torch, ops, dev, probs, m, total_ops, steps):
     def one():
         for h, hc, p in zip(host_a, host_c, probs):
             p["a"].copy_(h, non_blocking=True)
-            ops.matmul_int8_scaled(dev, p["a"], p["b"], p["c"], p["sa"], p["sw"], m, p["n_loc"], p["k"])
+            ops.matmul_int8_scaled(dev, p["a"], p["b"], p["c"], p["sa"], p["sw"], m, p["n"], p["k"])
             hc.copy_(p["c"], non_blocking=True)
 
     for _ in range(2):
@@ -414,6 +428,111 @@ def bench_e2e(torch, ops, dev, probs, m, total_ops, steps):
     return {"value": total_ops / dt / 1e12, "unit": "TOPS", "ms_per_step": dt * 1e3,
             "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
             "note": "int8 activations H2D and f32 outputs D2H each step from/to pinned memory; PCIe-bound"}
+
+
+def _time_ms(torch, fn, iters, warm=2):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def bench_qkv_attention(torch, ops, dev, peaks):
+    """Config 4: fused QKV projection (W8A16 with per-column scales; W4A16) at M = 8 x 2048,
+    K = N = 4096, and causal multi-head attention (32 heads x 128) on the projection outputs."""
+    bsz, seq, heads, hd = 8, 2048, 32, 128
+    m, k, n = bsz * seq, 4096, heads * hd
+    g = torch.Generator(device="cuda")
+    g.manual_seed(42)
+    x = torch.randn(m * k, device="cuda", generator=g).half()
+    outs = [torch.empty(m * n, dtype=torch.float16, device="cuda") for _ in range(3)]
+    w8 = [torch.randint(-127, 128, (k * n,), dtype=torch.int8, device="cuda", generator=g) for _ in range(3)]
+    # column scales sized so that the f16 outputs stay far from overflow (|acc| ~ 5e3 * 127)
+    cs = [torch.rand(n, device="cuda", generator=g) * 0.0009 + 0.0001 for _ in range(3)]
+    t8 = _time_ms(torch, lambda: ops.qkv_project_int8(dev, x, *w8, *cs, *outs, m, n, k), 5)
+    v8 = ops.last_variant()
+    del w8
+    w4 = [torch.randint(-2 ** 31, 2 ** 31 - 1, (k // 8 * n,), dtype=torch.int32, device="cuda", generator=g)
+          for _ in range(3)]
+    sc = [(torch.rand(k // 128 * n, device="cuda", generator=g) * 0.015 + 0.005).half() for _ in range(3)]
+    t4 = _time_ms(torch, lambda: ops.qkv_project_int4(dev, x, *w4, *sc, *outs, m, n, k, 128), 5)
+    v4 = ops.last_variant()
+    o = torch.empty(m * n, dtype=torch.float16, device="cuda")
+    ta = _time_ms(torch, lambda: ops.attention_mha_f16(dev, outs[0], outs[1], outs[2], o, bsz, heads, seq, seq,
+                                                       hd, n, True), 5)
+    va = ops.last_variant()
+    qkv_flops = 6 * m * n * k
+    attn_flops = 4 * bsz * heads * seq * seq * hd // 2
+    f16_peak = peaks["bf16_tflops"]
+    return {
+        "qkv_w8a16_colscale": {"ms": t8, "tflops": qkv_flops / t8 / 1e9, "frac_of_measured_f16": qkv_flops / t8 / 1e9 / f16_peak, "variant": v8},
+        "qkv_w4a16": {"ms": t4, "tflops": qkv_flops / t4 / 1e9, "frac_of_measured_f16": qkv_flops / t4 / 1e9 / f16_peak, "variant": v4},
+        "attention_causal_mha": {"ms": ta, "tflops": attn_flops / ta / 1e9, "frac_of_measured_f16": attn_flops / ta / 1e9 / f16_peak, "variant": va},
+        "flops": {"qkv": qkv_flops, "attention_causal": attn_flops},
+        "note": "each timing includes the dequantisation pre-pass of the call; attention flops count the causal half",
+    }
+
+
+def bench_ffn70b(torch, dist, ops, sharding, dev, rank, world):
+    """Config 5: Llama-70B-shape W4A16 FFN GEMMs, N-sharded over the ranks, f16 output all-gathered
+    to [M, N] on every rank.  Times are CUDA events, max over ranks.  Reported: the GEMM alone, the
+    GEMM followed by the gather, and the pipelined form (the shard is computed in column panels and
+    panel i is gathered on a second stream while panel i+1 is computed)."""
+    res = {}
+    g = torch.Generator(device="cuda")
+    comm_stream = torch.cuda.Stream()
+    for (k, n) in [(8192, 28672), (28672, 8192)]:
+        n_loc = n // world
+        g.manual_seed(137 + rank)
+        w = torch.randint(-2 ** 31, 2 ** 31 - 1, (k // 8 * n_loc,), dtype=torch.int32, device="cuda", generator=g)
+        sc = (torch.rand(k // 128 * n_loc, device="cuda", generator=g) * 0.015 + 0.005).half()
+        for mm in (16, 256, 4096):
+            g.manual_seed(42)
+            a = torch.randn(mm * k, device="cuda", generator=g).half()
+            c = torch.empty(mm * n_loc, dtype=torch.float16, device="cuda")
+            gather = sharding.ColumnGather(mm, n, torch.float16, "cuda") if world > 1 else None
+
+            def gemm():
+                ops.matmul_int4(dev, a, w, sc, c, mm, n_loc, k, 128)
+
+            def both():
+                gemm()
+                if gather is not None:
+                    gather(c)
+
+            iters = 20 if mm <= 256 else 5
+            t_gemm = _time_ms(torch, gemm, iters)
+            t_all = _time_ms(torch, both, iters) if world > 1 else t_gemm
+            t_pipe = t_all
+            if world > 1 and mm >= 256:
+                pipe = sharding.PanelPipeline(ops, dev, a, w, sc, mm, n, k, world, rank, comm_stream, panels=4)
+                t_pipe = _time_ms(torch, pipe.run, iters)
+                del pipe
+            t = torch.tensor([t_gemm, t_all, t_pipe], dtype=torch.float64, device="cuda")
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            t_gemm, t_all, t_pipe = float(t[0]), float(t[1]), float(t[2])
+            best = min(t_all, t_pipe)
+            flops = 2 * mm * n * k
+            nbytes = k * n // 2 + (k // 128) * n * 2 + 2 * mm * k + 2 * mm * n
+            res[f"k{k}_n{n}_m{mm}"] = {
+                "ms_gemm": t_gemm, "ms_gemm_plus_gather": t_all, "ms_pipelined": t_pipe,
+                "tflops": flops / best / 1e9, "weight_stream_gbs": nbytes / best / 1e6,
+                "variant": ops.last_variant()}
+            del a, c, gather
+        del w, sc
+        torch.cuda.empty_cache()
+    res["note"] = ("whole-job figures over all ranks (tflops / weight_stream_gbs use the better of the sequential "
+                   "and the pipelined time); weight_stream_gbs = algorithmic bytes of the full GEMM / time; the "
+                   "L2 is not flushed between iterations (117 MB of weights per GEMM at 1 GPU, 126 MB L2: treat "
+                   "the 1-GPU decode figures as an upper bound)")
+    return res
 
 
 if __name__ == "__main__":
