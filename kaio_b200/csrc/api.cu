@@ -375,9 +375,14 @@ static int32_t run_int8(int epi, const int8_t* a, size_t a_len, const int8_t* b,
         return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool scales_aligned = epi != EPI_ROWCOL || ((uintptr_t)w_scale % 16 == 0);
-    if (w8a8_fast_path_ok(a, b, c, m, n, k) && scales_aligned)
+    if (w8a8_fast_path_ok(a, b, c, m, n, k) && scales_aligned) {
+        if (w8a8_2cta_ok(m, n, k))
+            return finish(launch_w8a8_gemm_2cta(*ctx, epi, a, b, c, scale, a_scale, w_scale, m, n,
+                                                k, s),
+                          "matmul_int8", "w8a8_tcgen05_2cta");
         return finish(launch_w8a8_gemm(*ctx, epi, a, b, c, scale, a_scale, w_scale, m, n, k, s),
                       "matmul_int8", "w8a8_tcgen05");
+    }
     return finish(launch_int8_generic(epi, a, b, c, scale, a_scale, w_scale, m, n, k, s),
                   "matmul_int8", "int8_generic");
 }

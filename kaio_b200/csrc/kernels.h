@@ -48,6 +48,11 @@ bool w8a8_fast_path_ok(const void* a, const void* b, const void* out, uint32_t m
 cudaError_t launch_w8a8_gemm(const DeviceCtx& ctx, int epi, const int8_t* a, const int8_t* b,
                              void* out, float scale, const float* a_scale, const float* w_scale,
                              uint32_t m, uint32_t n, uint32_t k, cudaStream_t stream);
+bool w8a8_2cta_ok(uint32_t m, uint32_t n, uint32_t k);
+cudaError_t launch_w8a8_gemm_2cta(const DeviceCtx& ctx, int epi, const int8_t* a, const int8_t* b,
+                                  void* out, float scale, const float* a_scale,
+                                  const float* w_scale, uint32_t m, uint32_t n, uint32_t k,
+                                  cudaStream_t stream);
 cudaError_t launch_int8_generic(int epi, const int8_t* a, const int8_t* b, void* out, float scale,
                                 const float* a_scale, const float* w_scale, uint32_t m, uint32_t n,
                                 uint32_t k, cudaStream_t stream);

@@ -10,8 +10,11 @@
 //               A is K-major, B is read MN-major straight from its row-major [K,N] layout,
 //               so no transpose or repack of the weights is needed.  Accumulators live in
 //               tensor memory, double buffered (2 x 256 columns).
-//   warps 2-5   epilogue: tcgen05.ld the s32 accumulators, cvt.rn.f32.s32, scale, 16-byte
-//               stores.  Runs on buffer b while the mainloop fills buffer b^1.
+//   warps 2-5   epilogue: tcgen05.ld the s32 accumulators, cvt.rn.f32.s32, scale, stage a
+//               [32 rows][32 columns] block in swizzled shared memory and hand it to a TMA bulk
+//               store (full 128-byte lines; tile edges are clipped by the tensor map).  Runs on
+//               buffer b while the mainloop fills buffer b^1.  (Per-thread row-strided 16-byte
+//               stores were the bottleneck of an earlier version: 2.3 vs 3.4 POPS without them.)
 //
 // Shapes: K % 32 == 0 (reference contract), N % 16 == 0 and 16-byte aligned bases (TMA
 // stride/alignment rules).  Ragged M and N tile edges are zero-filled by TMA on the way in
@@ -33,7 +36,9 @@ constexpr int B_BYTES = 2 * B_HALF_BYTES;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;  // 48 KiB
 constexpr int TMEM_COLS = 512;                  // 2 accumulator buffers x 256 columns
 constexpr int NUM_THREADS = 192;
-constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 256;
+constexpr int STG_BYTES = 32 * 128;              // one staged block: 32 rows x 128 B
+constexpr int STG_TOTAL = 4 * 2 * STG_BYTES;     // 4 epilogue warps x 2 buffers
+constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + STG_TOTAL + 256;
 
 constexpr uint32_t IDESC = make_idesc(/*d=s32*/ 2, /*a=s8*/ 1, /*b=s8*/ 1, /*a K-major*/ 0,
                                       /*b MN-major*/ 1, BM, BN);
@@ -52,15 +57,18 @@ struct Params {
 template <int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                 const __grid_constant__ CUtensorMap tmap_b, const Params p)
+                 const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_c, const Params p)
 {
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment: required by the 128-byte swizzle pattern.
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + STAGES * STAGE_BYTES);
+    uint8_t* stg_gen = smem_gen + STAGES * STAGE_BYTES;
+    const uint32_t stg_base = smem_base + STAGES * STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + STAGES * STAGE_BYTES + STG_TOTAL);
     // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
-    const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+    const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES + STG_TOTAL;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
     auto tmem_full_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
@@ -89,6 +97,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         fence_barrier_init();
         tma_prefetch_desc(&tmap_a);
         tma_prefetch_desc(&tmap_b);
+        tma_prefetch_desc(&tmap_c);
     }
     if (warp == 1) {
         tmem_alloc<TMEM_COLS>(smem_u32(const_cast<uint32_t*>(tmem_slot)));
@@ -101,20 +110,19 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
-        if (lane == 0) {
-            uint32_t it = 0;
-            bool ok = true;
-            for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-                const int32_t m0 = (tile % tiles_m) * BM;
-                const int32_t n0 = (tile / tiles_m) * BN;
-                for (uint32_t kb = 0; kb < num_kb; ++kb, ++it) {
-                    const uint32_t s = it % STAGES;
-                    const uint32_t ph = (it / STAGES) & 1u;
-                    if (!mbar_wait_bounded(empty_bar(s), ph ^ 1u, abort_flag, p.status, SITE_EMPTY,
-                                           KERNEL_W8A8)) {
-                        ok = false;
-                        break;
-                    }
+        // Converged warp, one elected lane issues (keeps addresses in uniform registers).
+        uint32_t s = 0, ph = 0;
+        bool ok = true;
+        for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+            const int32_t m0 = (tile % tiles_m) * BM;
+            const int32_t n0 = (tile / tiles_m) * BN;
+            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                if (!mbar_wait_bounded(empty_bar(s), ph ^ 1u, abort_flag, p.status, SITE_EMPTY,
+                                       KERNEL_W8A8)) {
+                    ok = false;
+                    break;
+                }
+                if (elect_one()) {
                     const uint32_t stage = smem_base + s * STAGE_BYTES;
                     mbar_expect_tx(full_bar(s), STAGE_BYTES);
                     const int32_t k0 = kb * BK;
@@ -122,56 +130,62 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     tma_load_2d(stage + A_BYTES, &tmap_b, full_bar(s), n0, k0);
                     tma_load_2d(stage + A_BYTES + B_HALF_BYTES, &tmap_b, full_bar(s), n0 + 128, k0);
                 }
+                __syncwarp();
+                if (++s == STAGES) {
+                    s = 0;
+                    ph ^= 1u;
+                }
             }
-            if (!ok) {
-                // Give copies already in flight a bounded time to land before the CTA exits.
-                for (uint32_t spin = 0; spin < 2000; ++spin)
-                    __nanosleep(100);
-            }
+        }
+        if (!ok) {
+            // Give copies already in flight a bounded time to land before the CTA exits.
+            for (uint32_t spin = 0; spin < 2000; ++spin)
+                __nanosleep(100);
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            uint32_t it = 0;
-            uint32_t local_tile = 0;
-            bool ok = true;
-            for (uint32_t tile = blockIdx.x; ok && tile < num_tiles;
-                 tile += gridDim.x, ++local_tile) {
-                const uint32_t buf = local_tile & 1u;
-                const uint32_t acc_ph = (local_tile >> 1) & 1u;
-                if (!mbar_wait_bounded(tmem_empty_bar(buf), acc_ph ^ 1u, abort_flag, p.status,
-                                       SITE_TMEM_EMPTY, KERNEL_W8A8)) {
+        // Converged warp, one elected lane issues.
+        uint32_t s = 0, ph = 0, local_tile = 0;
+        bool ok = true;
+        for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++local_tile) {
+            const uint32_t buf = local_tile & 1u;
+            const uint32_t acc_ph = (local_tile >> 1) & 1u;
+            if (!mbar_wait_bounded(tmem_empty_bar(buf), acc_ph ^ 1u, abort_flag, p.status,
+                                   SITE_TMEM_EMPTY, KERNEL_W8A8)) {
+                ok = false;
+                break;
+            }
+            tc_fence_after_sync();
+            const uint32_t d_tmem = tmem_base + buf * BN;
+            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                if (!mbar_wait_bounded(full_bar(s), ph, abort_flag, p.status, SITE_FULL,
+                                       KERNEL_W8A8)) {
                     ok = false;
                     break;
                 }
                 tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + buf * BN;
-                for (uint32_t kb = 0; kb < num_kb; ++kb, ++it) {
-                    const uint32_t s = it % STAGES;
-                    const uint32_t ph = (it / STAGES) & 1u;
-                    if (!mbar_wait_bounded(full_bar(s), ph, abort_flag, p.status, SITE_FULL,
-                                           KERNEL_W8A8)) {
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after_sync();
-                    const uint32_t stage = smem_base + s * STAGE_BYTES;
-                    // A: K-major, 8-row groups 1024 B apart.  B: MN-major, 8-k groups 1024 B
-                    // apart, the two 128-byte N chunks B_HALF_BYTES apart.
-                    const uint64_t a_desc = make_smem_desc_sw128(stage, 16, 1024);
-                    const uint64_t b_desc =
-                        make_smem_desc_sw128(stage + A_BYTES, B_HALF_BYTES, 1024);
+                const uint32_t stage = smem_base + s * STAGE_BYTES;
+                // A: K-major, 8-row groups 1024 B apart.  B: MN-major, 8-k groups 1024 B
+                // apart, the two 128-byte N chunks B_HALF_BYTES apart.
+                const uint64_t a_desc = make_smem_desc_sw128(stage, 16, 1024);
+                const uint64_t b_desc = make_smem_desc_sw128(stage + A_BYTES, B_HALF_BYTES, 1024);
+                if (elect_one()) {
 #pragma unroll
                     for (uint32_t kk = 0; kk < BK / UMMA_K; ++kk) {
                         // advance A by 32 bytes inside the swizzled row, B by 32 k-rows of 128 B
-                        const uint64_t a_k = a_desc + ((kk * UMMA_K) >> 4);
-                        const uint64_t b_k = b_desc + ((kk * UMMA_K * 128) >> 4);
-                        umma_i8(d_tmem, a_k, b_k, IDESC, (kb | kk) != 0 ? 1u : 0u);
+                        umma_i8(d_tmem, a_desc + (uint64_t)((kk * UMMA_K) >> 4),
+                                b_desc + (uint64_t)((kk * UMMA_K * 128) >> 4), IDESC,
+                                (kb | kk) != 0 ? 1u : 0u);
                     }
                     umma_commit(empty_bar(s));  // frees the stage when these MMAs retire
+                    if (kb + 1 == num_kb)
+                        umma_commit(tmem_full_bar(buf));
                 }
-                if (ok)
-                    umma_commit(tmem_full_bar(buf));
+                __syncwarp();
+                if (++s == STAGES) {
+                    s = 0;
+                    ph ^= 1u;
+                }
             }
         }
     } else {
@@ -191,11 +205,11 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
             tc_fence_after_sync();
             const uint32_t row = m0 + quarter * 32 + lane;
-            const bool row_ok = row < p.m;
             float row_scale = 1.0f;
-            if (EPI == EPI_ROWCOL && row_ok)
+            if (EPI == EPI_ROWCOL && row < p.m)
                 row_scale = __ldg(p.a_scale + row);
             const uint32_t taddr = tmem_base + buf * BN + ((quarter * 32u) << 16);
+            const uint32_t ewarp = warp - 2;
 #pragma unroll 1
             for (uint32_t c = 0; c < BN / 32; ++c) {
                 const uint32_t col0 = n0 + c * 32;
@@ -204,41 +218,50 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 uint32_t r[32];
                 tmem_ld_32x32b_x32(taddr + c * 32, r);
                 tmem_ld_wait();
-                if (row_ok) {
-                    if (EPI == EPI_S32) {
-                        int32_t* dst = reinterpret_cast<int32_t*>(p.out) + (size_t)row * p.n + col0;
+                if (EPI != EPI_S32) {
 #pragma unroll
-                        for (int j = 0; j < 32; j += 4)
-                            if (col0 + j < p.n)
-                                *reinterpret_cast<int4*>(dst + j) =
-                                    make_int4(r[j], r[j + 1], r[j + 2], r[j + 3]);
-                    } else {
-                        float* dst = reinterpret_cast<float*>(p.out) + (size_t)row * p.n + col0;
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            if (col0 + j < p.n) {  // N % 16 == 0: whole vector in or out
-                                float4 v;
-                                float f0 = __int2float_rn((int32_t)r[j + 0]);
-                                float f1 = __int2float_rn((int32_t)r[j + 1]);
-                                float f2 = __int2float_rn((int32_t)r[j + 2]);
-                                float f3 = __int2float_rn((int32_t)r[j + 3]);
-                                if (EPI == EPI_SCALAR) {
-                                    v.x = __fmul_rn(f0, p.scale);
-                                    v.y = __fmul_rn(f1, p.scale);
-                                    v.z = __fmul_rn(f2, p.scale);
-                                    v.w = __fmul_rn(f3, p.scale);
-                                } else {
-                                    const float4 ws =
-                                        __ldg(reinterpret_cast<const float4*>(p.w_scale + col0 + j));
-                                    v.x = __fmul_rn(__fmul_rn(f0, row_scale), ws.x);
-                                    v.y = __fmul_rn(__fmul_rn(f1, row_scale), ws.y);
-                                    v.z = __fmul_rn(__fmul_rn(f2, row_scale), ws.z);
-                                    v.w = __fmul_rn(__fmul_rn(f3, row_scale), ws.w);
-                                }
-                                *reinterpret_cast<float4*>(dst + j) = v;
-                            }
+                    for (int j = 0; j < 32; j += 4) {
+                        float f0 = __int2float_rn((int32_t)r[j + 0]);
+                        float f1 = __int2float_rn((int32_t)r[j + 1]);
+                        float f2 = __int2float_rn((int32_t)r[j + 2]);
+                        float f3 = __int2float_rn((int32_t)r[j + 3]);
+                        if (EPI == EPI_SCALAR) {
+                            f0 = __fmul_rn(f0, p.scale);
+                            f1 = __fmul_rn(f1, p.scale);
+                            f2 = __fmul_rn(f2, p.scale);
+                            f3 = __fmul_rn(f3, p.scale);
+                        } else {
+                            float4 ws = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (col0 + j < p.n)  // N % 16 == 0: whole vector in or out
+                                ws = __ldg(reinterpret_cast<const float4*>(p.w_scale + col0 + j));
+                            f0 = __fmul_rn(__fmul_rn(f0, row_scale), ws.x);
+                            f1 = __fmul_rn(__fmul_rn(f1, row_scale), ws.y);
+                            f2 = __fmul_rn(__fmul_rn(f2, row_scale), ws.z);
+                            f3 = __fmul_rn(__fmul_rn(f3, row_scale), ws.w);
                         }
+                        r[j + 0] = __float_as_uint(f0);
+                        r[j + 1] = __float_as_uint(f1);
+                        r[j + 2] = __float_as_uint(f2);
+                        r[j + 3] = __float_as_uint(f3);
                     }
+                }
+                // stage the [32 rows][32 columns] block (128-byte rows, 128-byte swizzle) and
+                // store it with one TMA bulk store; the buffer used two blocks ago must have
+                // been read out by its store first
+                if (lane == 0)
+                    tma_store_wait_read<1>();
+                __syncwarp();
+                const uint32_t stg_off = (ewarp * 2 + (c & 1u)) * STG_BYTES;
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    *reinterpret_cast<uint4*>(stg_gen + stg_off + sw128_offset(lane, j)) =
+                        make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    tma_store_2d(&tmap_c, stg_base + stg_off, (int32_t)col0,
+                                 (int32_t)(m0 + quarter * 32));
+                    tma_store_commit();
                 }
             }
             tc_fence_before_sync();
@@ -249,6 +272,8 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
 
     // ---------------------------------------------------------------- teardown
+    if (warp >= 2 && lane == 0)
+        tma_store_wait_all<0>();  // the staged blocks must be out before shared memory goes away
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 1) {
@@ -287,6 +312,11 @@ cudaError_t launch_w8a8_gemm(const DeviceCtx& ctx, int epi, const int8_t* a, con
     err = encode_2d_u8(&tmap_b, b, n, k, n, 128, BK);
     if (err != cudaSuccess)
         return err;
+    CUtensorMap tmap_c;  // f32 and s32 outputs have the same geometry
+    err = encode_tensor_map_2d(&tmap_c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, out, n, m,
+                               (uint64_t)n * 4, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (err != cudaSuccess)
+        return err;
 
     Params p;
     p.out = out;
@@ -312,7 +342,7 @@ cudaError_t launch_w8a8_gemm(const DeviceCtx& ctx, int epi, const int8_t* a, con
                 return err;                                                                       \
             attr_set[E][ctx.device] = true;                                                       \
         }                                                                                         \
-        w8a8_gemm_kernel<E><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmap_a, tmap_b, p);        \
+        w8a8_gemm_kernel<E><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmap_a, tmap_b, tmap_c, p); \
     } while (0)
 
     switch (epi) {

@@ -1,0 +1,352 @@
+// W8A8 GEMM on CTA pairs (tcgen05 cta_group::2): C[M,N] = epilogue(A[M,K] (s8) * B[K,N] (s8)).
+//
+// Same arithmetic and the same operand layouts as the single-CTA kernel in w8a8_gemm.cu (which
+// stays the path for M <= 128); this one is for the prefill shapes, where a 128x256 tile per SM
+// needs 96 bytes of operands per clock from L2 and shared memory -- more than either delivers.
+// A pair of CTAs (a cluster of 2 on neighbouring SMs) computes a 256x256 tile with one
+// tcgen05.mma.cta_group::2 M256 N256 K32 per step: each CTA stages its own 128 rows of A and
+// only ITS HALF (128 columns) of B, and the tensor cores of both SMs read both halves.  Operand
+// traffic per SM drops by a third (64 B/clk at full rate) with plain, un-multicast TMA loads.
+//
+// Per CTA (192 threads):
+//   warp 0     TMA producer: A box [128 rows][128 B of K], B box [128 k][128 B of N] (this CTA's
+//              column half), 128-byte swizzle, 6-stage ring of 32 KiB.
+//              Both CTAs' loads credit their bytes to the LEADER's "stage full" barrier (the
+//              pair form of the TMA load lets the barrier live in the peer CTA), so the leader
+//              learns of the peer's data without a software relay -- a remote mbarrier arrive
+//              costs ~1800 cycles here and made a forwarding warp the bottleneck.
+//   warp 1     leader CTA only: waits for the stage (64 KiB from both CTAs), issues 4 pair MMAs
+//              per stage, and commits with a multicast arrive that frees the stage in both CTAs.
+//   warps 2-5  epilogue on this CTA's 128 accumulator rows (double-buffered tensor memory):
+//              tcgen05.ld, cvt.rn.f32.s32, scale, swizzled staging, TMA bulk store; then an
+//              arrive on the leader's "accumulator free" barrier.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace kaio {
+namespace w8a8x2 {
+
+constexpr int BM_CTA = 128;   // rows per CTA
+constexpr int BM = 256;       // rows per pair tile
+constexpr int BN = 256;
+constexpr int BK = 128;       // bytes == s8 elements per stage along K
+constexpr int UMMA_K = 32;
+constexpr int STAGES = 6;
+constexpr int A_BYTES = BM_CTA * BK;   // 16 KiB
+constexpr int B_BYTES = BK * 128;      // 16 KiB: [BK k-rows][this CTA's 128 B of N]
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;  // 32 KiB
+constexpr int STG_BYTES = 32 * 128;
+constexpr int STG_TOTAL = 4 * 2 * STG_BYTES;
+constexpr int TMEM_COLS = 512;  // 2 accumulator buffers x 256 columns, in each CTA
+constexpr int NUM_THREADS = 192;
+constexpr int NUM_BARS = 2 * STAGES + 4;
+constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + STG_TOTAL + NUM_BARS * 8 + 64;
+
+constexpr uint32_t IDESC = make_idesc(/*d=s32*/ 2, /*a=s8*/ 1, /*b=s8*/ 1, /*a K-major*/ 0,
+                                      /*b MN-major*/ 1, BM, BN);
+
+enum : uint32_t {
+    SITE_EMPTY = 11, SITE_FULL = 12, SITE_PEER_FULL = 13, SITE_TMEM_EMPTY = 14, SITE_TMEM_FULL = 15
+};
+
+struct Params {
+    const float* a_scale;
+    const float* w_scale;
+    float scale;
+    uint32_t m, n, k;
+    uint32_t* status;
+};
+
+template <int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+w8a8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                      const __grid_constant__ CUtensorMap tmap_b,
+                      const __grid_constant__ CUtensorMap tmap_c, const Params p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    uint8_t* stg_gen = smem_gen + STAGES * STAGE_BYTES;
+    const uint32_t stg_base = smem_base + STAGES * STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + STAGES * STAGE_BYTES + STG_TOTAL);
+    const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES + STG_TOTAL;
+    auto full_bar = [&](uint32_t s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](uint32_t s) { return bar_base + 8u * (STAGES + s); };
+    auto tmem_full_bar = [&](uint32_t b) { return bar_base + 8u * (2 * STAGES + b); };
+    auto tmem_empty_bar = [&](uint32_t b) { return bar_base + 8u * (2 * STAGES + 2 + b); };  // leader
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + NUM_BARS);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();  // 0 = leader
+    const uint32_t pair = blockIdx.x >> 1;
+    const uint32_t num_pairs = gridDim.x >> 1;
+
+    const uint32_t tiles_m = (p.m + BM - 1) / BM;
+    const uint32_t tiles_n = (p.n + BN - 1) / BN;
+    const uint32_t num_tiles = tiles_m * tiles_n;
+    const uint32_t num_kb = (p.k + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (uint32_t b = 0; b < 2; ++b) {
+            mbar_init(tmem_full_bar(b), 1);
+            mbar_init(tmem_empty_bar(b), 8);  // 4 epilogue warps of each CTA
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        tma_prefetch_desc(&tmap_a);
+        tma_prefetch_desc(&tmap_b);
+        tma_prefetch_desc(&tmap_c);
+    }
+    if (warp == 1) {
+        tmem_alloc_2cta<TMEM_COLS>(smem_u32(const_cast<uint32_t*>(tmem_slot)));
+        tmem_relinquish_2cta();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();  // both CTAs' barriers exist before anyone arrives remotely
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        uint32_t s = 0, ph = 0;
+        bool ok = true;
+        for (uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+            const int32_t m0 = (tile % tiles_m) * BM + rank * BM_CTA;
+            const int32_t n0 = (tile / tiles_m) * BN + rank * 128;
+            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                if (!mbar_wait_bounded_cluster(empty_bar(s), ph ^ 1u, abort_flag, p.status,
+                                               SITE_EMPTY, KERNEL_W8A8)) {
+                    ok = false;
+                    break;
+                }
+                if (elect_one()) {
+                    const uint32_t stage = smem_base + s * STAGE_BYTES;
+                    const int32_t k0 = kb * BK;
+                    const uint32_t leader_full = mapa_shared(full_bar(s), 0);
+                    if (rank == 0)
+                        mbar_expect_tx(full_bar(s), 2 * STAGE_BYTES);  // both CTAs' boxes
+                    tma_load_2d_pair(stage, &tmap_a, leader_full, k0, m0);
+                    tma_load_2d_pair(stage + A_BYTES, &tmap_b, leader_full, n0, k0);
+                }
+                __syncwarp();
+                if (++s == STAGES) {
+                    s = 0;
+                    ph ^= 1u;
+                }
+            }
+        }
+        if (!ok)
+            for (uint32_t spin = 0; spin < 2000; ++spin)
+                __nanosleep(100);
+    } else if (warp == 1 && rank == 1) {
+        // the peer CTA issues no MMAs: the leader's instruction drives both tensor cores
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ leader: MMA issuer
+        uint32_t s = 0, ph = 0, local_tile = 0;
+        bool ok = true;
+        for (uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs, ++local_tile) {
+            const uint32_t buf = local_tile & 1u;
+            const uint32_t acc_ph = (local_tile >> 1) & 1u;
+            if (!mbar_wait_bounded_cluster(tmem_empty_bar(buf), acc_ph ^ 1u, abort_flag, p.status,
+                                           SITE_TMEM_EMPTY, KERNEL_W8A8)) {
+                ok = false;
+                break;
+            }
+            tc_fence_after_sync();
+            const uint32_t d_tmem = tmem_base + buf * BN;
+            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                if (!mbar_wait_bounded_cluster(full_bar(s), ph, abort_flag, p.status, SITE_FULL,
+                                               KERNEL_W8A8)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t stage = smem_base + s * STAGE_BYTES;
+                // the same offsets address the operands in both CTAs' shared memory
+                const uint64_t a_desc = make_smem_desc_sw128(stage, 16, 1024);
+                const uint64_t b_desc = make_smem_desc_sw128(stage + A_BYTES, 16, 1024);
+                if (elect_one()) {
+#pragma unroll
+                    for (uint32_t kk = 0; kk < BK / UMMA_K; ++kk) {
+                        umma_i8_2cta(d_tmem, a_desc + (uint64_t)((kk * UMMA_K) >> 4),
+                                     b_desc + (uint64_t)((kk * UMMA_K * 128) >> 4), IDESC,
+                                     (kb | kk) != 0 ? 1u : 0u);
+                    }
+                    umma_commit_2cta(empty_bar(s), 3);  // frees the stage in both CTAs
+                    if (kb + 1 == num_kb)
+                        umma_commit_2cta(tmem_full_bar(buf), 3);
+                }
+                __syncwarp();
+                if (++s == STAGES) {
+                    s = 0;
+                    ph ^= 1u;
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..5)
+        const uint32_t quarter = warp & 3u;
+        const uint32_t ewarp = warp - 2;
+        const uint32_t leader_empty0 = mapa_shared(tmem_empty_bar(0), 0);
+        const uint32_t leader_empty1 = mapa_shared(tmem_empty_bar(1), 0);
+        uint32_t local_tile = 0;
+        for (uint32_t tile = pair; tile < num_tiles; tile += num_pairs, ++local_tile) {
+            const uint32_t buf = local_tile & 1u;
+            const uint32_t acc_ph = (local_tile >> 1) & 1u;
+            const uint32_t m0 = (tile % tiles_m) * BM + rank * BM_CTA;
+            const uint32_t n0 = (tile / tiles_m) * BN;
+            if (!mbar_wait_bounded_cluster(tmem_full_bar(buf), acc_ph, abort_flag, p.status,
+                                           SITE_TMEM_FULL, KERNEL_W8A8))
+                break;
+            tc_fence_after_sync();
+            const uint32_t row = m0 + quarter * 32 + lane;
+            float row_scale = 1.0f;
+            if (EPI == EPI_ROWCOL && row < p.m)
+                row_scale = __ldg(p.a_scale + row);
+            const uint32_t taddr = tmem_base + buf * BN + ((quarter * 32u) << 16);
+#pragma unroll 1
+            for (uint32_t c = 0; c < BN / 32; ++c) {
+                const uint32_t col0 = n0 + c * 32;
+                if (col0 >= p.n)
+                    break;  // warp-uniform
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(taddr + c * 32, r);
+                tmem_ld_wait();
+                if (EPI != EPI_S32) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        float f0 = __int2float_rn((int32_t)r[j + 0]);
+                        float f1 = __int2float_rn((int32_t)r[j + 1]);
+                        float f2 = __int2float_rn((int32_t)r[j + 2]);
+                        float f3 = __int2float_rn((int32_t)r[j + 3]);
+                        if (EPI == EPI_SCALAR) {
+                            f0 = __fmul_rn(f0, p.scale);
+                            f1 = __fmul_rn(f1, p.scale);
+                            f2 = __fmul_rn(f2, p.scale);
+                            f3 = __fmul_rn(f3, p.scale);
+                        } else {
+                            float4 ws = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (col0 + j < p.n)  // N % 16 == 0: whole vector in or out
+                                ws = __ldg(reinterpret_cast<const float4*>(p.w_scale + col0 + j));
+                            f0 = __fmul_rn(__fmul_rn(f0, row_scale), ws.x);
+                            f1 = __fmul_rn(__fmul_rn(f1, row_scale), ws.y);
+                            f2 = __fmul_rn(__fmul_rn(f2, row_scale), ws.z);
+                            f3 = __fmul_rn(__fmul_rn(f3, row_scale), ws.w);
+                        }
+                        r[j + 0] = __float_as_uint(f0);
+                        r[j + 1] = __float_as_uint(f1);
+                        r[j + 2] = __float_as_uint(f2);
+                        r[j + 3] = __float_as_uint(f3);
+                    }
+                }
+                if (lane == 0)
+                    tma_store_wait_read<1>();  // the buffer used two blocks ago has been read out
+                __syncwarp();
+                const uint32_t stg_off = (ewarp * 2 + (c & 1u)) * STG_BYTES;
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    *reinterpret_cast<uint4*>(stg_gen + stg_off + sw128_offset(lane, j)) =
+                        make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    tma_store_2d(&tmap_c, stg_base + stg_off, (int32_t)col0,
+                                 (int32_t)(m0 + quarter * 32));
+                    tma_store_commit();
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive_cluster(buf ? leader_empty1 : leader_empty0);
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    if (warp >= 2 && lane == 0)
+        tma_store_wait_all<0>();
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();  // neither CTA leaves while the other may still touch its barriers
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc_2cta<TMEM_COLS>(tmem_base);
+    }
+}
+
+}  // namespace w8a8x2
+
+bool w8a8_2cta_ok(uint32_t m, uint32_t n, uint32_t k)
+{
+    (void)n;
+    (void)k;
+    return m > 128;
+}
+
+cudaError_t launch_w8a8_gemm_2cta(const DeviceCtx& ctx, int epi, const int8_t* a, const int8_t* b,
+                                  void* out, float scale, const float* a_scale,
+                                  const float* w_scale, uint32_t m, uint32_t n, uint32_t k,
+                                  cudaStream_t stream)
+{
+    using namespace w8a8x2;
+    CUtensorMap tmap_a, tmap_b, tmap_c;
+    cudaError_t err = encode_tensor_map_2d(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, k, m, k,
+                                           BK, BM_CTA, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (err != cudaSuccess)
+        return err;
+    err = encode_tensor_map_2d(&tmap_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, n, k, n, 128, BK,
+                               CU_TENSOR_MAP_SWIZZLE_128B);
+    if (err != cudaSuccess)
+        return err;
+    err = encode_tensor_map_2d(&tmap_c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, out, n, m,
+                               (uint64_t)n * 4, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (err != cudaSuccess)
+        return err;
+    Params p;
+    p.a_scale = a_scale;
+    p.w_scale = w_scale;
+    p.scale = scale;
+    p.m = m;
+    p.n = n;
+    p.k = k;
+    p.status = ctx.status;
+    const uint32_t tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
+    const uint32_t max_pairs = (uint32_t)ctx.num_sms / 2;
+    const uint32_t pairs = tiles < max_pairs ? tiles : max_pairs;
+
+    static bool attr_set[3][64] = {};
+#define KAIO_LAUNCH_W8A8X2(E)                                                                     \
+    do {                                                                                          \
+        if (!attr_set[E][ctx.device]) {                                                           \
+            err = cudaFuncSetAttribute(w8a8_gemm_2cta_kernel<E>,                                  \
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);  \
+            if (err != cudaSuccess)                                                               \
+                return err;                                                                       \
+            attr_set[E][ctx.device] = true;                                                       \
+        }                                                                                         \
+        w8a8_gemm_2cta_kernel<E><<<pairs * 2, NUM_THREADS, SMEM_BYTES, stream>>>(tmap_a, tmap_b,  \
+                                                                                 tmap_c, p);      \
+    } while (0)
+    switch (epi) {
+    case EPI_SCALAR:
+        KAIO_LAUNCH_W8A8X2(EPI_SCALAR);
+        break;
+    case EPI_ROWCOL:
+        KAIO_LAUNCH_W8A8X2(EPI_ROWCOL);
+        break;
+    default:
+        KAIO_LAUNCH_W8A8X2(EPI_S32);
+        break;
+    }
+#undef KAIO_LAUNCH_W8A8X2
+    return cudaGetLastError();
+}
+
+}  // namespace kaio

@@ -48,7 +48,7 @@ def run_case(oracle, m, n, k, scale, seed):
 @pytest.mark.parametrize("m,n,k,scale,seed", SHAPES)
 def test_round_trip(oracle, m, n, k, scale, seed):
     variant = run_case(oracle, m, n, k, scale, seed)
-    expect = "w8a8_tcgen05" if n % 16 == 0 else "int8_generic"
+    expect = ("w8a8_tcgen05_2cta" if m > 128 else "w8a8_tcgen05") if n % 16 == 0 else "int8_generic"
     assert variant == expect
 
 
