@@ -9,6 +9,7 @@
 //   validate_attention_tc_dims  kaio-ops/src/attention_tc_kernel.rs:139-223
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 #include <string>
 
@@ -376,7 +377,10 @@ static int32_t run_int8(int epi, const int8_t* a, size_t a_len, const int8_t* b,
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool scales_aligned = epi != EPI_ROWCOL || ((uintptr_t)w_scale % 16 == 0);
     if (w8a8_fast_path_ok(a, b, c, m, n, k) && scales_aligned) {
-        if (w8a8_2cta_ok(m, n, k))
+        bool pair = w8a8_2cta_ok(m, n, k);
+        if (const char* e = getenv("KAIO_B200_PAIR"))  // tuning aid: 0/1 forces single CTA / pair
+            pair = (e[0] == '1');
+        if (pair)
             return finish(launch_w8a8_gemm_2cta(*ctx, epi, a, b, c, scale, a_scale, w_scale, m, n,
                                                 k, s),
                           "matmul_int8", "w8a8_tcgen05_2cta");

@@ -13,41 +13,53 @@
 //      traffic per weight; for the prefill shapes this is a few percent of the GEMM.
 //   2. f16_gemm_kernel: one persistent launch over all (up to three) weight matrices -- the
 //      tile scheduler walks (projection, m-tile, n-tile), so the fused QKV ops stay one GEMM
-//      launch with three outputs.  Per CTA: warp 0 TMA producer (x tile [128 rows][64 k] and
-//      weight tile [64 k][256 n], 128-byte swizzle, 4-stage ring), warp 1 issues
-//      tcgen05.mma kind::f16 M128 N256 K16 (x K-major, weights MN-major straight from the
-//      row-major [K,N] layout), f32 accumulators double-buffered in tensor memory, warps 2-5
-//      epilogue (post-scale, f16/f32 narrow, predicated stores).
+//      launch with three outputs.  For M > 128 the workers are CTA pairs (tcgen05 cta_group::2,
+//      256x256 tiles: each CTA stages its 128 rows of x and its 128 weight columns, plain TMA
+//      loads credited to the leader's barrier, multicast commit); for smaller M single CTAs with
+//      128x256 tiles.  Per CTA: warp 0 TMA producer (128-byte swizzle ring), warp 1 issues
+//      tcgen05.mma kind::f16 K16 (x K-major, weights MN-major straight from the row-major [K,N]
+//      layout), f32 accumulators double-buffered in tensor memory, warps 2-5 epilogue
+//      (post-scale, f16/f32 narrow, swizzled staging, TMA bulk stores clipped at the edges).
 //
 // Shapes: N % 8 == 0 and 16-byte aligned bases (TMA).  Everything else takes the generic kernel.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "kernels.h"
 
 namespace kaio {
 namespace f16g {
 
-constexpr int BM = 128;
+constexpr int BM_CTA = 128;  // rows per CTA
 constexpr int BN = 256;
-constexpr int BK = 64;     // f16 elements per stage along K (128 bytes of x per row)
+constexpr int BK = 64;       // f16 elements per stage along K (128 bytes of x per row)
 constexpr int UMMA_K = 16;
-constexpr int STAGES = 4;
-constexpr int A_BYTES = BM * 128;           // 16 KiB: [128 rows][64 k f16]
-constexpr int B_CHUNK_BYTES = BK * 128;     // 8 KiB: [64 k][64 n f16]
-constexpr int B_CHUNKS = BN * 2 / 128;      // 4 chunks of 64 columns
-constexpr int B_BYTES = B_CHUNKS * B_CHUNK_BYTES;  // 32 KiB
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;     // 48 KiB
+constexpr int A_BYTES = BM_CTA * 128;    // 16 KiB: [128 rows][64 k f16]
+constexpr int B_CHUNK_BYTES = BK * 128;  // 8 KiB: [64 k][64 n f16]
+constexpr int STG_BYTES = 32 * 128;      // one staged output block: 32 rows x 128 B
+constexpr int STG_TOTAL = 4 * 2 * STG_BYTES;
 constexpr int TMEM_COLS = 512;
 constexpr int NUM_THREADS = 192;
-constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 256;
 constexpr int MAX_PROBS = 3;
 
-constexpr uint32_t IDESC = make_idesc(/*d=f32*/ 1, /*a=f16*/ 0, /*b=f16*/ 0, /*a K-major*/ 0,
-                                      /*b MN-major*/ 1, BM, BN);
+// PAIR = false: one CTA per 128x256 tile, 4 weight chunks per stage, 4 stages of 48 KiB.
+// PAIR = true : a CTA pair per 256x256 tile (tcgen05 cta_group::2); each CTA stages its 128
+//               rows of x and ITS 128 weight columns (2 chunks), 6 stages of 32 KiB.
+template <bool PAIR>
+struct Cfg {
+    static constexpr int B_CHUNKS = PAIR ? 2 : 4;
+    static constexpr int STAGES = PAIR ? 6 : 4;
+    static constexpr int STAGE_BYTES = A_BYTES + B_CHUNKS * B_CHUNK_BYTES;
+    static constexpr int BM = PAIR ? 256 : 128;
+    static constexpr int NUM_BARS = 2 * STAGES + 4;
+    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + STG_TOTAL + NUM_BARS * 8 + 64;
+    static constexpr uint32_t IDESC = make_idesc(/*d=f32*/ 1, /*a=f16*/ 0, /*b=f16*/ 0,
+                                                 /*a K-major*/ 0, /*b MN-major*/ 1, BM, BN);
+};
 
 enum : uint32_t { SITE_EMPTY = 1, SITE_FULL = 2, SITE_TMEM_EMPTY = 3, SITE_TMEM_FULL = 4 };
 
 struct Problem {
-    void* out;               // f32 or f16 [M,N]
     const float* col_scale;  // per-column post-scale or nullptr
     float scale;             // scalar post-scale
 };
@@ -56,7 +68,6 @@ struct Params {
     Problem probs[MAX_PROBS];
     uint32_t num_probs;
     uint32_t m, n, k;
-    int out_f16;
     int post_scale;
     uint32_t* status;
 };
@@ -64,116 +75,146 @@ struct Params {
 struct TensorMaps {
     CUtensorMap x;
     CUtensorMap w[MAX_PROBS];
+    CUtensorMap out[MAX_PROBS];
 };
 
+template <bool PAIR, bool OUT_F16>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 f16_gemm_kernel(const __grid_constant__ TensorMaps maps, const Params p)
 {
+    using C = Cfg<PAIR>;
+    constexpr int STAGES = C::STAGES;
+    constexpr int STAGE_BYTES = C::STAGE_BYTES;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + STAGES * STAGE_BYTES);
-    const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+    uint8_t* stg_gen = smem_gen + STAGES * STAGE_BYTES;
+    const uint32_t stg_base = smem_base + STAGES * STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + STAGES * STAGE_BYTES + STG_TOTAL);
+    const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES + STG_TOTAL;
     auto full_bar = [&](uint32_t s) { return bar_base + 8u * s; };
     auto empty_bar = [&](uint32_t s) { return bar_base + 8u * (STAGES + s); };
     auto tmem_full_bar = [&](uint32_t b) { return bar_base + 8u * (2 * STAGES + b); };
     auto tmem_empty_bar = [&](uint32_t b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * STAGES + 4);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + C::NUM_BARS);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;  // 0 = leader
+    const uint32_t worker = PAIR ? (blockIdx.x >> 1) : blockIdx.x;
+    const uint32_t num_workers = PAIR ? (gridDim.x >> 1) : gridDim.x;
 
-    const uint32_t tiles_m = (p.m + BM - 1) / BM;
+    const uint32_t tiles_m = (p.m + C::BM - 1) / C::BM;
     const uint32_t tiles_n = (p.n + BN - 1) / BN;
     const uint32_t tiles_per_prob = tiles_m * tiles_n;
     const uint32_t num_tiles = tiles_per_prob * p.num_probs;
     const uint32_t num_kb = (p.k + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < STAGES; ++s) {
+        for (uint32_t s = 0; s < (uint32_t)STAGES; ++s) {
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
         }
         for (uint32_t b = 0; b < 2; ++b) {
             mbar_init(tmem_full_bar(b), 1);
-            mbar_init(tmem_empty_bar(b), 4);
+            mbar_init(tmem_empty_bar(b), PAIR ? 8 : 4);  // epilogue warps (of both CTAs)
         }
         *abort_flag = 0;
         fence_barrier_init();
         tma_prefetch_desc(&maps.x);
-        for (uint32_t i = 0; i < p.num_probs; ++i)
+        for (uint32_t i = 0; i < p.num_probs; ++i) {
             tma_prefetch_desc(&maps.w[i]);
+            tma_prefetch_desc(&maps.out[i]);
+        }
     }
     if (warp == 1) {
-        tmem_alloc<TMEM_COLS>(smem_u32(const_cast<uint32_t*>(tmem_slot)));
-        tmem_relinquish();
+        if (PAIR) {
+            tmem_alloc_2cta<TMEM_COLS>(smem_u32(const_cast<uint32_t*>(tmem_slot)));
+            tmem_relinquish_2cta();
+        } else {
+            tmem_alloc<TMEM_COLS>(smem_u32(const_cast<uint32_t*>(tmem_slot)));
+            tmem_relinquish();
+        }
     }
     tc_fence_before_sync();
     __syncthreads();
+    if (PAIR)
+        cluster_sync_all();  // both CTAs' barriers exist before anyone signals remotely
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
-    // tile -> (projection, m-tile, n-tile); m fastest so CTAs running side by side share a
+    // tile -> (projection, m-tile, n-tile); m fastest so workers running side by side share a
     // weight panel in L2
     auto decode_tile = [&](uint32_t tile, uint32_t& prob, uint32_t& m0, uint32_t& n0) {
         prob = tile / tiles_per_prob;
         const uint32_t r = tile - prob * tiles_per_prob;
-        m0 = (r % tiles_m) * BM;
+        m0 = (r % tiles_m) * C::BM + rank * BM_CTA;
         n0 = (r / tiles_m) * BN;
     };
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer (converged warp)
         uint32_t s = 0, ph = 0;
-        for (uint32_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+        bool ok = true;
+        for (uint32_t tile = worker; ok && tile < num_tiles; tile += num_workers) {
             uint32_t prob, m0, n0;
             decode_tile(tile, prob, m0, n0);
             const CUtensorMap* wmap = &maps.w[prob];
-            bool ok = true;
+            const uint32_t ncol0 = n0 + (PAIR ? rank * 128 : 0);  // this CTA's weight columns
             for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                if (!mbar_wait_bounded(empty_bar(s), ph ^ 1u, abort_flag, p.status, SITE_EMPTY,
-                                       KERNEL_DQ_GEMM)) {
+                if (!mbar_wait_bounded_cluster(empty_bar(s), ph ^ 1u, abort_flag, p.status,
+                                               SITE_EMPTY, KERNEL_DQ_GEMM)) {
                     ok = false;
                     break;
                 }
                 if (elect_one()) {
                     const uint32_t stage = smem_base + s * STAGE_BYTES;
                     const int32_t k0 = kb * BK;
-                    mbar_expect_tx(full_bar(s), STAGE_BYTES);
-                    tma_load_2d(stage, &maps.x, full_bar(s), k0, (int32_t)m0);
+                    if (PAIR) {
+                        // both CTAs credit their bytes to the leader's barrier
+                        const uint32_t leader_full = mapa_shared(full_bar(s), 0);
+                        if (rank == 0)
+                            mbar_expect_tx(full_bar(s), 2 * STAGE_BYTES);
+                        tma_load_2d_pair(stage, &maps.x, leader_full, k0, (int32_t)m0);
 #pragma unroll
-                    for (int c = 0; c < B_CHUNKS; ++c)
-                        tma_load_2d(stage + A_BYTES + c * B_CHUNK_BYTES, wmap, full_bar(s),
-                                    (int32_t)n0 + c * 64, k0);
+                        for (int c = 0; c < C::B_CHUNKS; ++c)
+                            tma_load_2d_pair(stage + A_BYTES + c * B_CHUNK_BYTES, wmap, leader_full,
+                                             (int32_t)ncol0 + c * 64, k0);
+                    } else {
+                        mbar_expect_tx(full_bar(s), STAGE_BYTES);
+                        tma_load_2d(stage, &maps.x, full_bar(s), k0, (int32_t)m0);
+#pragma unroll
+                        for (int c = 0; c < C::B_CHUNKS; ++c)
+                            tma_load_2d(stage + A_BYTES + c * B_CHUNK_BYTES, wmap, full_bar(s),
+                                        (int32_t)ncol0 + c * 64, k0);
+                    }
                 }
                 __syncwarp();
-                if (++s == STAGES) {
+                if (++s == (uint32_t)STAGES) {
                     s = 0;
                     ph ^= 1u;
                 }
             }
-            if (!ok)
-                break;
         }
         if (*abort_flag)
             for (uint32_t spin = 0; spin < 2000; ++spin)
                 __nanosleep(100);
-    } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer (converged warp)
+    } else if (warp == 1 && rank == 0) {
+        // ------------------------------------------------------------ MMA issuer (leader, converged warp)
         uint32_t s = 0, ph = 0, local_tile = 0;
-        for (uint32_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local_tile) {
+        bool ok = true;
+        for (uint32_t tile = worker; ok && tile < num_tiles; tile += num_workers, ++local_tile) {
             const uint32_t buf = local_tile & 1u;
             const uint32_t acc_ph = (local_tile >> 1) & 1u;
-            if (!mbar_wait_bounded(tmem_empty_bar(buf), acc_ph ^ 1u, abort_flag, p.status,
-                                   SITE_TMEM_EMPTY, KERNEL_DQ_GEMM))
+            if (!mbar_wait_bounded_cluster(tmem_empty_bar(buf), acc_ph ^ 1u, abort_flag, p.status,
+                                           SITE_TMEM_EMPTY, KERNEL_DQ_GEMM))
                 break;
             tc_fence_after_sync();
             const uint32_t d_tmem = tmem_base + buf * BN;
-            bool ok = true;
             for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                if (!mbar_wait_bounded(full_bar(s), ph, abort_flag, p.status, SITE_FULL,
-                                       KERNEL_DQ_GEMM)) {
+                if (!mbar_wait_bounded_cluster(full_bar(s), ph, abort_flag, p.status, SITE_FULL,
+                                               KERNEL_DQ_GEMM)) {
                     ok = false;
                     break;
                 }
@@ -182,117 +223,142 @@ f16_gemm_kernel(const __grid_constant__ TensorMaps maps, const Params p)
                 // x: K-major, 8-row groups 1024 B apart.  weights: MN-major, 8-k groups 1024 B
                 // apart, the 64-column chunks B_CHUNK_BYTES apart.
                 const uint64_t a_desc = make_smem_desc_sw128(stage, 16, 1024);
-                const uint64_t b_desc =
-                    make_smem_desc_sw128(stage + A_BYTES, B_CHUNK_BYTES, 1024);
+                const uint64_t b_desc = make_smem_desc_sw128(stage + A_BYTES, B_CHUNK_BYTES, 1024);
                 if (elect_one()) {
 #pragma unroll
                     for (uint32_t kk = 0; kk < BK / UMMA_K; ++kk) {
                         // x advances 32 bytes inside its swizzled row, weights 16 k-rows of 128 B
-                        umma_f16(d_tmem, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 128),
-                                 IDESC, (kb | kk) != 0 ? 1u : 0u);
+                        if (PAIR)
+                            umma_f16_2cta(d_tmem, a_desc + (uint64_t)(kk * 2),
+                                          b_desc + (uint64_t)(kk * 128), C::IDESC,
+                                          (kb | kk) != 0 ? 1u : 0u);
+                        else
+                            umma_f16(d_tmem, a_desc + (uint64_t)(kk * 2),
+                                     b_desc + (uint64_t)(kk * 128), C::IDESC,
+                                     (kb | kk) != 0 ? 1u : 0u);
                     }
-                    umma_commit(empty_bar(s));
-                    if (kb + 1 == num_kb)
-                        umma_commit(tmem_full_bar(buf));
+                    if (PAIR) {
+                        umma_commit_2cta(empty_bar(s), 3);  // frees the stage in both CTAs
+                        if (kb + 1 == num_kb)
+                            umma_commit_2cta(tmem_full_bar(buf), 3);
+                    } else {
+                        umma_commit(empty_bar(s));
+                        if (kb + 1 == num_kb)
+                            umma_commit(tmem_full_bar(buf));
+                    }
                 }
                 __syncwarp();
-                if (++s == STAGES) {
+                if (++s == (uint32_t)STAGES) {
                     s = 0;
                     ph ^= 1u;
                 }
             }
-            if (!ok)
-                break;
         }
-    } else {
+    } else if (warp >= 2) {
         // ------------------------------------------------------------ epilogue (warps 2..5)
         const uint32_t quarter = warp & 3u;
+        const uint32_t ewarp = warp - 2;
+        const uint32_t leader_empty0 = PAIR ? mapa_shared(tmem_empty_bar(0), 0) : tmem_empty_bar(0);
+        const uint32_t leader_empty1 = PAIR ? mapa_shared(tmem_empty_bar(1), 0) : tmem_empty_bar(1);
+        constexpr uint32_t COLS_PER_BLOCK = OUT_F16 ? 64 : 32;  // 128 bytes of output per row
         uint32_t local_tile = 0;
-        for (uint32_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local_tile) {
+        for (uint32_t tile = worker; tile < num_tiles; tile += num_workers, ++local_tile) {
             const uint32_t buf = local_tile & 1u;
             const uint32_t acc_ph = (local_tile >> 1) & 1u;
             uint32_t prob, m0, n0;
             decode_tile(tile, prob, m0, n0);
             const Problem& pr = p.probs[prob];
-            if (!mbar_wait_bounded(tmem_full_bar(buf), acc_ph, abort_flag, p.status, SITE_TMEM_FULL,
-                                   KERNEL_DQ_GEMM))
+            const CUtensorMap* omap = &maps.out[prob];
+            if (!mbar_wait_bounded_cluster(tmem_full_bar(buf), acc_ph, abort_flag, p.status,
+                                           SITE_TMEM_FULL, KERNEL_DQ_GEMM))
                 break;
             tc_fence_after_sync();
-            const uint32_t row = m0 + quarter * 32 + lane;
-            const bool row_ok = row < p.m;
             const uint32_t taddr = tmem_base + buf * BN + ((quarter * 32u) << 16);
 #pragma unroll 1
-            for (uint32_t c = 0; c < BN / 32; ++c) {
-                const uint32_t col0 = n0 + c * 32;
+            for (uint32_t c = 0; c < BN / COLS_PER_BLOCK; ++c) {
+                const uint32_t col0 = n0 + c * COLS_PER_BLOCK;
                 if (col0 >= p.n)
                     break;  // warp-uniform
-                uint32_t r[32];
-                tmem_ld_32x32b_x32(taddr + c * 32, r);
-                tmem_ld_wait();
-                if (!row_ok)
-                    continue;
-                float v[32];
+                uint32_t stg[32];  // one 128-byte output row
 #pragma unroll
-                for (int j = 0; j < 32; ++j)
-                    v[j] = __uint_as_float(r[j]);
-                if (p.post_scale) {
-                    if (pr.col_scale != nullptr) {
+                for (uint32_t half = 0; half < COLS_PER_BLOCK / 32; ++half) {
+                    uint32_t r[32];
+                    tmem_ld_32x32b_x32(taddr + c * COLS_PER_BLOCK + half * 32, r);
+                    tmem_ld_wait();
+                    if (p.post_scale) {
+                        const uint32_t cbase = col0 + half * 32;
+                        if (pr.col_scale != nullptr) {
 #pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            if (col0 + j < p.n) {  // N % 8 == 0: whole vector in or out
-                                const float4 cs =
-                                    __ldg(reinterpret_cast<const float4*>(pr.col_scale + col0 + j));
-                                v[j] = __fmul_rn(v[j], cs.x);
-                                v[j + 1] = __fmul_rn(v[j + 1], cs.y);
-                                v[j + 2] = __fmul_rn(v[j + 2], cs.z);
-                                v[j + 3] = __fmul_rn(v[j + 3], cs.w);
+                            for (int j = 0; j < 32; j += 4) {
+                                float4 cs = make_float4(0.f, 0.f, 0.f, 0.f);
+                                if (cbase + j < p.n)  // N % 8 == 0 and 16-byte aligned: whole vector
+                                    cs = __ldg(reinterpret_cast<const float4*>(pr.col_scale + cbase + j));
+                                r[j] = __float_as_uint(__fmul_rn(__uint_as_float(r[j]), cs.x));
+                                r[j + 1] = __float_as_uint(__fmul_rn(__uint_as_float(r[j + 1]), cs.y));
+                                r[j + 2] = __float_as_uint(__fmul_rn(__uint_as_float(r[j + 2]), cs.z));
+                                r[j + 3] = __float_as_uint(__fmul_rn(__uint_as_float(r[j + 3]), cs.w));
                             }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                r[j] = __float_as_uint(__fmul_rn(__uint_as_float(r[j]), pr.scale));
+                        }
+                    }
+                    if (OUT_F16) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 2) {
+                            const __half2 h = __floats2half2_rn(__uint_as_float(r[j]),
+                                                                __uint_as_float(r[j + 1]));
+                            stg[half * 16 + (j >> 1)] = *reinterpret_cast<const uint32_t*>(&h);
                         }
                     } else {
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
-                            v[j] = __fmul_rn(v[j], pr.scale);
+                            stg[j] = r[j];
                     }
                 }
-                if (p.out_f16) {
-                    __half* dst = reinterpret_cast<__half*>(pr.out) + (size_t)row * p.n + col0;
+                // stage the [32 rows][128 B] block (128-byte swizzle) and bulk-store it; the
+                // buffer used two blocks ago must have been read out first
+                if (lane == 0)
+                    tma_store_wait_read<1>();
+                __syncwarp();
+                const uint32_t stg_off = (ewarp * 2 + (c & 1u)) * STG_BYTES;
 #pragma unroll
-                    for (int j = 0; j < 32; j += 8) {
-                        if (col0 + j < p.n) {
-                            uint4 pk;
-                            __half2 h0 = __floats2half2_rn(v[j], v[j + 1]);
-                            __half2 h1 = __floats2half2_rn(v[j + 2], v[j + 3]);
-                            __half2 h2 = __floats2half2_rn(v[j + 4], v[j + 5]);
-                            __half2 h3 = __floats2half2_rn(v[j + 6], v[j + 7]);
-                            pk.x = *reinterpret_cast<uint32_t*>(&h0);
-                            pk.y = *reinterpret_cast<uint32_t*>(&h1);
-                            pk.z = *reinterpret_cast<uint32_t*>(&h2);
-                            pk.w = *reinterpret_cast<uint32_t*>(&h3);
-                            *reinterpret_cast<uint4*>(dst + j) = pk;
-                        }
-                    }
-                } else {
-                    float* dst = reinterpret_cast<float*>(pr.out) + (size_t)row * p.n + col0;
-#pragma unroll
-                    for (int j = 0; j < 32; j += 4)
-                        if (col0 + j < p.n)
-                            *reinterpret_cast<float4*>(dst + j) =
-                                make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                for (int j = 0; j < 8; ++j)
+                    *reinterpret_cast<uint4*>(stg_gen + stg_off + sw128_offset(lane, j)) =
+                        make_uint4(stg[4 * j], stg[4 * j + 1], stg[4 * j + 2], stg[4 * j + 3]);
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    tma_store_2d(omap, stg_base + stg_off, (int32_t)col0,
+                                 (int32_t)(m0 + quarter * 32));
+                    tma_store_commit();
                 }
             }
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0)
-                mbar_arrive(tmem_empty_bar(buf));
+            if (lane == 0) {
+                if (PAIR)
+                    mbar_arrive_cluster(buf ? leader_empty1 : leader_empty0);
+                else
+                    mbar_arrive(buf ? leader_empty1 : leader_empty0);
+            }
         }
     }
 
     // ---------------------------------------------------------------- teardown
+    if (warp >= 2 && lane == 0)
+        tma_store_wait_all<0>();  // staged blocks must be out before shared memory goes away
     tc_fence_before_sync();
     __syncthreads();
+    if (PAIR)
+        cluster_sync_all();  // neither CTA leaves while the other may still signal it
     if (warp == 1) {
         tc_fence_after_sync();
-        tmem_dealloc<TMEM_COLS>(tmem_base);
+        if (PAIR)
+            tmem_dealloc_2cta<TMEM_COLS>(tmem_base);
+        else
+            tmem_dealloc<TMEM_COLS>(tmem_base);
     }
 }
 
@@ -386,6 +452,40 @@ size_t dq_gemm_workspace_bytes(int num_probs, uint32_t n, uint32_t k)
     return (size_t)num_probs * (((size_t)k * n * sizeof(__half) + 255) & ~(size_t)255);
 }
 
+template <bool PAIR, bool OUT_F16>
+static cudaError_t launch_f16_gemm(const DeviceCtx& ctx, const f16g::TensorMaps& maps,
+                                   const f16g::Params& p, cudaStream_t stream)
+{
+    using namespace f16g;
+    using C = Cfg<PAIR>;
+    static bool attr_set[64] = {};
+    cudaError_t err;
+    if (!attr_set[ctx.device]) {
+        err = cudaFuncSetAttribute(f16_gemm_kernel<PAIR, OUT_F16>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        if (err != cudaSuccess)
+            return err;
+        attr_set[ctx.device] = true;
+    }
+    const uint32_t tiles =
+        ((p.m + C::BM - 1) / C::BM) * ((p.n + BN - 1) / BN) * p.num_probs;
+    const uint32_t max_workers = PAIR ? (uint32_t)ctx.num_sms / 2 : (uint32_t)ctx.num_sms;
+    const uint32_t workers = tiles < max_workers ? tiles : max_workers;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(PAIR ? workers * 2 : workers);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = PAIR ? 2 : 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, f16_gemm_kernel<PAIR, OUT_F16>, maps, p);
+}
+
 cudaError_t launch_dq_gemm(const DeviceCtx& ctx, int wfmt, const __half* x, const DqProblem* probs,
                            int num_probs, bool out_f16, bool post_scale, uint32_t m, uint32_t n,
                            uint32_t k, void* dq_workspace, cudaStream_t stream)
@@ -410,9 +510,13 @@ cudaError_t launch_dq_gemm(const DeviceCtx& ctx, int wfmt, const __half* x, cons
     if (err != cudaSuccess)
         return err;
 
+    // KAIO_B200_PAIR=0/1 forces single-CTA / CTA-pair tiles (tuning aid); default: pairs for M > 128
+    bool pair = m > 128;
+    if (const char* e = getenv("KAIO_B200_PAIR"))
+        pair = (e[0] == '1');
     TensorMaps maps;
     err = encode_tensor_map_2d(&maps.x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x, k, m,
-                               (uint64_t)k * 2, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
+                               (uint64_t)k * 2, BK, BM_CTA, CU_TENSOR_MAP_SWIZZLE_128B);
     if (err != cudaSuccess)
         return err;
     for (int i = 0; i < MAX_PROBS; ++i) {
@@ -421,10 +525,19 @@ cudaError_t launch_dq_gemm(const DeviceCtx& ctx, int wfmt, const __half* x, cons
                                    (uint64_t)n * 2, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B);
         if (err != cudaSuccess)
             return err;
+        if (out_f16)
+            err = encode_tensor_map_2d(&maps.out[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                                       probs[j].out, n, m, (uint64_t)n * 2, 64, 32,
+                                       CU_TENSOR_MAP_SWIZZLE_128B);
+        else
+            err = encode_tensor_map_2d(&maps.out[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4,
+                                       probs[j].out, n, m, (uint64_t)n * 4, 32, 32,
+                                       CU_TENSOR_MAP_SWIZZLE_128B);
+        if (err != cudaSuccess)
+            return err;
     }
     Params p = {};
     for (int i = 0; i < num_probs; ++i) {
-        p.probs[i].out = probs[i].out;
         p.probs[i].col_scale = probs[i].col_scale;
         p.probs[i].scale = probs[i].scale;
     }
@@ -432,21 +545,13 @@ cudaError_t launch_dq_gemm(const DeviceCtx& ctx, int wfmt, const __half* x, cons
     p.m = m;
     p.n = n;
     p.k = k;
-    p.out_f16 = out_f16 ? 1 : 0;
     p.post_scale = post_scale ? 1 : 0;
     p.status = ctx.status;
-    const uint32_t tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN) * (uint32_t)num_probs;
-    const uint32_t grid = tiles < (uint32_t)ctx.num_sms ? tiles : (uint32_t)ctx.num_sms;
-    static bool attr_set[64] = {};
-    if (!attr_set[ctx.device]) {
-        err = cudaFuncSetAttribute(f16_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   SMEM_BYTES);
-        if (err != cudaSuccess)
-            return err;
-        attr_set[ctx.device] = true;
-    }
-    f16_gemm_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(maps, p);
-    return cudaGetLastError();
+    if (pair)
+        return out_f16 ? launch_f16_gemm<true, true>(ctx, maps, p, stream)
+                       : launch_f16_gemm<true, false>(ctx, maps, p, stream);
+    return out_f16 ? launch_f16_gemm<false, true>(ctx, maps, p, stream)
+                   : launch_f16_gemm<false, false>(ctx, maps, p, stream);
 }
 
 }  // namespace kaio
