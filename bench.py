@@ -25,7 +25,6 @@ from __future__ import annotations
 import argparse
 import json
 import os
-import subprocess
 import sys
 import threading
 import time
@@ -61,61 +60,67 @@ def load_traffic():
 
 
 class ClockSampler:
-    """Samples SM clock / throttle reasons with nvidia-smi while the timed region runs."""
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clock, power and throttle reasons through NVML (read-only queries) every few
+    milliseconds while the timed region runs."""
+    REASONS = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20,
+               "hw_thermal_slowdown": 0x40, "hw_power_brake_slowdown": 0x80}
 
     def __init__(self, gpu_index: int):
-        self.gpu_index, self.proc, self.lines = gpu_index, None, []
+        self.gpu_index, self.samples, self.stop_flag, self.thread = gpu_index, [], False, None
+        self.handle, self.err = None, None
+        try:
+            import pynvml
+            self.nvml = pynvml
+            pynvml.nvmlInit()
+            # NVML enumerates physical GPUs; honour CUDA_VISIBLE_DEVICES when it lists indices
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+            phys = gpu_index
+            if vis and all(v.strip().isdigit() for v in vis.split(",")):
+                ids = [int(v) for v in vis.split(",")]
+                if gpu_index < len(ids):
+                    phys = ids[gpu_index]
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.sm_max = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        except Exception as exc:  # NVML missing: report it instead of a number
+            self.err = repr(exc)
+
+    def _loop(self):
+        n = self.nvml
+        while not self.stop_flag:
+            try:
+                sm = n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)
+                pw = n.nvmlDeviceGetPowerUsage(self.handle) / 1000.0
+                rs = n.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+                self.samples.append((float(sm), pw, int(rs)))
+            except Exception as exc:
+                self.err = repr(exc)
+                return
+            time.sleep(0.002)
 
     def start(self):
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-i", str(self.gpu_index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
-
-    def _read(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
+        if self.handle is None:
+            return
+        self.thread = threading.Thread(target=self._loop, daemon=True)
+        self.thread.start()
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, reasons, mx, pw = [], set(), None, []
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
-            parts = [x.strip() for x in line.split(",")]
-            if len(parts) < 9:
-                continue
-            try:
-                sm.append(float(parts[1]))
-                mx = float(parts[2])
-                pw.append(float(parts[3]))
-            except ValueError:
-                continue
-            for name, val in zip(names, parts[5:9]):
-                if val.lower().startswith("active"):
+        if self.thread is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [f"NVML unavailable: {self.err}"]}
+        self.stop_flag = True
+        self.thread.join(timeout=2)
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.sm_max, "reasons": [f"no samples: {self.err}"]}
+        reasons = set()
+        for _, _, rs in self.samples:
+            for name, bit in self.REASONS.items():
+                if rs & bit:
                     reasons.add(name)
-        # keep samples taken under load (top half of power draw) for the median clock
-        if sm:
-            order = sorted(range(len(sm)), key=lambda i: pw[i])
-            loaded = [sm[i] for i in order[len(order) // 2:]]
-            loaded.sort()
-            med = loaded[len(loaded) // 2]
-        else:
-            med = None
-        return {"sm_mhz": med, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm),
-                "power_w_max": max(pw) if pw else None}
+        # median clock over the samples taken under load (upper half of the power readings)
+        order = sorted(self.samples, key=lambda t: t[1])
+        loaded = sorted(t[0] for t in order[len(order) // 2:])
+        return {"sm_mhz": loaded[len(loaded) // 2], "sm_max_mhz": self.sm_max, "reasons": sorted(reasons),
+                "samples": len(self.samples), "power_w_max": max(t[1] for t in self.samples),
+                "source": "NVML, 2 ms period, during the timed loop"}
 
 
 # ------------------------------------------------------------------------------ reference arm
@@ -174,7 +179,7 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="kaio_b200", choices=["kaio_b200", "reference"])
     ap.add_argument("--decode-only", action="store_true",
