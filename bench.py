@@ -487,8 +487,10 @@ def bench_qkv_attention(torch, ops, dev, peaks):
 def bench_ffn70b(torch, dist, ops, sharding, dev, rank, world):
     """Config 5: Llama-70B-shape W4A16 FFN GEMMs, N-sharded over the ranks, f16 output all-gathered
     to [M, N] on every rank.  Times are CUDA events, max over ranks.  Reported: the GEMM alone, the
-    GEMM followed by the gather, and the pipelined form (the shard is computed in column panels and
-    panel i is gathered on a second stream while panel i+1 is computed)."""
+    GEMM followed by the NCCL gather, the pipelined form (the shard is computed in column panels and
+    panel i is gathered on a second stream while panel i+1 is computed), and the fused form (one
+    kernel whose epilogue stores each tile into every rank's buffer over peer memory, followed by
+    a symmetric-memory barrier)."""
     res = {}
     g = torch.Generator(device="cuda")
     comm_stream = torch.cuda.Stream()
@@ -514,20 +516,26 @@ def bench_ffn70b(torch, dist, ops, sharding, dev, rank, world):
             iters = 20 if mm <= 256 else 5
             t_gemm = _time_ms(torch, gemm, iters)
             t_all = _time_ms(torch, both, iters) if world > 1 else t_gemm
-            t_pipe = t_all
+            t_pipe = t_fused = t_all
             if world > 1 and mm >= 256:
                 pipe = sharding.PanelPipeline(ops, dev, a, w, sc, mm, n, k, world, rank, comm_stream, panels=4)
                 t_pipe = _time_ms(torch, pipe.run, iters)
                 del pipe
-            t = torch.tensor([t_gemm, t_all, t_pipe], dtype=torch.float64, device="cuda")
+            if world > 1:
+                # one kernel per rank: the epilogue stores into every rank's buffer (peer memory)
+                fused = sharding.FusedGatherGemm(ops, dev, mm, n, k, world, rank)
+                t_fused = _time_ms(torch, lambda: fused.run(a, w, sc), iters)
+                del fused
+            t = torch.tensor([t_gemm, t_all, t_pipe, t_fused], dtype=torch.float64, device="cuda")
             if world > 1:
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            t_gemm, t_all, t_pipe = float(t[0]), float(t[1]), float(t[2])
-            best = min(t_all, t_pipe)
+            t_gemm, t_all, t_pipe, t_fused = float(t[0]), float(t[1]), float(t[2]), float(t[3])
+            best = min(t_all, t_pipe, t_fused)
             flops = 2 * mm * n * k
             nbytes = k * n // 2 + (k // 128) * n * 2 + 2 * mm * k + 2 * mm * n
             res[f"k{k}_n{n}_m{mm}"] = {
                 "ms_gemm": t_gemm, "ms_gemm_plus_gather": t_all, "ms_pipelined": t_pipe,
+                "ms_fused_peer_store": t_fused,
                 "tflops": flops / best / 1e9, "weight_stream_gbs": nbytes / best / 1e6,
                 "variant": ops.last_variant()}
             del a, c, gather

@@ -98,6 +98,22 @@ int32_t kaio_b200_matmul_int4_noalloc(const kaio_f16* a, size_t a_len, const uin
                                       float* c, size_t c_len, uint32_t m, uint32_t n, uint32_t k,
                                       uint32_t group_size, void* stream);
 
+/* Extension (no reference counterpart; KAIO is single-device): column-parallel W4A16 GEMM fused
+ * with the all-gather of its output.  The caller is rank `rank` of `world` (<= 8) processes, one per
+ * GPU of a node; it passes its shard of the weights (columns [rank*N/world, (rank+1)*N/world): a
+ * contiguous slice of the packed buffer, and the matching [K/128, N/world] scales) and `out_ptrs`, a
+ * HOST array of `world` device pointers: out_ptrs[r] is rank r's f16 [m, n_total] output buffer as
+ * mapped in THIS process (peer memory for r != rank, e.g. from torch symmetric memory or CUDA IPC).
+ * The kernel's epilogue stores every output block straight into all `world` buffers (TMA bulk
+ * stores / plain stores over NVLink), so the transfer overlaps the GEMM tile by tile; no NCCL call
+ * is involved.  The caller must synchronise the ranks (all kernels complete) before anyone reads. */
+int32_t kaio_b200_matmul_int4_allgather(const kaio_f16* a, size_t a_len,
+                                        const uint32_t* b_packed_shard, size_t b_len,
+                                        const kaio_f16* scales_shard, size_t scales_len,
+                                        void* const* out_ptrs, size_t out_len, uint32_t world,
+                                        uint32_t rank, uint32_t m, uint32_t n_total, uint32_t k,
+                                        uint32_t group_size, void* stream);
+
 /* ---- fused QKV projection ---------------------------------------------------------- */
 
 /* Replaces kaio_ops::qkv_project_int8 (kaio-ops/src/qkv_project_int8_kernel.rs:2008-2064),
@@ -153,6 +169,24 @@ int32_t kaio_b200_attention_mha_f16(const kaio_f16* q, size_t q_len, const kaio_
                                     size_t out_len, uint32_t batch, uint32_t heads, uint32_t seq_q,
                                     uint32_t seq_k, uint32_t head_dim, uint32_t row_stride,
                                     int32_t causal, void* stream);
+
+/* ---- quantisers (the step in front of the GEMMs; host code in the reference's examples) ---- */
+
+/* GPU form of `derive_scale` + `quantize` applied per row
+ * (examples/int8_matmul/src/main.rs:41-61): scale[i] = max_k |x[i,k]| / 127 (1 for an all-zero
+ * row), q[i,k] = clamp(round(x[i,k] / scale[i]), -127, 127), round half away from zero.
+ * x f32 [m,k], q s8 [m,k], scale f32 [m].  Feeds kaio_b200_matmul_int8_scaled. */
+int32_t kaio_b200_quantize_rows_int8(const float* x, size_t x_len, int8_t* q, size_t q_len,
+                                     float* scale, size_t scale_len, uint32_t m, uint32_t k,
+                                     void* stream);
+
+/* GPU form of `quantize_gptq_lite` + `pack_s4_weights` (examples/int4_matmul/src/main.rs:48-99):
+ * per (column, group of 128 k): scale = max |w| / 7 (1 if zero) stored as f16,
+ * q = clamp(round(w / scale), -8, 7) with the f32 scale; packed as kaio_b200_matmul_int4 expects.
+ * w f32 [k,n] row-major, packed u32 [(k/8)*n], scales f16 [k/128, n]. */
+int32_t kaio_b200_quantize_pack_int4(const float* w, size_t w_len, uint32_t* packed,
+                                     size_t packed_len, kaio_f16* scales, size_t scales_len,
+                                     uint32_t k, uint32_t n, uint32_t group_size, void* stream);
 
 /* ---- library state ------------------------------------------------------------------- */
 

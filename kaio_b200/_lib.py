@@ -24,6 +24,8 @@ SIGNATURES = {
     "kaio_b200_matmul_int8_acc": [_VP, _SZ, _VP, _SZ, _VP, _SZ, _U32, _U32, _U32, _VP],
     "kaio_b200_matmul_int4": [_VP, _SZ, _VP, _SZ, _VP, _SZ, _VP, _SZ, _U32, _U32, _U32, _U32, _VP],
     "kaio_b200_matmul_int4_noalloc": [_VP, _SZ, _VP, _SZ, _VP, _SZ, _VP, _SZ, _U32, _U32, _U32, _U32, _VP],
+    "kaio_b200_matmul_int4_allgather": [_VP, _SZ, _VP, _SZ, _VP, _SZ, _VP, _SZ, _U32, _U32, _U32, _U32, _U32,
+                                        _U32, _VP],
     "kaio_b200_matmul_int4_f16out": [_VP, _SZ, _VP, _SZ, _VP, _SZ, _VP, _SZ, _U32, _U32, _U32, _U32, _VP],
     "kaio_b200_qkv_project_int8": [_VP, _SZ, _VP, _SZ, _VP, _SZ, _VP, _SZ, _F32, _F32, _F32,
                                    _VP, _SZ, _VP, _SZ, _VP, _SZ, _U32, _U32, _U32, _VP],
@@ -34,6 +36,8 @@ SIGNATURES = {
     "kaio_b200_attention_tc": [_VP, _SZ, _VP, _SZ, _VP, _SZ, _VP, _SZ, _U32, _U32, _U32, _U32, _I32, _VP],
     "kaio_b200_attention_mha_f16": [_VP, _SZ, _VP, _SZ, _VP, _SZ, _VP, _SZ, _U32, _U32, _U32, _U32, _U32,
                                     _U32, _I32, _VP],
+    "kaio_b200_quantize_rows_int8": [_VP, _SZ, _VP, _SZ, _VP, _SZ, _U32, _U32, _VP],
+    "kaio_b200_quantize_pack_int4": [_VP, _SZ, _VP, _SZ, _VP, _SZ, _U32, _U32, _U32, _VP],
     "kaio_b200_device_status": [_VP, C.POINTER(_U32)],
 }
 

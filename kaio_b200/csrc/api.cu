@@ -712,6 +712,142 @@ KAIO_API int32_t kaio_b200_attention_mha_f16(const kaio_f16* q, size_t q_len, co
     return finish(launch_attention_generic(p, s), op, "attention_generic");
 }
 
+// ---------------------------------------------------------------- quantisers
+KAIO_API int32_t kaio_b200_quantize_rows_int8(const float* x, size_t x_len, int8_t* q, size_t q_len,
+                                              float* scale, size_t scale_len, uint32_t m,
+                                              uint32_t k, void* stream)
+{
+    const char* op = "quantize_rows_int8";
+    if (m == 0 || k == 0)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG, "%s dimensions must be non-zero", op);
+    const size_t mk = (size_t)m * k;
+    if (x_len < mk)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: X buffer too small: need %zu f32 (%u\xC3\x97%u), got %zu", op, mk, m, k,
+                    x_len);
+    if (q_len < mk)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: Q buffer too small: need %zu i8 (%u\xC3\x97%u), got %zu", op, mk, m, k,
+                    q_len);
+    if (scale_len < m)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: scale buffer too small: need %u f32, got %zu", op, m, scale_len);
+    REQUIRE_PTR(x, op, "X");
+    REQUIRE_PTR(q, op, "Q");
+    REQUIRE_PTR(scale, op, "scale");
+    DeviceCtx* ctx;
+    int32_t rc;
+    if ((rc = get_ctx(&ctx)))
+        return rc;
+    return finish(launch_quantize_rows_int8(x, q, scale, m, k, static_cast<cudaStream_t>(stream)),
+                  op, "quantize_rows_int8");
+}
+
+KAIO_API int32_t kaio_b200_quantize_pack_int4(const float* w, size_t w_len, uint32_t* packed,
+                                              size_t packed_len, kaio_f16* scales,
+                                              size_t scales_len, uint32_t k, uint32_t n,
+                                              uint32_t group_size, void* stream)
+{
+    const char* op = "quantize_pack_int4";
+    if (k == 0 || n == 0)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG, "%s dimensions must be non-zero", op);
+    if (group_size != 128)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG, "%s: group_size must be 128 (got %u)", op,
+                    group_size);
+    if (k % 128 != 0)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: K must be a multiple of group_size=128 (got %u)", op, k);
+    const size_t kn = (size_t)k * n, words = (size_t)(k / 8) * n, cells = (size_t)(k / 128) * n;
+    if (w_len < kn)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: W buffer too small: need %zu f32 (%u\xC3\x97%u), got %zu", op, kn, k, n,
+                    w_len);
+    if (packed_len < words)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: packed buffer too small: need %zu u32, got %zu", op, words, packed_len);
+    if (scales_len < cells)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: scales buffer too small: need %zu f16, got %zu", op, cells, scales_len);
+    REQUIRE_PTR(w, op, "W");
+    REQUIRE_PTR(packed, op, "packed");
+    REQUIRE_PTR(scales, op, "scales");
+    DeviceCtx* ctx;
+    int32_t rc;
+    if ((rc = get_ctx(&ctx)))
+        return rc;
+    return finish(launch_quantize_pack_s4(w, packed, reinterpret_cast<__half*>(scales), k, n,
+                                          static_cast<cudaStream_t>(stream)),
+                  op, "quantize_pack_s4");
+}
+
+// ---------------------------------------------------------------- sharded W4A16 + all-gather
+KAIO_API int32_t kaio_b200_matmul_int4_allgather(const kaio_f16* a, size_t a_len,
+                                                 const uint32_t* b_packed_shard, size_t b_len,
+                                                 const kaio_f16* scales_shard, size_t scales_len,
+                                                 void* const* out_ptrs, size_t out_len,
+                                                 uint32_t world, uint32_t rank, uint32_t m,
+                                                 uint32_t n_total, uint32_t k, uint32_t group_size,
+                                                 void* stream)
+{
+    const char* op = "matmul_int4_allgather";
+    if (world == 0 || world > 8 || rank >= world)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG, "%s: world must be 1..8 and rank < world (got %u, %u)",
+                    op, world, rank);
+    if (n_total == 0 || n_total % world != 0 || (n_total / world) % 8 != 0)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: N (%u) must split into %u shards of a multiple of 8 columns", op, n_total,
+                    world);
+    const uint32_t n_loc = n_total / world;
+    const size_t need_out = (size_t)m * n_total;
+    int32_t rc = validate_int4("f16", a_len, b_len, scales_len, need_out, m, n_loc, k, group_size);
+    if (rc)
+        return rc;
+    if (out_len < need_out)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: output buffers too small: need %zu f16 (%u\xC3\x97%u), got %zu", op, need_out,
+                    m, n_total, out_len);
+    REQUIRE_PTR(a, op, "A");
+    REQUIRE_PTR(b_packed_shard, op, "B packed");
+    REQUIRE_PTR(scales_shard, op, "scales");
+    REQUIRE_PTR(out_ptrs, op, "out_ptrs");
+    OutputCopies copies = {};
+    copies.count = world;
+    copies.ld = n_total;
+    for (uint32_t r = 0; r < world; ++r) {
+        if (out_ptrs[r] == nullptr || (uintptr_t)out_ptrs[r] % 16 != 0)
+            return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                        "%s: output pointer %u is null or not 16-byte aligned", op, r);
+        copies.ptrs[r] = reinterpret_cast<kaio_f16*>(out_ptrs[r]) + (size_t)rank * n_loc;
+    }
+    DeviceCtx* ctx;
+    if ((rc = get_ctx(&ctx)))
+        return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    DqProblem pr;
+    pr.w = b_packed_shard;
+    pr.scales = reinterpret_cast<const __half*>(scales_shard);
+    pr.col_scale = nullptr;
+    pr.scale = 1.0f;
+    pr.out = copies.ptrs[rank];
+    const __half* x = reinterpret_cast<const __half*>(a);
+    if (w4a16_decode_ok(x, &pr, 1, m, n_loc, k)) {
+        if ((rc = ensure_workspace(ctx, w4a16_decode_workspace_bytes(*ctx, n_loc, k),
+                                   w4a16_decode_num_counters(n_loc))))
+            return rc;
+        return finish(launch_w4a16_decode(*ctx, x, pr, true, m, n_loc, k, ctx->workspace,
+                                          ctx->tile_counters, s, &copies),
+                      op, "w4a16_decode_splitk_allgather");
+    }
+    if (!dq_gemm_fast_path_ok(WFMT_S4_PACKED, x, &pr, 1, true, m, n_loc, k))
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: A, B packed and the outputs must be 16-byte aligned", op);
+    if ((rc = ensure_dq_workspace(ctx, dq_gemm_workspace_bytes(1, n_loc, k))))
+        return rc;
+    return finish(launch_dq_gemm(*ctx, WFMT_S4_PACKED, x, &pr, 1, true, false, m, n_loc, k,
+                                 ctx->dq_workspace, s, &copies),
+                  op, "w4a16_tcgen05_allgather");
+}
+
 // ---------------------------------------------------------------- allocation-free decode entry
 // Scratch of kaio_b200_matmul_int4_noalloc: split-K partial tiles, tile arrival counters and a
 // status block, in a fixed array that is part of the loaded module (every GPU that loads the

@@ -41,6 +41,7 @@ constexpr int STG_TOTAL = 4 * 2 * STG_BYTES;
 constexpr int TMEM_COLS = 512;
 constexpr int NUM_THREADS = 192;
 constexpr int MAX_PROBS = 3;
+constexpr int MAX_OUT_MAPS = 8;  // 3 projections, or up to 8 copies of one output (sharded all-gather)
 
 // PAIR = false: one CTA per 128x256 tile, 4 weight chunks per stage, 4 stages of 48 KiB.
 // PAIR = true : a CTA pair per 256x256 tile (tcgen05 cta_group::2); each CTA stages its 128
@@ -67,6 +68,7 @@ struct Problem {
 struct Params {
     Problem probs[MAX_PROBS];
     uint32_t num_probs;
+    uint32_t copies;  // each output block is stored to `copies` tensor maps (out[prob*copies + r])
     uint32_t m, n, k;
     int post_scale;
     uint32_t* status;
@@ -75,7 +77,7 @@ struct Params {
 struct TensorMaps {
     CUtensorMap x;
     CUtensorMap w[MAX_PROBS];
-    CUtensorMap out[MAX_PROBS];
+    CUtensorMap out[MAX_OUT_MAPS];
 };
 
 template <bool PAIR, bool OUT_F16>
@@ -123,10 +125,10 @@ f16_gemm_kernel(const __grid_constant__ TensorMaps maps, const Params p)
         *abort_flag = 0;
         fence_barrier_init();
         tma_prefetch_desc(&maps.x);
-        for (uint32_t i = 0; i < p.num_probs; ++i) {
+        for (uint32_t i = 0; i < p.num_probs; ++i)
             tma_prefetch_desc(&maps.w[i]);
+        for (uint32_t i = 0; i < p.num_probs * p.copies; ++i)
             tma_prefetch_desc(&maps.out[i]);
-        }
     }
     if (warp == 1) {
         if (PAIR) {
@@ -268,7 +270,7 @@ f16_gemm_kernel(const __grid_constant__ TensorMaps maps, const Params p)
             uint32_t prob, m0, n0;
             decode_tile(tile, prob, m0, n0);
             const Problem& pr = p.probs[prob];
-            const CUtensorMap* omap = &maps.out[prob];
+            const CUtensorMap* omap = &maps.out[prob * p.copies];
             if (!mbar_wait_bounded_cluster(tmem_full_bar(buf), acc_ph, abort_flag, p.status,
                                            SITE_TMEM_FULL, KERNEL_DQ_GEMM))
                 break;
@@ -330,8 +332,12 @@ f16_gemm_kernel(const __grid_constant__ TensorMaps maps, const Params p)
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
-                    tma_store_2d(omap, stg_base + stg_off, (int32_t)col0,
-                                 (int32_t)(m0 + quarter * 32));
+                    // one store per destination: with the sharded all-gather the destinations are
+                    // the [M, N] buffers of every rank (peer memory), so the transfer overlaps the
+                    // GEMM tile by tile
+                    for (uint32_t r = 0; r < p.copies; ++r)
+                        tma_store_2d(omap + r, stg_base + stg_off, (int32_t)col0,
+                                     (int32_t)(m0 + quarter * 32));
                     tma_store_commit();
                 }
             }
@@ -488,7 +494,8 @@ static cudaError_t launch_f16_gemm(const DeviceCtx& ctx, const f16g::TensorMaps&
 
 cudaError_t launch_dq_gemm(const DeviceCtx& ctx, int wfmt, const __half* x, const DqProblem* probs,
                            int num_probs, bool out_f16, bool post_scale, uint32_t m, uint32_t n,
-                           uint32_t k, void* dq_workspace, cudaStream_t stream)
+                           uint32_t k, void* dq_workspace, cudaStream_t stream,
+                           const OutputCopies* copies)
 {
     using namespace f16g;
     const size_t per = dq_gemm_workspace_bytes(1, n, k);
@@ -525,14 +532,27 @@ cudaError_t launch_dq_gemm(const DeviceCtx& ctx, int wfmt, const __half* x, cons
                                    (uint64_t)n * 2, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B);
         if (err != cudaSuccess)
             return err;
+    }
+    // output maps: one per projection, or one per destination of the single output.  A destination
+    // map covers only this call's n columns of a wider row (row stride ld), so TMA clips at the
+    // shard's edge.
+    const uint32_t num_copies = copies ? copies->count : 1u;
+    for (int i = 0; i < MAX_OUT_MAPS; ++i) {
+        void* base;
+        uint64_t ld;
+        if (copies) {
+            base = copies->ptrs[(uint32_t)i < num_copies ? i : 0];
+            ld = copies->ld;
+        } else {
+            base = probs[i < num_probs ? i : 0].out;
+            ld = n;
+        }
         if (out_f16)
-            err = encode_tensor_map_2d(&maps.out[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
-                                       probs[j].out, n, m, (uint64_t)n * 2, 64, 32,
-                                       CU_TENSOR_MAP_SWIZZLE_128B);
+            err = encode_tensor_map_2d(&maps.out[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, n, m,
+                                       ld * 2, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B);
         else
-            err = encode_tensor_map_2d(&maps.out[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4,
-                                       probs[j].out, n, m, (uint64_t)n * 4, 32, 32,
-                                       CU_TENSOR_MAP_SWIZZLE_128B);
+            err = encode_tensor_map_2d(&maps.out[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, base, n, m,
+                                       ld * 4, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B);
         if (err != cudaSuccess)
             return err;
     }
@@ -542,6 +562,7 @@ cudaError_t launch_dq_gemm(const DeviceCtx& ctx, int wfmt, const __half* x, cons
         p.probs[i].scale = probs[i].scale;
     }
     p.num_probs = (uint32_t)num_probs;
+    p.copies = num_copies;
     p.m = m;
     p.n = n;
     p.k = k;

@@ -71,20 +71,38 @@ cudaError_t launch_dq_generic(int wfmt, const __half* x, const DqProblem* probs,
                               bool out_f16, bool post_scale, uint32_t m, uint32_t n, uint32_t k,
                               cudaStream_t stream);
 
+struct OutputCopies;
 bool w4a16_decode_ok(const void* x, const DqProblem* probs, int num_probs, uint32_t m, uint32_t n,
                      uint32_t k);
 size_t w4a16_decode_workspace_bytes(const DeviceCtx& ctx, uint32_t n, uint32_t k);
 size_t w4a16_decode_num_counters(uint32_t n);
 cudaError_t launch_w4a16_decode(const DeviceCtx& ctx, const __half* x, const DqProblem& prob,
                                 bool out_f16, uint32_t m, uint32_t n, uint32_t k, void* workspace,
-                                uint32_t* counters, cudaStream_t stream);
+                                uint32_t* counters, cudaStream_t stream,
+                                const OutputCopies* copies = nullptr);
 
 bool dq_gemm_fast_path_ok(int wfmt, const void* x, const DqProblem* probs, int num_probs,
                           bool out_f16, uint32_t m, uint32_t n, uint32_t k);
+// Destinations of a single-output GEMM: the [m, n] result is stored to every ptrs[r] (already
+// offset to this call's first column) with row stride ld elements.  Used by the sharded
+// all-gather form, where the destinations are the output buffers of all ranks (peer memory).
+struct OutputCopies {
+    void* ptrs[8];
+    uint32_t count;
+    uint64_t ld;
+};
+
 size_t dq_gemm_workspace_bytes(int num_probs, uint32_t n, uint32_t k);
 cudaError_t launch_dq_gemm(const DeviceCtx& ctx, int wfmt, const __half* x, const DqProblem* probs,
                            int num_probs, bool out_f16, bool post_scale, uint32_t m, uint32_t n,
-                           uint32_t k, void* dq_workspace, cudaStream_t stream);
+                           uint32_t k, void* dq_workspace, cudaStream_t stream,
+                           const OutputCopies* copies = nullptr);
+
+// ---------------------------------------------------------------- quantisers
+cudaError_t launch_quantize_rows_int8(const float* x, int8_t* q, float* scale, uint32_t m,
+                                      uint32_t k, cudaStream_t stream);
+cudaError_t launch_quantize_pack_s4(const float* w, uint32_t* packed, __half* scales, uint32_t k,
+                                    uint32_t n, cudaStream_t stream);
 
 // ---------------------------------------------------------------- attention
 struct AttnParams {

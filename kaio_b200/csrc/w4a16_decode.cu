@@ -73,7 +73,9 @@ enum : uint32_t {
 struct Params {
     const __half* a;       // [M,K]
     const __half* scales;  // [K/128, N]
-    void* out;             // f32 or f16 [M,N]
+    void* out[8];          // destinations, f32 or f16, row stride `ld` (one entry unless sharded)
+    uint32_t copies;
+    uint64_t ld;
     float* partials;       // [grid][2][128*16]
     uint32_t* counters;    // [tiles]
     uint32_t m, n, k;
@@ -542,14 +544,16 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const Params p)
             if (write_out) {
                 const uint32_t col = tile * BN + tid;
                 if (col < p.n) {
+                    for (uint32_t d = 0; d < p.copies; ++d) {
 #pragma unroll
-                    for (uint32_t r = 0; r < NROWS; ++r) {
-                        if (r < p.m) {
-                            const size_t idx = (size_t)r * p.n + col;
-                            if (OUT_F16)
-                                reinterpret_cast<__half*>(p.out)[idx] = __float2half_rn(acc[r]);
-                            else
-                                reinterpret_cast<float*>(p.out)[idx] = acc[r];
+                        for (uint32_t r = 0; r < NROWS; ++r) {
+                            if (r < p.m) {
+                                const size_t idx = (size_t)r * p.ld + col;
+                                if (OUT_F16)
+                                    reinterpret_cast<__half*>(p.out[d])[idx] = __float2half_rn(acc[r]);
+                                else
+                                    reinterpret_cast<float*>(p.out[d])[idx] = acc[r];
+                            }
                         }
                     }
                 }
@@ -604,7 +608,7 @@ size_t w4a16_decode_num_counters(uint32_t n)
 
 cudaError_t launch_w4a16_decode(const DeviceCtx& ctx, const __half* x, const DqProblem& prob,
                                 bool out_f16, uint32_t m, uint32_t n, uint32_t k, void* workspace,
-                                uint32_t* counters, cudaStream_t stream)
+                                uint32_t* counters, cudaStream_t stream, const OutputCopies* copies)
 {
     using namespace w4dec;
     CUtensorMap tmap_w;
@@ -617,7 +621,10 @@ cudaError_t launch_w4a16_decode(const DeviceCtx& ctx, const __half* x, const DqP
     Params p;
     p.a = x;
     p.scales = prob.scales;
-    p.out = prob.out;
+    for (int i = 0; i < 8; ++i)
+        p.out[i] = copies ? copies->ptrs[(uint32_t)i < copies->count ? i : 0] : prob.out;
+    p.copies = copies ? copies->count : 1u;
+    p.ld = copies ? copies->ld : n;
     p.partials = reinterpret_cast<float*>(workspace);
     p.counters = counters;
     p.m = m;

@@ -115,6 +115,17 @@ def matmul_int4(device, a, b_packed, scales, c, m, n, k, group_size):
           m, n, k, group_size)
 
 
+def matmul_int4_allgather(device, a, b_packed_shard, scales_shard, out_ptrs, out_numel, world, rank,
+                          m, n_total, k, group_size=GROUP_SIZE):
+    """Extension: this rank's column shard of a W4A16 GEMM, stored by the kernel into every rank's
+    f16 ``[m, n_total]`` buffer.  ``out_ptrs`` are ``world`` device addresses as mapped in this
+    process (e.g. ``torch.distributed._symmetric_memory`` ``buffer_ptrs``)."""
+    arr = (C.c_void_p * world)(*[C.c_void_p(int(p)) for p in out_ptrs])
+    _call(device, "kaio_b200_matmul_int4_allgather", *_buf(a, torch.float16, "a"),
+          *_buf(b_packed_shard, torch.int32, "b_packed_shard"), *_buf(scales_shard, torch.float16, "scales_shard"),
+          C.cast(arr, C.c_void_p), C.c_size_t(out_numel), world, rank, m, n_total, k, group_size)
+
+
 # ------------------------------------------------------------------ fused QKV
 
 def qkv_project_int8(device, x, w_q, w_k, w_v, scale_q, scale_k, scale_v, q_out, k_out, v_out, m, n, k):
@@ -149,6 +160,22 @@ def qkv_project_int4(device, x, w_q_packed, w_k_packed, w_v_packed, scales_q, sc
           *_buf(scales_k, torch.float16, "scales_k"), *_buf(scales_v, torch.float16, "scales_v"),
           *_buf(q_out, torch.float16, "q_out"), *_buf(k_out, torch.float16, "k_out"),
           *_buf(v_out, torch.float16, "v_out"), m, n, k, group_size)
+
+
+# ------------------------------------------------------------------ quantisers
+
+def quantize_rows_int8(device, x, q, scale, m, k):
+    """Per-row symmetric INT8 quantiser (``derive_scale`` + ``quantize`` of
+    examples/int8_matmul/src/main.rs:41-61, applied per row)."""
+    _call(device, "kaio_b200_quantize_rows_int8", *_buf(x, torch.float32, "x"), *_buf(q, torch.int8, "q"),
+          *_buf(scale, torch.float32, "scale"), m, k)
+
+
+def quantize_pack_int4(device, w, packed, scales, k, n, group_size=GROUP_SIZE):
+    """Group-wise INT4 quantiser + packer (``quantize_gptq_lite`` + ``pack_s4_weights`` of
+    examples/int4_matmul/src/main.rs:48-99)."""
+    _call(device, "kaio_b200_quantize_pack_int4", *_buf(w, torch.float32, "w"),
+          *_buf(packed, torch.int32, "packed"), *_buf(scales, torch.float16, "scales"), k, n, group_size)
 
 
 # ------------------------------------------------------------------ attention

@@ -125,3 +125,29 @@ class PanelPipeline:
                 full5[:, :, q, :].copy_(self.gathered[q].view(self.world, self.m, self.pw).transpose(0, 1))
         main.wait_stream(self.comm_stream)
         return self.full
+
+
+class FusedGatherGemm:
+    """Sharded W4A16 GEMM whose epilogue writes into every rank's output buffer (peer memory):
+    one kernel per rank does the GEMM and the all-gather, tile by tile over NVLink.
+
+    The ``[M, N]`` f16 output lives in torch symmetric memory so that every rank holds a mapping
+    of every other rank's buffer.  ``run()`` launches the kernel and then meets the other ranks
+    at the symmetric-memory barrier; after it returns (and the stream is synchronised or ordered),
+    ``self.out`` holds the full product on every rank.
+    """
+
+    def __init__(self, ops, device, m, n, k, world, rank, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.ops, self.device = ops, device
+        self.m, self.n, self.k, self.world, self.rank = m, n, k, world, rank
+        self.flat = symm_mem.empty(m * n, dtype=torch.float16, device=f"cuda:{device.ordinal}")
+        self.handle = symm_mem.rendezvous(self.flat, group if group is not None else dist.group.WORLD)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.out = self.flat.view(m, n)
+
+    def run(self, a, w_packed_shard, scales_shard):
+        self.ops.matmul_int4_allgather(self.device, a, w_packed_shard, scales_shard, self.ptrs,
+                                       self.m * self.n, self.world, self.rank, self.m, self.n, self.k)
+        self.handle.barrier()  # every rank's stores have landed before anyone reads
+        return self.out

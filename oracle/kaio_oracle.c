@@ -15,6 +15,7 @@
  *   qkv_int8         kaio-ops/tests/qkv_project_int8_e2e.rs:48-72 (cpu_reference_qkv_int8)
  *   qkv_int4         kaio-ops/tests/qkv_project_int4_e2e.rs:70-100 (cpu_reference_qkv_int4)
  *   attention        kaio-ops/tests/common/mod.rs:163-235         (cpu_attention_f16xf16_f32)
+ *   quantisers       examples/int8_matmul/src/main.rs:41-61, examples/int4_matmul/src/main.rs:48-85
  *
  * Parity pin: the restatement is checked against the known-answer vectors those
  * tests hold (0x11111111 / 0xFFFFFFFF pack words and the [8,-8,0,0] product,
@@ -340,6 +341,54 @@ KAIO_EXPORT void kaio_oracle_attention(const uint16_t *q, const uint16_t *k, con
         free(row);
         free(qf);
         free(o);
+    }
+}
+
+/* ----------------------------------------------------------- quantisers */
+
+/* derive_scale + quantize of examples/int8_matmul/src/main.rs:41-61, applied per row:
+ * scale = max|x| / 127 (1 if zero); q = clamp(round(x / scale), -127, 127); `round` is
+ * round-half-away-from-zero like Rust's f32::round. */
+KAIO_EXPORT void kaio_oracle_quantize_rows_int8(const float *x, uint32_t m, uint32_t k, int8_t *q,
+                                                float *scale)
+{
+    for (uint32_t i = 0; i < m; i++) {
+        float mx = 0.0f;
+        for (uint32_t j = 0; j < k; j++) {
+            float a = fabsf(x[(size_t)i * k + j]);
+            mx = a > mx ? a : mx;
+        }
+        float s = (mx == 0.0f) ? 1.0f : mx / 127.0f;
+        scale[i] = s;
+        for (uint32_t j = 0; j < k; j++) {
+            float v = roundf(x[(size_t)i * k + j] / s);
+            v = v < -127.0f ? -127.0f : (v > 127.0f ? 127.0f : v);
+            q[(size_t)i * k + j] = (int8_t)v;
+        }
+    }
+}
+
+/* quantize_gptq_lite of examples/int4_matmul/src/main.rs:48-85: per (column, group):
+ * scale = max|w| / 7 (1 if zero), stored as f16; q = clamp(round(w / scale_f32), -8, 7). */
+KAIO_EXPORT void kaio_oracle_quantize_gptq_lite(const float *w, uint32_t k, uint32_t n,
+                                                uint32_t group_size, int8_t *q, uint16_t *scales)
+{
+    uint32_t groups = k / group_size;
+    for (uint32_t col = 0; col < n; col++) {
+        for (uint32_t g = 0; g < groups; g++) {
+            float mx = 0.0f;
+            for (uint32_t kk = g * group_size; kk < (g + 1) * group_size; kk++) {
+                float a = fabsf(w[(size_t)kk * n + col]);
+                mx = a > mx ? a : mx;
+            }
+            float s = (mx == 0.0f) ? 1.0f : mx / 7.0f;
+            scales[(size_t)g * n + col] = kaio_oracle_f32_to_f16(s);
+            for (uint32_t kk = g * group_size; kk < (g + 1) * group_size; kk++) {
+                float v = roundf(w[(size_t)kk * n + col] / s);
+                v = v < -8.0f ? -8.0f : (v > 7.0f ? 7.0f : v);
+                q[(size_t)kk * n + col] = (int8_t)v;
+            }
+        }
     }
 }
 

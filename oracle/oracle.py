@@ -162,6 +162,25 @@ def attention(q, k, v, seq_q, seq_k, d_k, d_v, causal=False, strides=None, rows=
     return out
 
 
+def quantize_rows_int8(x, m, k):
+    """Per-row ``derive_scale`` + ``quantize`` -- examples/int8_matmul/src/main.rs:41-61."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    q = np.zeros((m, k), dtype=np.int8)
+    scale = np.zeros(m, dtype=np.float32)
+    lib().kaio_oracle_quantize_rows_int8(_p(x), C.c_uint32(m), C.c_uint32(k), _p(q), _p(scale))
+    return q, scale
+
+
+def quantize_gptq_lite(w, k, n, group_size=128):
+    """``quantize_gptq_lite`` -- examples/int4_matmul/src/main.rs:48-85.  Returns (q [K,N], scales)."""
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    q = np.zeros((k, n), dtype=np.int8)
+    scales = np.zeros((k // group_size) * n, dtype=np.float16)
+    lib().kaio_oracle_quantize_gptq_lite(_p(w), C.c_uint32(k), C.c_uint32(n), C.c_uint32(group_size),
+                                         _p(q), _p(scales))
+    return q, scales
+
+
 # ---------------------------------------------------------------------------
 # Deterministic generators of the reference tests (64-bit LCG).  Pure numpy,
 # vectorised by jumping the LCG, bit-identical to the scalar Rust closures.

@@ -145,3 +145,28 @@ def test_rejects_bad_arguments():
         ops.matmul_int4(d, a, b, s, c, 0, 8, 128, 128)
     with pytest.raises(InvalidConfig, match="scales buffer too small"):
         ops.matmul_int4(d, a, b, s[:3], c, 16, 8, 128, 128)
+
+
+@pytest.mark.parametrize("m", [8, 200])
+def test_allgather_form_with_local_destinations(oracle, m):
+    """The sharded all-gather entry point on one GPU: two local buffers stand in for the ranks'
+    output buffers; 'rank 1 of 2' must write its shard into columns [N/2, N) of both and touch
+    nothing else."""
+    n, k, world, rank = 512, 512, 2, 1
+    rng = np.random.default_rng(m)
+    w = rng.integers(-8, 8, (k, n), dtype=np.int8)
+    a = rng.standard_normal(m * k).astype(np.float16)
+    sc = rng.uniform(0.005, 0.02, (k // G) * n).astype(np.float16)
+    n_loc = n // world
+    lo = rank * n_loc
+    w_loc = np.ascontiguousarray(w[:, lo:lo + n_loc])
+    sc_loc = np.ascontiguousarray(sc.reshape(-1, n)[:, lo:lo + n_loc]).reshape(-1)
+    want = oracle.matmul_int4(a, oracle.pack_s4(w_loc, k, n_loc), sc_loc, m, n_loc, k, f16_out=True)
+    bufs = [torch.full((m * n,), 7.0, device="cuda", dtype=torch.float16) for _ in range(world)]
+    ops.matmul_int4_allgather(device(), dev(a), dev(oracle.pack_s4(w_loc, k, n_loc)), dev(sc_loc),
+                              [b.data_ptr() for b in bufs], m * n, world, rank, m, n, k)
+    assert ops.device_status(device())[0] == 0
+    for b in bufs:
+        got = host(b, (m, n)).astype(np.float32)
+        assert np.all(got[:, :lo] == 7.0)
+        assert max_rel(got[:, lo:], want.astype(np.float32)) < 2e-2

@@ -276,3 +276,33 @@ def test_row_range_leaves_other_rows_untouched(oracle):
     full = oracle.matmul_int8(a, b, 0.5, m, n, k)
     part = oracle.matmul_int8(a, b, 0.5, m, n, k, rows=(2, 5))
     assert np.array_equal(part[2:5], full[2:5]) and np.all(part[:2] == 0) and np.all(part[5:] == 0)
+
+
+# ---------------------------------------------------------------- quantisers
+
+def test_quantizers_match_numpy_restatement(oracle):
+    """examples/int8_matmul/src/main.rs:41-61 and examples/int4_matmul/src/main.rs:48-85 restated
+    with numpy (round half away from zero = sign * floor(|v| + 0.5))."""
+    rng = np.random.default_rng(1)
+    m, k = 5, 64
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    x[2] = 0
+    q, s = oracle.quantize_rows_int8(x, m, k)
+    for i in range(m):
+        mx = np.abs(x[i]).max()
+        sc = np.float32(1.0) if mx == 0 else np.float32(mx) / np.float32(127.0)
+        v = (x[i] / sc).astype(np.float32)
+        r = np.sign(v) * np.floor(np.abs(v) + np.float32(0.5))
+        assert s[i] == sc and np.array_equal(q[i], np.clip(r, -127, 127).astype(np.int8))
+    kk, n = 256, 6
+    w = (rng.standard_normal((kk, n)) * 0.1).astype(np.float32)
+    qw, sc = oracle.quantize_gptq_lite(w, kk, n)
+    for col in range(n):
+        for g in range(kk // 128):
+            blk = w[g * 128:(g + 1) * 128, col]
+            mx = np.abs(blk).max()
+            s32 = np.float32(1.0) if mx == 0 else np.float32(mx) / np.float32(7.0)
+            v = (blk / s32).astype(np.float32)
+            r = np.clip(np.sign(v) * np.floor(np.abs(v) + np.float32(0.5)), -8, 7).astype(np.int8)
+            assert sc[g * n + col] == np.float16(s32) and np.array_equal(qw[g * 128:(g + 1) * 128, col], r)
+    assert qw.max() == 7 and qw.min() >= -8
