@@ -184,6 +184,8 @@ def main():
     ap.add_argument("--impl", default="kaio_b200", choices=["kaio_b200", "reference"])
     ap.add_argument("--decode-only", action="store_true",
                     help="run only the W4A16 decode leg and print its JSON (profiling aid)")
+    ap.add_argument("--qkv-attention-only", action="store_true",
+                    help="run only the fused-QKV + attention leg and print its JSON (profiling aid)")
     ap.add_argument("--skip-extras", action="store_true",
                     help="only the headline step (no decode / e2e / cpu baseline legs)")
     args = ap.parse_args()
@@ -211,6 +213,9 @@ def main():
     m = M_PREFILL
     if args.decode_only:
         print(json.dumps({"w4a16_decode": bench_decode(torch, ops, dev, peaks, load_traffic())}), flush=True)
+        return
+    if args.qkv_attention_only:
+        print(json.dumps({"qkv_attention": bench_qkv_attention(torch, ops, dev, peaks)}), flush=True)
         return
 
     # ---- synthetic inputs (seeded; config 3 value ranges), resident in HBM

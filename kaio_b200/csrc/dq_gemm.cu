@@ -41,6 +41,7 @@ constexpr int STG_TOTAL = 4 * 2 * STG_BYTES;
 constexpr int TMEM_COLS = 512;
 constexpr int NUM_THREADS = 192;
 constexpr int MAX_PROBS = 3;
+constexpr uint32_t RASTER_GM = 8;  // m-tiles per rasterisation group
 constexpr int MAX_OUT_MAPS = 8;  // 3 projections, or up to 8 copies of one output (sharded all-gather)
 
 // PAIR = false: one CTA per 128x256 tile, 4 weight chunks per stage, 4 stages of 48 KiB.
@@ -146,13 +147,21 @@ f16_gemm_kernel(const __grid_constant__ TensorMaps maps, const Params p)
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
-    // tile -> (projection, m-tile, n-tile); m fastest so workers running side by side share a
-    // weight panel in L2
+    // tile -> (projection, m-tile, n-tile).  Within a projection the tiles are walked in groups of
+    // RASTER_GM m-tiles: m fastest inside the group, then n, then the next group.  The workers
+    // running side by side then cover a near-square patch (few x rows x few weight panels), the
+    // group's x rows stay in L2 while the weight panels sweep past, and the weights (tens of MB)
+    // stay in L2 from one group to the next: each operand comes from DRAM about once.
     auto decode_tile = [&](uint32_t tile, uint32_t& prob, uint32_t& m0, uint32_t& n0) {
         prob = tile / tiles_per_prob;
         const uint32_t r = tile - prob * tiles_per_prob;
-        m0 = (r % tiles_m) * C::BM + rank * BM_CTA;
-        n0 = (r / tiles_m) * BN;
+        const uint32_t group_tiles = RASTER_GM * tiles_n;
+        const uint32_t g = r / group_tiles;
+        const uint32_t rem = r - g * group_tiles;
+        const uint32_t gm = (tiles_m - g * RASTER_GM) < RASTER_GM ? (tiles_m - g * RASTER_GM) : RASTER_GM;
+        const uint32_t nt = rem / gm, mi = rem - nt * gm;
+        m0 = (g * RASTER_GM + mi) * C::BM + rank * BM_CTA;
+        n0 = nt * BN;
     };
 
     if (warp == 0) {

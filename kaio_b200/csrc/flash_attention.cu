@@ -288,21 +288,32 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
                 col_lim = row + 1;
             const bool need_mask = col_base + BKV > col_lim;
 
-            // ---- pass 1: block maximum of the scaled scores
-            float m_blk = -INFINITY;
+            // only the diagonal block (causal) and the seq_k tail need per-element masks; the
+            // test is made warp-uniform so the common blocks run mask-free code
+            const bool blk_mask = __any_sync(0xffffffffu, need_mask);
+
+            // ---- pass 1: block maximum of the raw scores (the scale is positive: scale after)
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll 1
             for (uint32_t c = 0; c < BKV / 32; ++c) {
                 uint32_t r[32];
                 tmem_ld_32x32b_x32(s_tmem + c * 32, r);
                 tmem_ld_wait();
+                if (blk_mask) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float x = __uint_as_float(r[i]) * p.scale_log2;
-                    if (need_mask && col_base + c * 32 + i >= col_lim)
-                        x = -INFINITY;
-                    m_blk = fmaxf(m_blk, x);
+                    for (int i = 0; i < 32; ++i)
+                        if (col_base + c * 32 + i >= col_lim)
+                            r[i] = 0xff800000u;  // -inf
+                }
+#pragma unroll
+                for (int i = 0; i < 32; i += 4) {  // four independent chains
+                    mx0 = fmaxf(mx0, __uint_as_float(r[i]));
+                    mx1 = fmaxf(mx1, __uint_as_float(r[i + 1]));
+                    mx2 = fmaxf(mx2, __uint_as_float(r[i + 2]));
+                    mx3 = fmaxf(mx3, __uint_as_float(r[i + 3]));
                 }
             }
+            const float m_blk = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
             // ---- lazy rescale: keep the old reference unless the max grew by more than 2^8
             float alpha = 1.0f;
             if (j == 0) {
@@ -338,31 +349,39 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
                 }
                 tmem_st_wait();
             }
-            // ---- pass 2: p = 2^(x - m_ref), row sum, f16 pairs into tensor memory
+            // ---- pass 2: p = 2^(s * scale - m_ref), row sum, f16 pairs into tensor memory
             const uint32_t p_tmem = tmem_base + TMEM_P + (j & 1u) * (BKV / 2) + lane_sel;
+            float ls0 = 0.0f, ls1 = 0.0f, ls2 = 0.0f, ls3 = 0.0f;
 #pragma unroll 1
             for (uint32_t c = 0; c < BKV / 32; ++c) {
                 uint32_t r[32];
                 tmem_ld_32x32b_x32(s_tmem + c * 32, r);
                 tmem_ld_wait();
+                if (blk_mask) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (col_base + c * 32 + i >= col_lim)
+                            r[i] = 0xff800000u;  // -inf -> p = 0
+                }
                 uint32_t pk[16];
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float x0 = __uint_as_float(r[i]) * p.scale_log2 - m_ref;
-                    float x1 = __uint_as_float(r[i + 1]) * p.scale_log2 - m_ref;
-                    if (need_mask) {
-                        if (col_base + c * 32 + i >= col_lim)
-                            x0 = -INFINITY;
-                        if (col_base + c * 32 + i + 1 >= col_lim)
-                            x1 = -INFINITY;
-                    }
-                    const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
-                    l_sum += p0 + p1;
-                    const __half2 hp = __floats2half2_rn(p0, p1);
-                    pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&hp);
+                for (int i = 0; i < 32; i += 4) {
+                    const float p0 = ex2_approx(fmaf(__uint_as_float(r[i]), p.scale_log2, -m_ref));
+                    const float p1 = ex2_approx(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -m_ref));
+                    const float p2 = ex2_approx(fmaf(__uint_as_float(r[i + 2]), p.scale_log2, -m_ref));
+                    const float p3 = ex2_approx(fmaf(__uint_as_float(r[i + 3]), p.scale_log2, -m_ref));
+                    ls0 += p0;
+                    ls1 += p1;
+                    ls2 += p2;
+                    ls3 += p3;
+                    const __half2 h01 = __floats2half2_rn(p0, p1);
+                    const __half2 h23 = __floats2half2_rn(p2, p3);
+                    pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&h01);
+                    pk[(i >> 1) + 1] = *reinterpret_cast<const uint32_t*>(&h23);
                 }
                 tmem_st_32x32b_x16(p_tmem + c * 16, pk);
             }
+            l_sum += (ls0 + ls1) + (ls2 + ls3);
             tmem_st_wait();
             tc_fence_before_sync();
             __syncwarp();

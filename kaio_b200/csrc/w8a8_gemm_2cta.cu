@@ -40,6 +40,7 @@ constexpr int STG_TOTAL = 4 * 2 * STG_BYTES;
 constexpr int TMEM_COLS = 512;  // 2 accumulator buffers x 256 columns, in each CTA
 constexpr int NUM_THREADS = 192;
 constexpr int NUM_BARS = 2 * STAGES + 4;
+constexpr uint32_t RASTER_GM = 8;  // m-tiles per rasterisation group
 constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + STG_TOTAL + NUM_BARS * 8 + 64;
 
 constexpr uint32_t IDESC = make_idesc(/*d=s32*/ 2, /*a=s8*/ 1, /*b=s8*/ 1, /*a K-major*/ 0,
@@ -88,6 +89,18 @@ w8a8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t num_tiles = tiles_m * tiles_n;
     const uint32_t num_kb = (p.k + BK - 1) / BK;
 
+    // Tiles are walked in groups of RASTER_GM m-tiles (m fastest inside the group, then n, then
+    // the next group): pairs running side by side cover a near-square patch, the group's rows of
+    // A stay in L2 while the B panels sweep past, and B stays in L2 from group to group.
+    auto tile_origin = [&](uint32_t tile, uint32_t& tm, uint32_t& tn) {
+        const uint32_t group_tiles = RASTER_GM * tiles_n;
+        const uint32_t g = tile / group_tiles;
+        const uint32_t rem = tile - g * group_tiles;
+        const uint32_t gm = (tiles_m - g * RASTER_GM) < RASTER_GM ? (tiles_m - g * RASTER_GM) : RASTER_GM;
+        tn = rem / gm;
+        tm = g * RASTER_GM + (rem - tn * gm);
+    };
+
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < STAGES; ++s) {
             mbar_init(full_bar(s), 1);
@@ -118,8 +131,10 @@ w8a8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
         uint32_t s = 0, ph = 0;
         bool ok = true;
         for (uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs) {
-            const int32_t m0 = (tile % tiles_m) * BM + rank * BM_CTA;
-            const int32_t n0 = (tile / tiles_m) * BN + rank * 128;
+            uint32_t tm, tn;
+            tile_origin(tile, tm, tn);
+            const int32_t m0 = tm * BM + rank * BM_CTA;
+            const int32_t n0 = tn * BN + rank * 128;
             for (uint32_t kb = 0; kb < num_kb; ++kb) {
                 if (!mbar_wait_bounded_cluster(empty_bar(s), ph ^ 1u, abort_flag, p.status,
                                                SITE_EMPTY, KERNEL_W8A8)) {
@@ -200,8 +215,10 @@ w8a8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
         for (uint32_t tile = pair; tile < num_tiles; tile += num_pairs, ++local_tile) {
             const uint32_t buf = local_tile & 1u;
             const uint32_t acc_ph = (local_tile >> 1) & 1u;
-            const uint32_t m0 = (tile % tiles_m) * BM + rank * BM_CTA;
-            const uint32_t n0 = (tile / tiles_m) * BN;
+            uint32_t tm, tn;
+            tile_origin(tile, tm, tn);
+            const uint32_t m0 = tm * BM + rank * BM_CTA;
+            const uint32_t n0 = tn * BN;
             if (!mbar_wait_bounded_cluster(tmem_full_bar(buf), acc_ph, abort_flag, p.status,
                                            SITE_TMEM_FULL, KERNEL_W8A8))
                 break;

@@ -91,3 +91,33 @@ def test_no_cpu_fallback_without_gpu(lib):
     rc = lib.kaio_b200_matmul_int8(a, 16 * 32, b, 32 * 16, c, 16 * 16, 1.0, 16, 16, 32, None)
     assert rc in (2, 3), err(lib)
     assert all(v == 0.0 for v in c)
+
+
+def test_cpp_mirror_header_compiles_and_reports_reference_errors(lib, tmp_path):
+    """include/kaio_ops.hpp (C++ mirror of the kaio-ops signatures) compiles against the header,
+    links against the library and surfaces validation errors as KaioError with the reference text."""
+    import os
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = tmp_path / "t.cpp"
+    src.write_text(r'''
+#include <cstdio>
+#include <cstring>
+#include "kaio_ops.hpp"
+int main() {
+    kaio_ops::KaioDevice dev(0);
+    kaio_ops::GpuBuffer<const int8_t> a(nullptr, 0), b(nullptr, 0);
+    kaio_ops::GpuBuffer<float> c(nullptr, 0);
+    try { kaio_ops::matmul_int8(dev, a, b, c, 1.0f, 16, 8, 31); }
+    catch (const kaio_ops::KaioError& e) {
+        if (e.is_invalid_config() && std::strstr(e.what(), "K must be a multiple of 32")) { std::puts("ok"); return 0; }
+    }
+    return 1;
+}
+''')
+    exe = tmp_path / "t"
+    libdir = os.path.join(root, "kaio_b200", "lib")
+    subprocess.run(["g++", "-std=c++17", "-I", os.path.join(root, "include"), str(src), "-o", str(exe),
+                    "-L", libdir, "-lkaio_b200", f"-Wl,-rpath,{libdir}"], check=True)
+    out = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert out.returncode == 0 and out.stdout.strip() == "ok"

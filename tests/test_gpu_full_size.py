@@ -1,0 +1,125 @@
+"""Parity at BASELINE.json's full sizes.  The CPU oracle cannot finish these shapes in seconds, so
+each case checks a row (or head) sample against the oracle -- all columns, full K -- plus a
+size-independent property of the whole output (linearity in the scales, agreement between entry
+points that must share accumulators)."""
+import numpy as np
+import pytest
+import torch
+
+from kaio_b200 import ops
+from helpers import assert_attention_close, dev, device, host, max_rel
+
+pytestmark = pytest.mark.gpu
+G = 128
+
+
+@pytest.mark.parametrize("k,n", [(4096, 11008), (11008, 4096), (4096, 4096)])
+def test_w8a8_prefill_config3(oracle, k, n):
+    m = 4096
+    rng = np.random.default_rng(42)
+    a = rng.integers(-127, 128, (m, k), dtype=np.int8)
+    b = rng.integers(-127, 128, (k, n), dtype=np.int8)
+    sa = rng.uniform(0.001, 0.01, m).astype(np.float32)
+    sw = rng.uniform(0.001, 0.01, n).astype(np.float32)
+    d = device()
+    ad, bd = dev(a), dev(b)
+    c = torch.empty(m * n, device="cuda", dtype=torch.float32)
+    acc = torch.empty(m * n, device="cuda", dtype=torch.int32)
+    ops.matmul_int8_scaled(d, ad, bd, c, dev(sa), dev(sw), m, n, k)
+    assert ops.last_variant() == "w8a8_tcgen05_2cta"
+    ops.matmul_int8_acc(d, ad, bd, acc, m, n, k)
+    assert ops.device_status(d)[0] == 0
+    rows = [0, 1, 127, 128, 255, 256, 2047, 4095] + rng.integers(0, m, 8).tolist()
+    for r in rows:  # bit-exact against the oracle on sampled rows
+        want, want_acc = oracle.matmul_int8(a[r:r + 1], b, 1.0, 1, n, k, want_acc=True)
+        assert np.array_equal(host(acc.view(m, n)[r]), want_acc[0])
+        want_scaled = oracle.matmul_int8_scaled(a[r:r + 1], b, sa[r:r + 1], sw, 1, n, k)
+        assert np.array_equal(host(c.view(m, n)[r]), want_scaled[0])
+    # whole output: the scaled result is exactly the epilogue applied to the accumulators
+    ref = (acc.view(m, n).to(torch.float32) * dev(sa).view(m, 1)) * dev(sw).view(1, n)
+    assert torch.equal(ref, c.view(m, n))
+
+
+@pytest.mark.parametrize("m", [1, 8, 16])
+def test_w4a16_decode_config2_full(oracle, m):
+    k, n = 4096, 11008
+    rng = np.random.default_rng(137)
+    w = rng.integers(-8, 8, k * n, dtype=np.int8)
+    a = rng.standard_normal(m * k).astype(np.float16)
+    s = rng.uniform(0.005, 0.02, (k // G) * n).astype(np.float16)
+    packed = oracle.pack_s4(w, k, n)
+    want = oracle.matmul_int4(a, packed, s, m, n, k, f16_out=True)
+    c = torch.empty(m * n, device="cuda", dtype=torch.float16)
+    ops.matmul_int4(device(), dev(a), dev(packed), dev(s), c, m, n, k, G)
+    assert ops.last_variant() == "w4a16_decode_splitk"
+    assert max_rel(host(c, (m, n)), want) < 2e-2
+
+
+def test_qkv_config4_sampled_rows(oracle):
+    m, k, n = 16384, 4096, 4096
+    rng = np.random.default_rng(42)
+    x = rng.standard_normal((m, k)).astype(np.float16)
+    d = device()
+    xd = dev(x)
+    outs = [torch.empty(m * n, device="cuda", dtype=torch.float16) for _ in range(3)]
+    rows = [0, 127, 128, 8191, 16383] + rng.integers(0, m, 3).tolist()
+    # W8A16 with per-column scales
+    w8 = [rng.integers(-127, 128, (k, n), dtype=np.int8) for _ in range(3)]
+    cs = [rng.uniform(0.0001, 0.001, n).astype(np.float32) for _ in range(3)]
+    ops.qkv_project_int8(d, xd, *[dev(w) for w in w8], *[dev(c) for c in cs], *outs, m, n, k)
+    assert ops.last_variant() == "qkv_w8a16_tcgen05"
+    for o, w, c in zip(outs, w8, cs):
+        got = host(o.view(m, n)[rows])
+        want = oracle.qkv_int8(x[rows], w, 0.0, len(rows), n, k, col_scale=c)
+        assert max_rel(got, want) < 1e-3
+    # W4A16
+    w4 = [rng.integers(-8, 8, (k, n), dtype=np.int8) for _ in range(3)]
+    sc = [rng.uniform(0.005, 0.02, (k // G) * n).astype(np.float16) for _ in range(3)]
+    packed = [oracle.pack_s4(w, k, n) for w in w4]
+    ops.qkv_project_int4(d, xd, *[dev(p) for p in packed], *[dev(s) for s in sc], *outs, m, n, k, G)
+    assert ops.last_variant() == "qkv_w4a16_tcgen05"
+    for o, p, s in zip(outs, packed, sc):
+        got = host(o.view(m, n)[rows])
+        want = oracle.qkv_int4(x[rows], p, s, len(rows), n, k)
+        assert max_rel(got, want) < 1e-3
+    assert ops.device_status(d)[0] == 0
+
+
+def test_attention_config4_sampled_heads(oracle):
+    b, h, s, hd = 8, 32, 2048, 128
+    stride = h * hd
+    g = torch.Generator(device="cuda")
+    g.manual_seed(42)
+    q, k, v = [torch.randn(b * s * stride, device="cuda", generator=g).half() for _ in range(3)]
+    o = torch.empty(b * s * stride, device="cuda", dtype=torch.float16)
+    ops.attention_mha_f16(device(), q, k, v, o, b, h, s, s, hd, stride, True)
+    assert ops.last_variant() == "flash_tcgen05"
+    assert ops.device_status(device())[0] == 0
+    for (bi, hi) in [(0, 0), (3, 17), (7, 31)]:
+        sl = lambda t: np.ascontiguousarray(host(t.view(b, s, h, hd)[bi, :, hi, :]))
+        qh, kh, vh = sl(q), sl(k), sl(v)
+        rows = (1900, 2048)  # the last query rows attend to (almost) all keys: the longest sums
+        want = oracle.attention(qh.reshape(-1), kh.reshape(-1), vh.reshape(-1), s, s, hd, hd, causal=True, rows=rows)
+        got = sl(o).astype(np.float32)
+        assert_attention_close(got[rows[0]:rows[1]], want[rows[0]:rows[1]])
+        want0 = oracle.attention(qh.reshape(-1), kh.reshape(-1), vh.reshape(-1), s, s, hd, hd, causal=True, rows=(0, 130))
+        assert_attention_close(got[:130], want0[:130])
+    # property: causal row 0 of every head is exactly V row 0
+    o4, v4 = o.view(b, s, h, hd), v.view(b, s, h, hd)
+    assert torch.allclose(o4[:, 0].float(), v4[:, 0].float(), atol=2e-3)
+
+
+@pytest.mark.parametrize("m,k,n", [(256, 8192, 28672), (4096, 28672, 8192)])
+def test_w4a16_ffn70b_config5_sampled_rows(oracle, m, k, n):
+    rng = np.random.default_rng(5)
+    w = rng.integers(-8, 8, (k, n), dtype=np.int8)
+    a = rng.standard_normal((m, k)).astype(np.float16)
+    s = rng.uniform(0.005, 0.02, (k // G) * n).astype(np.float16)
+    packed = oracle.pack_s4(w, k, n)
+    del w
+    c = torch.empty(m * n, device="cuda", dtype=torch.float16)
+    ops.matmul_int4(device(), dev(a), dev(packed), dev(s), c, m, n, k, G)
+    assert ops.last_variant() == "w4a16_tcgen05"
+    rows = [0, m // 2, m - 1]
+    want = oracle.matmul_int4(a[rows], packed, s, len(rows), n, k, f16_out=True)
+    assert max_rel(host(c.view(m, n)[rows]), want) < 2e-2
