@@ -7,20 +7,23 @@
 // in shared memory, seq_k <= 384) and adds the batched multi-head form that reads Q/K/V in place
 // from [batch*seq, heads*128] projection outputs.
 //
-// One CTA per (batch, head, 128 query rows), 192 threads:
-//   warp 0     TMA producer: Q once (two [128][64] boxes), then K and V blocks ([128 kv][128 d] as
+// One CTA per (batch, head, 256 query rows) = two query tiles of 128 rows, 320 threads:
+//   warp 0     TMA producer: Q once (four [128][64] boxes), then K and V blocks ([128 kv][128 d] as
 //              two 64-column boxes each) through a 2-stage ring; 128-byte swizzle.
-//   warp 1     MMA issuer (converged warp, elected lane):
-//                S_j  = Q K_j^T     tcgen05.mma kind::f16 M128 N128 K16 x8, Q and K from shared
-//                                   memory (both K-major), S in tensor memory (double buffered)
-//                O   += P_j V_j     M128 N128 K16 x8, P (f16) from TENSOR MEMORY, V from shared
-//                                   memory read MN-major (d contiguous), O in tensor memory
-//              QK^T of block j+1 is issued before P V of block j, so the tensor pipe works on the
-//              next scores while the softmax warps process the current ones.
-//   warps 2-5  softmax: thread = query row.  tcgen05.ld of the score row, scale by
-//              log2(e)/sqrt(d), causal / tail mask, running max with lazy rescale (O and the row
-//              sum are rescaled only when the max grows by more than 2^8), ex2, row sum, P packed
-//              to f16 and stored to tensor memory; at the end O / sum -> global.
+//   warp 1     MMA issuer (converged warp, elected lane), for tile t in {0, 1}:
+//                S_t  = Q_t K_j^T   tcgen05.mma kind::f16 M128 N128 K16 x8, Q and K from shared
+//                                   memory (both K-major), S_t in tensor memory
+//                O_t += P_t V_j     M128 N128 K16 x8, P_t (f16) from TENSOR MEMORY (it overwrites
+//                                   the first 64 columns of S_t), V from shared memory read
+//                                   MN-major (d contiguous), O_t in tensor memory
+//              issue order per block: PV_0(j), QK_0(j+1), PV_1(j), QK_1(j+1) -- while one tile's
+//              softmax runs, the tensor pipe works on the other tile.
+//   warps 2-5  softmax of tile 0, warps 6-9 softmax of tile 1: thread = query row.  tcgen05.ld of
+//              the score row, block max (four independent chains), running max with lazy rescale
+//              (O and the row sum are rescaled only when the max grows by more than 2^8),
+//              ex2(s * log2(e)/sqrt(d) - max), row sum, P packed to f16 and stored to tensor
+//              memory; at the end O / sum -> global.  Two warps per scheduler hide each other's
+//              dependent chains; a single softmax warp-group left the tensor pipe 27 % busy.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -31,16 +34,16 @@ constexpr int BQ = 128;   // query rows per CTA
 constexpr int BKV = 128;  // key/value rows per block
 constexpr int D = 128;    // head dim
 constexpr int KV_STAGES = 2;
-constexpr int Q_BYTES = BQ * D * 2;           // 32 KiB: two [128][64] sub-tiles
+constexpr int Q_TILE_BYTES = BQ * D * 2;      // 32 KiB: two [128][64] sub-tiles
+constexpr int Q_BYTES = 2 * Q_TILE_BYTES;     // two query tiles per CTA
 constexpr int KV_TILE_BYTES = BKV * D * 2;    // 32 KiB each for K and V
 constexpr int STAGE_BYTES = 2 * KV_TILE_BYTES;  // K | V
 constexpr int SUB_BYTES = 128 * 128;          // one [128 rows][64 f16] sub-tile
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320;
 constexpr int SMEM_BYTES = 1024 + Q_BYTES + KV_STAGES * STAGE_BYTES + 256;
 constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t TMEM_S = 0;      // 2 x 128 columns (f32 scores)
-constexpr uint32_t TMEM_O = 256;    // 128 columns (f32 output accumulator)
-constexpr uint32_t TMEM_P = 384;    // 2 x 64 columns (f16 probabilities, 2 per column)
+constexpr uint32_t TMEM_S = 0;      // per tile: 128 columns of f32 scores; P (f16 pairs) reuses the first 64
+constexpr uint32_t TMEM_O = 256;    // per tile: 128 columns (f32 output accumulator)
 
 constexpr uint32_t IDESC_QK = make_idesc(1, 0, 0, /*a K-major*/ 0, /*b K-major*/ 0, BQ, BKV);
 constexpr uint32_t IDESC_PV = make_idesc(1, 0, 0, /*a K-major*/ 0, /*b MN-major*/ 1, BQ, D);
@@ -139,18 +142,24 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
     const uint32_t lane = threadIdx.x & 31;
 
     // heavy (late, causal) query blocks first
-    const uint32_t num_qb = (p.seq_q + BQ - 1) / BQ;
+    const uint32_t num_qb = (p.seq_q + 2 * BQ - 1) / (2 * BQ);
     const uint32_t qb = num_qb - 1 - blockIdx.x;
     const uint32_t bh = blockIdx.y;
     const uint32_t b = bh / p.heads, h = bh % p.heads;
-    const uint32_t q0 = qb * BQ;
-    // KV blocks this query block attends to
-    uint32_t kv_end = p.seq_k;
-    if (p.causal) {
-        const uint32_t lim = q0 + BQ;  // columns j <= i < q0 + BQ
-        kv_end = lim < kv_end ? lim : kv_end;
+    const uint32_t q0 = qb * 2 * BQ;
+    // KV blocks each query tile attends to (0 for a tile that lies beyond seq_q)
+    uint32_t nkv[2];
+#pragma unroll
+    for (uint32_t t = 0; t < 2; ++t) {
+        const uint32_t tq0 = q0 + t * BQ;
+        uint32_t kv_end = p.seq_k;
+        if (p.causal) {
+            const uint32_t lim = tq0 + BQ;  // columns j <= i < tq0 + BQ
+            kv_end = lim < kv_end ? lim : kv_end;
+        }
+        nkv[t] = tq0 < p.seq_q ? (kv_end + BKV - 1) / BKV : 0u;
     }
-    const uint32_t num_kv = (kv_end + BKV - 1) / BKV;
+    const uint32_t num_kv = nkv[0] > nkv[1] ? nkv[0] : nkv[1];
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
@@ -160,7 +169,7 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
         }
         for (uint32_t i = 0; i < 2; ++i) {
             mbar_init(s_full(i), 1);
-            mbar_init(p_full(i), 4);  // one arrive per softmax warp
+            mbar_init(p_full(i), 4);  // one arrive per softmax warp of the tile
             mbar_init(pv_done(i), 1);
         }
         *abort_flag = 0;
@@ -184,8 +193,12 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
         const int32_t q_row = (int32_t)(b * p.seq_q + q0);
         if (elect_one()) {
             mbar_expect_tx(q_full, Q_BYTES);
-            tma_load_2d(q_smem, &maps.q, q_full, col0, q_row);
-            tma_load_2d(q_smem + SUB_BYTES, &maps.q, q_full, col0 + 64, q_row);
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+                tma_load_2d(q_smem + t * Q_TILE_BYTES, &maps.q, q_full, col0, q_row + t * BQ);
+                tma_load_2d(q_smem + t * Q_TILE_BYTES + SUB_BYTES, &maps.q, q_full, col0 + 64,
+                            q_row + t * BQ);
+            }
         }
         __syncwarp();
         for (uint32_t j = 0; j < num_kv; ++j) {
@@ -210,19 +223,20 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
                 __nanosleep(100);
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        auto issue_qk = [&](uint32_t j) {
-            // S[j&1] = Q K_j^T : 8 steps of 16 along d; sub-tile d/64, 32 bytes inside the row
+        auto issue_qk = [&](uint32_t t, uint32_t j) {
+            // S_t = Q_t K_j^T : 8 steps of 16 along d; sub-tile d/64, 32 bytes inside the row
             const uint32_t stage = kv_smem + (j & 1u) * STAGE_BYTES;
-            const uint32_t d_tmem = tmem_base + TMEM_S + (j & 1u) * BKV;
+            const uint32_t qt = q_smem + t * Q_TILE_BYTES;
+            const uint32_t d_tmem = tmem_base + TMEM_S + t * BKV;
             if (elect_one()) {
 #pragma unroll
                 for (uint32_t kk = 0; kk < D / 16; ++kk) {
                     const uint32_t off = (kk >> 2) * SUB_BYTES + (kk & 3u) * 32;
-                    umma_f16(d_tmem, make_smem_desc_sw128(q_smem + off, 16, 1024),
+                    umma_f16(d_tmem, make_smem_desc_sw128(qt + off, 16, 1024),
                              make_smem_desc_sw128(stage + off, 16, 1024), IDESC_QK,
                              kk != 0 ? 1u : 0u);
                 }
-                umma_commit(s_full(j & 1u));
+                umma_commit(s_full(t));
             }
             __syncwarp();
         };
@@ -232,62 +246,86 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
                                    KERNEL_FLASH_ATTN);
             if (ok) {
                 tc_fence_after_sync();
-                issue_qk(0);
+                if (nkv[0] > 0)
+                    issue_qk(0, 0);
+                if (nkv[1] > 0)
+                    issue_qk(1, 0);
             }
         }
         for (uint32_t j = 0; ok && j < num_kv; ++j) {
-            if (j + 1 < num_kv) {
-                // scores of the next block while the softmax warps work on this one
-                if (!mbar_wait_bounded(kv_full((j + 1) & 1u), ((j + 1) >> 1) & 1u, abort_flag,
-                                       p.status, SITE_KV_FULL, KERNEL_FLASH_ATTN))
-                    break;
-                tc_fence_after_sync();
-                issue_qk(j + 1);
-            }
-            if (!mbar_wait_bounded(p_full(j & 1u), (j >> 1) & 1u, abort_flag, p.status, SITE_P_FULL,
-                                   KERNEL_FLASH_ATTN))
-                break;
-            tc_fence_after_sync();
-            // O += P_j V_j : 8 steps of 16 along kv; P in tensor memory (8 columns per step),
-            // V MN-major: 16 kv rows of 128 bytes per step, the two 64-column halves SUB_BYTES apart
-            const uint32_t v_smem = kv_smem + (j & 1u) * STAGE_BYTES + KV_TILE_BYTES;
-            const uint32_t p_tmem = tmem_base + TMEM_P + (j & 1u) * (BKV / 2);
-            if (elect_one()) {
+            bool next_ready = false;
 #pragma unroll
-                for (uint32_t kk = 0; kk < BKV / 16; ++kk) {
-                    umma_f16_ts(tmem_base + TMEM_O, p_tmem + kk * 8,
-                                make_smem_desc_sw128(v_smem + kk * 2048, SUB_BYTES, 1024), IDESC_PV,
-                                (j | kk) != 0 ? 1u : 0u);
+            for (uint32_t t = 0; t < 2; ++t) {
+                if (j < nkv[t]) {
+                    if (!mbar_wait_bounded(p_full(t), j & 1u, abort_flag, p.status, SITE_P_FULL,
+                                           KERNEL_FLASH_ATTN)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    // O_t += P_t V_j : 8 steps of 16 along kv; P in tensor memory (8 columns per
+                    // step), V MN-major: 16 kv rows of 128 bytes per step, the two 64-column
+                    // halves SUB_BYTES apart
+                    const uint32_t v_smem = kv_smem + (j & 1u) * STAGE_BYTES + KV_TILE_BYTES;
+                    const uint32_t p_tmem = tmem_base + TMEM_S + t * BKV;
+                    const bool last_reader = (t == 1) || (j >= nkv[1]);
+                    if (elect_one()) {
+#pragma unroll
+                        for (uint32_t kk = 0; kk < BKV / 16; ++kk) {
+                            umma_f16_ts(tmem_base + TMEM_O + t * D, p_tmem + kk * 8,
+                                        make_smem_desc_sw128(v_smem + kk * 2048, SUB_BYTES, 1024),
+                                        IDESC_PV, (j | kk) != 0 ? 1u : 0u);
+                        }
+                        umma_commit(pv_done(t));
+                        if (last_reader)
+                            umma_commit(kv_empty(j & 1u));  // K_j and V_j have been consumed
+                    }
+                    __syncwarp();
                 }
-                umma_commit(kv_empty(j & 1u));
-                umma_commit(pv_done(j & 1u));
+                // scores of the next block for this tile, issued behind its P V so the other
+                // tile's softmax overlaps them (in-order execution on the tensor pipe makes the
+                // overwrite of P_t by S_t safe)
+                if (j + 1 < nkv[t]) {
+                    if (!next_ready) {
+                        if (!mbar_wait_bounded(kv_full((j + 1) & 1u), ((j + 1) >> 1) & 1u,
+                                               abort_flag, p.status, SITE_KV_FULL,
+                                               KERNEL_FLASH_ATTN)) {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after_sync();
+                        next_ready = true;
+                    }
+                    issue_qk(t, j + 1);
+                }
             }
-            __syncwarp();
         }
     } else {
-        // ------------------------------------------------------------ softmax + epilogue (warps 2..5)
+        // ------------------------------------------------------------ softmax + epilogue
+        const uint32_t t = (warp - 2) >> 2;  // query tile of this warp-group
         const uint32_t quarter = warp & 3u;
         const uint32_t lane_sel = (quarter * 32u) << 16;
         const uint32_t row_local = quarter * 32 + lane;
-        const uint32_t row = q0 + row_local;  // query index inside this (batch, head)
-        float m_ref = 0.0f;                   // max used in the exponent (log2 units)
+        const uint32_t row = q0 + t * BQ + row_local;  // query index inside this (batch, head)
+        const uint32_t my_kv = nkv[t];
+        const uint32_t s_tmem = tmem_base + TMEM_S + t * BKV + lane_sel;
+        const uint32_t o_tmem = tmem_base + TMEM_O + t * D + lane_sel;
+        float m_ref = 0.0f;  // max used in the exponent (log2 units)
         float l_sum = 0.0f;
         bool ok = true;
-        for (uint32_t j = 0; j < num_kv; ++j) {
-            if (!mbar_wait_bounded(s_full(j & 1u), (j >> 1) & 1u, abort_flag, p.status, SITE_S_FULL,
+        for (uint32_t j = 0; j < my_kv; ++j) {
+            if (!mbar_wait_bounded(s_full(t), j & 1u, abort_flag, p.status, SITE_S_FULL,
                                    KERNEL_FLASH_ATTN)) {
                 ok = false;
                 break;
             }
             tc_fence_after_sync();
-            const uint32_t s_tmem = tmem_base + TMEM_S + (j & 1u) * BKV + lane_sel;
             const uint32_t col_base = j * BKV;
             // columns allowed for this row: j_abs < seq_k and (causal) j_abs <= row
             uint32_t col_lim = p.seq_k;
             if (p.causal && row + 1 < col_lim)
                 col_lim = row + 1;
             const bool need_mask = col_base + BKV > col_lim;
-
             // only the diagonal block (causal) and the seq_k tail need per-element masks; the
             // test is made warp-uniform so the common blocks run mask-free code
             const bool blk_mask = __any_sync(0xffffffffu, need_mask);
@@ -322,16 +360,10 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
                 alpha = ex2_approx(m_ref - m_blk);
                 m_ref = m_blk;
             }
-            const bool any_rescale = __any_sync(0xffffffffu, alpha != 1.0f);
-            // P[j&1] was last read by the P V MMAs of block j-2; O by those of block j-1
-            if (j >= 2 && !mbar_wait_bounded(pv_done(j & 1u), ((j - 2) >> 1) & 1u, abort_flag,
-                                             p.status, SITE_PV_DONE, KERNEL_FLASH_ATTN)) {
-                ok = false;
-                break;
-            }
-            if (any_rescale) {
-                if (!mbar_wait_bounded(pv_done((j - 1) & 1u), ((j - 1) >> 1) & 1u, abort_flag,
-                                       p.status, SITE_PV_DONE, KERNEL_FLASH_ATTN)) {
+            if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+                // O_t was last written by the P V MMAs of block j-1
+                if (!mbar_wait_bounded(pv_done(t), (j - 1) & 1u, abort_flag, p.status, SITE_PV_DONE,
+                                       KERNEL_FLASH_ATTN)) {
                     ok = false;
                     break;
                 }
@@ -340,17 +372,18 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
 #pragma unroll 1
                 for (uint32_t c = 0; c < D / 32; ++c) {
                     uint32_t r[32];
-                    tmem_ld_32x32b_x32(tmem_base + TMEM_O + lane_sel + c * 32, r);
+                    tmem_ld_32x32b_x32(o_tmem + c * 32, r);
                     tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
                         r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                    tmem_st_32x32b_x32(tmem_base + TMEM_O + lane_sel + c * 32, r);
+                    tmem_st_32x32b_x32(o_tmem + c * 32, r);
                 }
                 tmem_st_wait();
             }
-            // ---- pass 2: p = 2^(s * scale - m_ref), row sum, f16 pairs into tensor memory
-            const uint32_t p_tmem = tmem_base + TMEM_P + (j & 1u) * (BKV / 2) + lane_sel;
+            // ---- pass 2: p = 2^(s * scale - m_ref), row sum, f16 pairs into tensor memory.  P
+            // overwrites the first 64 columns of S: chunk c of P covers S columns [16c, 16c+16),
+            // which this thread has already loaded (chunks ascend, the load completes first).
             float ls0 = 0.0f, ls1 = 0.0f, ls2 = 0.0f, ls3 = 0.0f;
 #pragma unroll 1
             for (uint32_t c = 0; c < BKV / 32; ++c) {
@@ -379,30 +412,28 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
                     pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&h01);
                     pk[(i >> 1) + 1] = *reinterpret_cast<const uint32_t*>(&h23);
                 }
-                tmem_st_32x32b_x16(p_tmem + c * 16, pk);
+                tmem_st_32x32b_x16(s_tmem + c * 16, pk);
             }
             l_sum += (ls0 + ls1) + (ls2 + ls3);
             tmem_st_wait();
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0)
-                mbar_arrive(p_full(j & 1u));
+                mbar_arrive(p_full(t));
         }
         // ---- epilogue: O / l -> global
-        if (ok && num_kv > 0) {
-            const uint32_t last = num_kv - 1;
-            ok = mbar_wait_bounded(pv_done(last & 1u), (last >> 1) & 1u, abort_flag, p.status,
-                                   SITE_PV_DONE, KERNEL_FLASH_ATTN);
-        }
-        if (ok) {
+        if (ok && my_kv > 0)
+            ok = mbar_wait_bounded(pv_done(t), (my_kv - 1) & 1u, abort_flag, p.status, SITE_PV_DONE,
+                                   KERNEL_FLASH_ATTN);
+        if (ok && q0 + t * BQ < p.seq_q) {
             tc_fence_after_sync();
             const float inv = l_sum > 0.0f ? 1.0f / l_sum : 0.0f;
             const size_t obase = (size_t)b * p.o_batch + (size_t)h * p.o_head + (size_t)row * p.o_row;
 #pragma unroll 1
             for (uint32_t c = 0; c < D / 32; ++c) {
                 uint32_t r[32];
-                if (num_kv > 0) {
-                    tmem_ld_32x32b_x32(tmem_base + TMEM_O + lane_sel + c * 32, r);
+                if (my_kv > 0) {
+                    tmem_ld_32x32b_x32(o_tmem + c * 32, r);
                     tmem_ld_wait();
                 } else {
 #pragma unroll
@@ -519,7 +550,7 @@ cudaError_t launch_flash_attention(const DeviceCtx& ctx, const AttnParams& ap, c
             return err;
         attr_set[ctx.device] = true;
     }
-    dim3 grid((ap.seq_q + BQ - 1) / BQ, ap.batch * ap.heads);
+    dim3 grid((ap.seq_q + 2 * BQ - 1) / (2 * BQ), ap.batch * ap.heads);
     flash_attention_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(maps, p);
     return cudaGetLastError();
 }
