@@ -391,6 +391,18 @@ static int32_t run_int8(int epi, const int8_t* a, size_t a_len, const int8_t* b,
                   "matmul_int8", "int8_generic");
 }
 
+// Largest M the fused-dequant W4A16 kernel takes; above it the weights are dequantised once to
+// f16 and the paired f16 GEMM runs.  KAIO_B200_FUSED_MAX_M overrides it (tuning aid).
+static uint32_t fused_max_m()
+{
+    static const uint32_t v = [] {
+        if (const char* e = getenv("KAIO_B200_FUSED_MAX_M"))
+            return (uint32_t)strtoul(e, nullptr, 10);
+        return 512u;
+    }();
+    return v;
+}
+
 static int32_t run_int4(const kaio_f16* a, size_t a_len, const uint32_t* b, size_t b_len,
                         const kaio_f16* scales, size_t s_len, void* c, size_t c_len, bool out_f16,
                         uint32_t m, uint32_t n, uint32_t k, uint32_t group_size, void* stream)
@@ -422,6 +434,9 @@ static int32_t run_int4(const kaio_f16* a, size_t a_len, const uint32_t* b, size
                                           ctx->tile_counters, s),
                       "matmul_int4", "w4a16_decode_splitk");
     }
+    if (m <= fused_max_m() && w4a16_fused_ok(x, &pr, 1, m, n, k))
+        return finish(launch_w4a16_fused(*ctx, x, &pr, 1, out_f16, m, n, k, s), "matmul_int4",
+                      "w4a16_fused_dequant");
     if (dq_gemm_fast_path_ok(WFMT_S4_PACKED, x, &pr, 1, out_f16, m, n, k)) {
         if ((rc = ensure_dq_workspace(ctx, dq_gemm_workspace_bytes(1, n, k))))
             return rc;
@@ -446,6 +461,10 @@ static int32_t run_qkv(int wfmt, const char* op, const __half* x, DqProblem prob
     if ((rc = get_ctx(&ctx)))
         return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (wfmt == WFMT_S4_PACKED && !post_scale && m <= fused_max_m() &&
+        w4a16_fused_ok(x, probs, 3, m, n, k))
+        return finish(launch_w4a16_fused(*ctx, x, probs, 3, true, m, n, k, s), op,
+                      "qkv_w4a16_fused_dequant");
     if (dq_gemm_fast_path_ok(wfmt, x, probs, 3, true, m, n, k)) {
         if ((rc = ensure_dq_workspace(ctx, dq_gemm_workspace_bytes(3, n, k))))
             return rc;

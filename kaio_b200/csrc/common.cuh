@@ -128,11 +128,11 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity
 constexpr uint32_t WAIT_HINT_NS = 20000;
 constexpr uint32_t WAIT_POLL_LIMIT = 1u << 20;
 
-// Returns true when the phase completed; false when this wait (or another
+// One lane's wait.  Returns true when the phase completed; false when this wait (or another
 // thread of the CTA, through *abort_flag) gave up.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
-                                                  volatile uint32_t* abort_flag, uint32_t* status,
-                                                  uint32_t site, uint32_t kernel_id)
+__device__ __forceinline__ bool mbar_wait_lane(uint32_t bar, uint32_t parity,
+                                               volatile uint32_t* abort_flag, uint32_t* status,
+                                               uint32_t site, uint32_t kernel_id)
 {
     if (mbar_try_wait(bar, parity))
         return true;
@@ -150,6 +150,20 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
     *abort_flag = 1;
     report_status(status, DEV_TIMEOUT, site, kernel_id);
     return false;
+}
+
+// WARP-COLLECTIVE wait: all 32 lanes of a warp call it together.  Lanes can leave the polling
+// loop at different times (one lane may have been busy arriving on another barrier), and the
+// loop's give-up exit keeps the compiler from re-converging them right behind it; the closing
+// vote does, and makes the outcome uniform.  The `.sync.aligned` tcgen05 instructions (ld, st,
+// alloc) that follow a wait need exactly that: executed by a diverged warp their result is
+// undefined (seen as a rare wrong value in the lane that had done the extra arrive).
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
+                                                  volatile uint32_t* abort_flag, uint32_t* status,
+                                                  uint32_t site, uint32_t kernel_id)
+{
+    const bool ok = mbar_wait_lane(bar, parity, abort_flag, status, site, kernel_id);
+    return __all_sync(0xffffffffu, ok);
 }
 
 // ---------------------------------------------------------------- TMA
@@ -341,11 +355,12 @@ __device__ __forceinline__ void cluster_sync_all()
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-// Wait on a local mbarrier whose arrivals may come from the peer CTA (cluster-scope acquire).
-__device__ __forceinline__ bool mbar_wait_bounded_cluster(uint32_t bar, uint32_t parity,
-                                                          volatile uint32_t* abort_flag,
-                                                          uint32_t* status, uint32_t site,
-                                                          uint32_t kernel_id)
+// One lane's wait on a local mbarrier whose arrivals may come from the peer CTA (cluster-scope
+// acquire).
+__device__ __forceinline__ bool mbar_wait_lane_cluster(uint32_t bar, uint32_t parity,
+                                                       volatile uint32_t* abort_flag,
+                                                       uint32_t* status, uint32_t site,
+                                                       uint32_t kernel_id)
 {
     const unsigned long long t_start = clock64();
     for (uint32_t it = 0; it < WAIT_POLL_LIMIT; ++it) {
@@ -369,6 +384,16 @@ __device__ __forceinline__ bool mbar_wait_bounded_cluster(uint32_t bar, uint32_t
     *abort_flag = 1;
     report_status(status, DEV_TIMEOUT, site, kernel_id);
     return false;
+}
+
+// Warp-collective form (see mbar_wait_bounded).
+__device__ __forceinline__ bool mbar_wait_bounded_cluster(uint32_t bar, uint32_t parity,
+                                                          volatile uint32_t* abort_flag,
+                                                          uint32_t* status, uint32_t site,
+                                                          uint32_t kernel_id)
+{
+    const bool ok = mbar_wait_lane_cluster(bar, parity, abort_flag, status, site, kernel_id);
+    return __all_sync(0xffffffffu, ok);
 }
 
 // 2-D tiled load global -> this CTA's shared memory whose completion bytes are credited to an

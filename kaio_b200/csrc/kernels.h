@@ -81,6 +81,14 @@ cudaError_t launch_w4a16_decode(const DeviceCtx& ctx, const __half* x, const DqP
                                 uint32_t* counters, cudaStream_t stream,
                                 const OutputCopies* copies = nullptr);
 
+// Fused W4A16 GEMM for m > 16: int4 -> f16 dequantisation inside the GEMM (weights go from the
+// packed words to tensor memory, never to global memory as f16).  Needs no workspace.
+bool w4a16_fused_ok(const void* x, const DqProblem* probs, int num_probs, uint32_t m, uint32_t n,
+                    uint32_t k);
+cudaError_t launch_w4a16_fused(const DeviceCtx& ctx, const __half* x, const DqProblem* probs,
+                               int num_probs, bool out_f16, uint32_t m, uint32_t n, uint32_t k,
+                               cudaStream_t stream);
+
 bool dq_gemm_fast_path_ok(int wfmt, const void* x, const DqProblem* probs, int num_probs,
                           bool out_f16, uint32_t m, uint32_t n, uint32_t k);
 // Destinations of a single-output GEMM: the [m, n] result is stored to every ptrs[r] (already

@@ -22,19 +22,19 @@
 //   the last one to arrive sums the partials in ascending CTA order -- a fixed order, so the
 //   result does not depend on timing -- and writes the output.
 //
-// CTA = 26 warps:
+// CTA = 18 warps:
 //   warp 0       TMA producer: one box [128 columns][128 B = 256 k] of packed weights per stage,
 //                128-byte swizzle, L2 evict-first, 6-stage ring.
 //   warp 1       MMA issuer: 16 x tcgen05.mma kind::f16 (M128 N16 K16) per stage, A from tensor
 //                memory, B (activations) from shared memory; D double-buffered in tensor memory.
-//   warps 2,3,24,25  loaders: the stage's activation slice, written in the UMMA K-major
+//   warps 2,3,16,17  loaders: the stage's activation slice, written in the UMMA K-major
 //                128-byte-swizzle layout with each group of 8 k permuted to the order the
 //                dequantiser emits, and the stage's 2 x 128 group scales.
-//   warps 4-19   dequantisers: thread = weight column = tensor-memory lane (four warps per
-//                lane quarter, each taking 64 of the stage's 256 k).  16-byte
+//   warps 4-11   dequantisers: thread = weight column = tensor-memory lane (two warps per
+//                lane quarter, each taking one 128-k scale group of the stage).  16-byte
 //                conflict-free reads of the packed nibbles, 0x6400 magic-number conversion
 //                (exact), hmul2 by the group scale (the reference's rounding), tcgen05.st.
-//   warps 20-23  epilogue: tcgen05.ld of D^T (thread = column, 16 rows), split-K fix-up,
+//   warps 12-15  epilogue: tcgen05.ld of D^T (thread = column, 16 rows), split-K fix-up,
 //                coalesced stores.
 #include "common.cuh"
 #include "kernels.h"
@@ -52,8 +52,8 @@ constexpr int X_BYTES = NROWS * BKK * 2;  // 8 KiB activations, 4 sub-tiles [16 
 constexpr int S_BYTES = 2 * BN * 2;     // 512 B: 2 groups x 128 columns f16
 constexpr int STAGE_BYTES = 25 * 1024;  // W | X | scales, padded to keep W and X 1024-aligned
 constexpr int NUM_LOADER_WARPS = 4;
-constexpr int NUM_DEQUANT_WARPS = 16;
-constexpr int NUM_WARPS = 26;
+constexpr int NUM_DEQUANT_WARPS = 8;
+constexpr int NUM_WARPS = 18;
 constexpr int NUM_THREADS = NUM_WARPS * 32;
 constexpr int NUM_BARRIERS = 3 * STAGES + A_SLOTS + 4;
 constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + NUM_BARRIERS * 8 + 64;
@@ -344,9 +344,9 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const Params p)
             }
         }
         (void)ph;
-    } else if (warp == 2 || warp == 3 || warp == 24 || warp == 25) {
+    } else if (warp == 2 || warp == 3 || warp == 16 || warp == 17) {
         // ------------------------------------------------------------ activation / scale loaders
-        const uint32_t lw = warp < 4 ? warp - 2 : warp - 22;
+        const uint32_t lw = warp < 4 ? warp - 2 : warp - 14;
         const uint32_t groups = p.k >> 7;
         for (uint32_t it = lw; u_begin + it < u_end; it += NUM_LOADER_WARPS) {
             const uint32_t u = u_begin + it;
@@ -411,11 +411,18 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const Params p)
                 KAIO_STAMP(it, 1);
             }
         }
-    } else if (warp >= 4 && warp < 20) {
+    } else if (warp >= 4 && warp < 12) {
         // ------------------------------------------------------------ dequantisers
         const uint32_t q = warp & 3u;          // tensor-memory lane quarter of this warp
-        const uint32_t wg = (warp - 4) >> 2;   // which 64-k quarter of the stage (2 chunks of 32 k)
+        const uint32_t wg = (warp - 4) >> 2;   // which 128-k half (= scale group) of the stage
         const uint32_t row = q * 32 + lane;    // weight column inside the tile = TMEM lane
+        // loop-invariant offsets: this thread's four 16-byte chunks and its group scale
+        uint32_t w_off[4];
+#pragma unroll
+        for (uint32_t c = 0; c < 4; ++c)
+            w_off[c] = sw128_offset(row, wg * 4 + c);
+        const uint32_t sc_off = (wg * BN + row) * 2;
+        const uint32_t a_lane = tmem_base + ((q * 32u) << 16) + TMEM_A_COL + wg * 64;
         uint32_t it = 0;
         for (uint32_t u = u_begin; u < u_end; ++u, ++it) {
             const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
@@ -427,15 +434,12 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const Params p)
             if (warp == 4 && lane == 0)
                 KAIO_STAMP(it, 2);
             const uint8_t* stage = smem_gen + s * STAGE_BYTES;
-            const __half* s_s = reinterpret_cast<const __half*>(stage + W_BYTES + X_BYTES);
-            uint4 wv[2];
+            uint4 wv[4];
 #pragma unroll
-            for (uint32_t c = 0; c < 2; ++c)
-                wv[c] = *reinterpret_cast<const uint4*>(stage + sw128_offset(row, wg * 2 + c));
-            const __half2 sc = __half2half2(s_s[(wg >> 1) * BN + row]);
-            __syncwarp();
-            if (lane == 0)
-                mbar_arrive(w_empty(s));  // packed weights and scales of this stage are in registers
+            for (uint32_t c = 0; c < 4; ++c)
+                wv[c] = *reinterpret_cast<const uint4*>(stage + w_off[c]);
+            const __half2 sc =
+                __half2half2(*reinterpret_cast<const __half*>(stage + W_BYTES + X_BYTES + sc_off));
             // the tensor-memory block is free once the MMAs of unit it - A_SLOTS have retired
             if (it >= A_SLOTS) {
                 const uint32_t pit = it - A_SLOTS;
@@ -446,10 +450,9 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const Params p)
             tc_fence_after_sync();
             if (warp == 4 && lane == 0)
                 KAIO_STAMP(it, 3);
-            const uint32_t a_tmem =
-                tmem_base + ((q * 32u) << 16) + TMEM_A_COL + t * (BKK / 2) + wg * 32;
+            const uint32_t a_tmem = a_lane + t * (BKK / 2);
 #pragma unroll
-            for (uint32_t c = 0; c < 2; ++c) {
+            for (uint32_t c = 0; c < 4; ++c) {
                 uint32_t r[16];
                 dequant8(wv[c].x, sc, r[0], r[1], r[2], r[3]);
                 dequant8(wv[c].y, sc, r[4], r[5], r[6], r[7]);
@@ -460,15 +463,23 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const Params p)
             tmem_st_wait();
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0)
+            if (lane == 0) {
+                // The stage is released only here, behind the instructions that consumed the
+                // loaded words.  Releasing it right after the loads is not safe: nothing in the
+                // instruction stream then ties a load to the arrive, a load scheduled close to
+                // its use ran about a microsecond after the arrive, and the refill of the stage
+                // (six units ahead) occasionally landed first -- seen as a few columns computed
+                // from the wrong k block once in several hundred launches.
+                mbar_arrive(w_empty(s));
                 mbar_arrive(a_full(t));
+            }
 #ifdef KAIO_TRACE
             if (lane == 0 && trace_ptr && it < 16)
                 atomicMax(&trace_ptr[it * 8 + 4], (unsigned long long)clock64());
 #endif
         }
     } else {
-        // ------------------------------------------------------------ epilogue (warps 20..23)
+        // ------------------------------------------------------------ epilogue (warps 12..15)
         const uint32_t q = warp & 3u;
         const uint32_t tid = q * 32 + lane;  // weight column inside the tile = TMEM lane
         uint32_t seg = 0;

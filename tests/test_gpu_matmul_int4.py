@@ -104,6 +104,44 @@ def test_decode_shapes(oracle, m, n, k, f16_out):
     run(oracle, m, n, k, w, a, scales, f16_out=f16_out)
 
 
+@pytest.mark.parametrize("m", [17, 32, 33, 64, 100, 128, 129, 256, 257, 500])
+@pytest.mark.parametrize("n,k", [(200, 384), (1000, 1024), (4096, 2048)])
+def test_fused_dequant_shapes(oracle, m, n, k):
+    """16 < M <= 512 runs the kernel that dequantises inside the GEMM: every row-tile width
+    (32 / 64 / 128 / 256 rows, one and several row tiles), ragged rows and columns."""
+    rng = np.random.default_rng(m * 7 + n + k)
+    w = rng.integers(-8, 8, k * n, dtype=np.int8)
+    a = rng.standard_normal(m * k).astype(np.float16)
+    scales = rng.uniform(0.005, 0.02, (k // G) * n).astype(np.float16)
+    run(oracle, m, n, k, w, a, scales, f16_out=(m % 2 == 0))
+    assert ops.last_variant() == "w4a16_fused_dequant"
+
+
+def test_decode_is_repeatable():
+    """The split-K decode kernel sums its partial tiles in a fixed order, so repeated launches
+    must agree bit for bit.  Hundreds of launches with varying gaps between them: a stage of the
+    weight ring released too early once showed up as a few wrong columns in about one launch
+    of 400 on this shape."""
+    m, n, k = 16, 11008, 4096
+    g = torch.Generator(device="cuda").manual_seed(5)
+    w = torch.randint(-2**31, 2**31 - 1, (k // 8 * n,), dtype=torch.int32, device="cuda", generator=g)
+    scales = (torch.rand(k // G * n, device="cuda", generator=g) * 0.015 + 0.005).half()
+    a = torch.randn(m * k, device="cuda", generator=g).half()
+    first = None
+    for it in range(600):
+        c = torch.full((m * n,), float("nan"), device="cuda")
+        if it % 3 == 1:
+            torch.cuda.synchronize()
+        if it % 5 == 2:
+            torch.randn(1 << 20, device="cuda").sum()
+        ops.matmul_int4(device(), a, w, scales, c, m, n, k, G)
+        if first is None:
+            first = c
+        else:
+            assert torch.equal(c, first), f"launch {it} differs from launch 0"
+    assert ops.device_status(device())[0] == 0
+
+
 @pytest.mark.parametrize("m,n,k", [(48, 512, 1024), (300, 384, 640), (1024, 256, 4096)])
 def test_prefill_shapes(oracle, m, n, k):
     rng = np.random.default_rng(n + k)
