@@ -31,7 +31,7 @@ namespace w4f {
 
 constexpr int BN = 128;   // weight columns per tile = UMMA M
 constexpr int BKS = 64;   // k per stage
-constexpr int A_SLOTS = 4;  // tensor-memory ring of dequantised blocks (32 columns each)
+constexpr int A_SLOTS = 8;  // tensor-memory ring of dequantised blocks (32 columns each)
 constexpr int W_BYTES = BN * (BKS / 2);  // 4 KiB packed weights per stage
 constexpr int SC_BYTES = BN * 2;         // one scale group x 128 columns (every second stage)
 constexpr int NUM_THREADS = 448;
@@ -45,11 +45,11 @@ struct Cfg {
     static constexpr int X_BYTES = NROWS * 128;  // [NROWS rows][64 k f16]
     static constexpr int STAGE_BYTES = X_BYTES + W_BYTES + SC_BYTES;
     static constexpr int TMA_BYTES = X_BYTES + W_BYTES;  // without the scales
-    // as many stages as fit in ~200 KB, a multiple of A_SLOTS, at most 12
+    // as many stages as fit in ~200 KB, at most 12
     static constexpr int RAW = (200 * 1024) / STAGE_BYTES;
     static constexpr int STAGES = RAW >= 12 ? 12 : (RAW >= 8 ? 8 : 4);
     static constexpr int NBUF = NROWS <= 128 ? 2 : 1;  // D buffers in tensor memory
-    static constexpr int NUM_BARS = 2 * STAGES + A_SLOTS + 4;
+    static constexpr int NUM_BARS = 2 * STAGES + 2 * A_SLOTS + 4;
     static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + NUM_BARS * 8 + 64;
     static constexpr uint32_t IDESC = make_idesc(/*d=f32*/ 1, /*a=f16*/ 0, /*b=f16*/ 0,
                                                  /*a K-major*/ 0, /*b K-major*/ 0, BN, NROWS);
@@ -151,12 +151,13 @@ w4a16_fused_kernel(const __grid_constant__ TensorMaps maps, const Params p)
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + STAGES * C::STAGE_BYTES);
     const uint32_t bar_base = smem_base + STAGES * C::STAGE_BYTES;
     auto full_bar = [&](uint32_t s) { return bar_base + 8u * s; };
-    // mma_done[s]: the MMAs of the stage that used ring slot s have retired (frees the slot's
-    // shared memory and, A_SLOTS stages later at the latest, its tensor-memory block)
+    // mma_done[s]: the MMAs that read shared-memory stage s have retired;  a_free[t]: the MMAs
+    // that read tensor-memory block t have retired (the two rings have different depths)
     auto mma_done = [&](uint32_t s) { return bar_base + 8u * (STAGES + s); };
     auto a_full = [&](uint32_t t) { return bar_base + 8u * (2 * STAGES + t); };
-    auto d_full = [&](uint32_t b) { return bar_base + 8u * (2 * STAGES + A_SLOTS + b); };
-    auto d_empty = [&](uint32_t b) { return bar_base + 8u * (2 * STAGES + A_SLOTS + 2 + b); };
+    auto a_free = [&](uint32_t t) { return bar_base + 8u * (2 * STAGES + A_SLOTS + t); };
+    auto d_full = [&](uint32_t b) { return bar_base + 8u * (2 * STAGES + 2 * A_SLOTS + b); };
+    auto d_empty = [&](uint32_t b) { return bar_base + 8u * (2 * STAGES + 2 * A_SLOTS + 2 + b); };
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + C::NUM_BARS);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -183,8 +184,10 @@ w4a16_fused_kernel(const __grid_constant__ TensorMaps maps, const Params p)
             mbar_init(full_bar(s), 1);
             mbar_init(mma_done(s), 1);
         }
-        for (uint32_t t = 0; t < (uint32_t)A_SLOTS; ++t)
+        for (uint32_t t = 0; t < (uint32_t)A_SLOTS; ++t) {
             mbar_init(a_full(t), NUM_DEQUANT_WARPS);
+            mbar_init(a_free(t), 1);
+        }
         for (uint32_t b = 0; b < 2; ++b) {
             mbar_init(d_full(b), 1);
             mbar_init(d_empty(b), 4);
@@ -271,6 +274,7 @@ w4a16_fused_kernel(const __grid_constant__ TensorMaps maps, const Params p)
                         umma_f16_ts(d_tmem, a_tmem + kk * 8, b_desc0 + (uint64_t)(kk * 2), C::IDESC,
                                     (kb | kk) != 0 ? 1u : 0u);
                     umma_commit(mma_done(s));
+                    umma_commit(a_free(t));
                     if (kb + 1 == num_kb)
                         umma_commit(d_full(buf));
                 }
@@ -292,12 +296,11 @@ w4a16_fused_kernel(const __grid_constant__ TensorMaps maps, const Params p)
         const uint32_t w_off = row * 32 + ((kh ^ ((row >> 2) & 1u)) << 4);
         const uint32_t a_lane = tmem_base + ((q * 32u) << 16) + TMEM_A_COL + kh * 16;
         const uint32_t sc_off = STAGES * (C::X_BYTES + W_BYTES) + row * 2;
-        uint32_t it = 0, s = 0, ph = 0, t = 0;
-        uint32_t ps = 0, pph = 0;  // ring position of stage it - A_SLOTS
+        uint32_t s = 0, ph = 0, t = 0, tph = 0;
         bool ok = true;
         __half2 sc = __half2half2(__float2half(0.0f));
         for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-            for (uint32_t kb = 0; kb < num_kb; ++kb, ++it) {
+            for (uint32_t kb = 0; kb < num_kb; ++kb) {
                 if (!mbar_wait_bounded(full_bar(s), ph, abort_flag, p.status, SITE_FULL,
                                        KERNEL_DQ_GEMM)) {
                     ok = false;
@@ -309,16 +312,10 @@ w4a16_fused_kernel(const __grid_constant__ TensorMaps maps, const Params p)
                     sc = __half2half2(
                         *reinterpret_cast<const __half*>(smem_gen + sc_off + s * SC_BYTES));
                 // the tensor-memory block is free once the MMAs of stage it - A_SLOTS retired
-                if (it >= (uint32_t)A_SLOTS) {
-                    if (!mbar_wait_bounded(mma_done(ps), pph, abort_flag, p.status, SITE_A_FREE,
-                                           KERNEL_DQ_GEMM)) {
-                        ok = false;
-                        break;
-                    }
-                    if (++ps == (uint32_t)STAGES) {
-                        ps = 0;
-                        pph ^= 1u;
-                    }
+                if (!mbar_wait_bounded(a_free(t), tph ^ 1u, abort_flag, p.status, SITE_A_FREE,
+                                       KERNEL_DQ_GEMM)) {
+                    ok = false;
+                    break;
                 }
                 tc_fence_after_sync();
                 uint32_t r[16];
@@ -341,7 +338,10 @@ w4a16_fused_kernel(const __grid_constant__ TensorMaps maps, const Params p)
                     s = 0;
                     ph ^= 1u;
                 }
-                t = (t + 1) & (A_SLOTS - 1);
+                if (++t == (uint32_t)A_SLOTS) {
+                    t = 0;
+                    tph ^= 1u;
+                }
             }
         }
     } else {
