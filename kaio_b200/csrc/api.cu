@@ -434,9 +434,15 @@ static int32_t run_int4(const kaio_f16* a, size_t a_len, const uint32_t* b, size
                                           ctx->tile_counters, s),
                       "matmul_int4", "w4a16_decode_splitk");
     }
-    if (m <= fused_max_m() && w4a16_fused_ok(x, &pr, 1, m, n, k))
-        return finish(launch_w4a16_fused(*ctx, x, &pr, 1, out_f16, m, n, k, s), "matmul_int4",
-                      "w4a16_fused_dequant");
+    if (m <= fused_max_m() && w4a16_fused_ok(x, &pr, 1, m, n, k)) {
+        const size_t ws = w4a16_fused_workspace_bytes(*ctx, 1, m, n, k);
+        if (ws && (rc = ensure_workspace(ctx, ws, w4a16_fused_num_counters(*ctx, 1, m, n, k))))
+            return rc;
+        return finish(launch_w4a16_fused(*ctx, x, &pr, 1, out_f16, m, n, k,
+                                         ws ? ctx->workspace : nullptr,
+                                         ws ? ctx->tile_counters : nullptr, s),
+                      "matmul_int4", ws ? "w4a16_fused_dequant_splitk" : "w4a16_fused_dequant");
+    }
     if (dq_gemm_fast_path_ok(WFMT_S4_PACKED, x, &pr, 1, out_f16, m, n, k)) {
         if ((rc = ensure_dq_workspace(ctx, dq_gemm_workspace_bytes(1, n, k))))
             return rc;
@@ -462,9 +468,15 @@ static int32_t run_qkv(int wfmt, const char* op, const __half* x, DqProblem prob
         return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (wfmt == WFMT_S4_PACKED && !post_scale && m <= fused_max_m() &&
-        w4a16_fused_ok(x, probs, 3, m, n, k))
-        return finish(launch_w4a16_fused(*ctx, x, probs, 3, true, m, n, k, s), op,
-                      "qkv_w4a16_fused_dequant");
+        w4a16_fused_ok(x, probs, 3, m, n, k)) {
+        const size_t ws = w4a16_fused_workspace_bytes(*ctx, 3, m, n, k);
+        if (ws && (rc = ensure_workspace(ctx, ws, w4a16_fused_num_counters(*ctx, 3, m, n, k))))
+            return rc;
+        return finish(launch_w4a16_fused(*ctx, x, probs, 3, true, m, n, k,
+                                         ws ? ctx->workspace : nullptr,
+                                         ws ? ctx->tile_counters : nullptr, s),
+                      op, ws ? "qkv_w4a16_fused_dequant_splitk" : "qkv_w4a16_fused_dequant");
+    }
     if (dq_gemm_fast_path_ok(wfmt, x, probs, 3, true, m, n, k)) {
         if ((rc = ensure_dq_workspace(ctx, dq_gemm_workspace_bytes(3, n, k))))
             return rc;

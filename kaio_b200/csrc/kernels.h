@@ -85,9 +85,15 @@ cudaError_t launch_w4a16_decode(const DeviceCtx& ctx, const __half* x, const DqP
 // packed words to tensor memory, never to global memory as f16).  Needs no workspace.
 bool w4a16_fused_ok(const void* x, const DqProblem* probs, int num_probs, uint32_t m, uint32_t n,
                     uint32_t k);
+// Scratch of its stream-K form (f32 partial tiles + arrival counters); 0 when the column tiles
+// fill the SMs well enough.  Without scratch (nullptr) every tile runs whole on one CTA.
+size_t w4a16_fused_workspace_bytes(const DeviceCtx& ctx, int num_probs, uint32_t m, uint32_t n,
+                                   uint32_t k);
+size_t w4a16_fused_num_counters(const DeviceCtx& ctx, int num_probs, uint32_t m, uint32_t n,
+                                uint32_t k);
 cudaError_t launch_w4a16_fused(const DeviceCtx& ctx, const __half* x, const DqProblem* probs,
                                int num_probs, bool out_f16, uint32_t m, uint32_t n, uint32_t k,
-                               cudaStream_t stream);
+                               void* workspace, uint32_t* counters, cudaStream_t stream);
 
 bool dq_gemm_fast_path_ok(int wfmt, const void* x, const DqProblem* probs, int num_probs,
                           bool out_f16, uint32_t m, uint32_t n, uint32_t k);

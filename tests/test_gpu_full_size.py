@@ -120,7 +120,7 @@ def test_w4a16_ffn70b_config5_sampled_rows(oracle, m, k, n):
     c = torch.empty(m * n, device="cuda", dtype=torch.float16)
     ops.matmul_int4(device(), dev(a), dev(packed), dev(s), c, m, n, k, G)
     # M <= 512 dequantises inside the GEMM; larger M dequantises once, then runs the f16 GEMM
-    assert ops.last_variant() == ("w4a16_fused_dequant" if m <= 512 else "w4a16_tcgen05")
+    assert ops.last_variant().startswith("w4a16_fused_dequant" if m <= 512 else "w4a16_tcgen05")
     rows = [0, m // 2, m - 1]
     want = oracle.matmul_int4(a[rows], packed, s, len(rows), n, k, f16_out=True)
     assert max_rel(host(c.view(m, n)[rows]), want) < 2e-2
