@@ -869,6 +869,15 @@ KAIO_API int32_t kaio_b200_matmul_int4_allgather(const kaio_f16* a, size_t a_len
                                           ctx->tile_counters, s, &copies),
                       op, "w4a16_decode_splitk_allgather");
     }
+    if (m <= fused_max_m() && w4a16_fused_ok(x, &pr, 1, m, n_loc, k)) {
+        const size_t ws = w4a16_fused_workspace_bytes(*ctx, 1, m, n_loc, k);
+        if (ws && (rc = ensure_workspace(ctx, ws, w4a16_fused_num_counters(*ctx, 1, m, n_loc, k))))
+            return rc;
+        return finish(launch_w4a16_fused(*ctx, x, &pr, 1, true, m, n_loc, k,
+                                         ws ? ctx->workspace : nullptr,
+                                         ws ? ctx->tile_counters : nullptr, s, &copies),
+                      op, "w4a16_fused_dequant_allgather");
+    }
     if (!dq_gemm_fast_path_ok(WFMT_S4_PACKED, x, &pr, 1, true, m, n_loc, k))
         return fail(KAIO_B200_ERR_INVALID_CONFIG,
                     "%s: A, B packed and the outputs must be 16-byte aligned", op);

@@ -93,7 +93,8 @@ size_t w4a16_fused_num_counters(const DeviceCtx& ctx, int num_probs, uint32_t m,
                                 uint32_t k);
 cudaError_t launch_w4a16_fused(const DeviceCtx& ctx, const __half* x, const DqProblem* probs,
                                int num_probs, bool out_f16, uint32_t m, uint32_t n, uint32_t k,
-                               void* workspace, uint32_t* counters, cudaStream_t stream);
+                               void* workspace, uint32_t* counters, cudaStream_t stream,
+                               const OutputCopies* copies = nullptr);
 
 bool dq_gemm_fast_path_ok(int wfmt, const void* x, const DqProblem* probs, int num_probs,
                           bool out_f16, uint32_t m, uint32_t n, uint32_t k);

@@ -79,6 +79,11 @@ struct Params {
     uint32_t num_probs;
     uint32_t m, n, k;
     int out_f16;
+    // Single-projection calls may store the result to several destinations (the sharded
+    // all-gather form: every rank's output buffer, peer memory); row stride `ld` elements.
+    void* copies[8];
+    uint32_t num_copies;  // 0 = store to probs[prob].out with row stride n
+    uint64_t ld;
     // Stream-K (one row tile, too few column tiles to fill the SMs): the (tile, k stage) units
     // are cut into gridDim contiguous ranges; a tile that a cut splits is summed from f32 partial
     // tiles in a workspace by the last CTA to arrive, in ascending CTA order (deterministic).
@@ -469,18 +474,22 @@ w4a16_fused_kernel(const __grid_constant__ TensorMaps maps, const Params p)
             const uint32_t taddr = tmem_base + ((q * 32u) << 16) + buf * NROWS;
             // rows [m0 + c * 32, +32) of this thread's column, f32 -> output
             auto store_rows = [&](const uint32_t (&r)[32], uint32_t c) {
-                if (col < p.n) {
+                if (col >= p.n)
+                    return;
+                const uint32_t nd = p.num_copies ? p.num_copies : 1u;
+                for (uint32_t d = 0; d < nd; ++d) {
+                    void* const dst = p.num_copies ? p.copies[d] : p.probs[prob].out;
+                    const size_t ld = p.num_copies ? (size_t)p.ld : (size_t)p.n;
 #pragma unroll
                     for (uint32_t i = 0; i < 32; ++i) {
                         const uint32_t rr = m0 + c * 32 + i;
                         if (rr < p.m) {
-                            const size_t idx = (size_t)rr * p.n + col;
+                            const size_t idx = (size_t)rr * ld + col;
                             if (p.out_f16)
-                                reinterpret_cast<__half*>(p.probs[prob].out)[idx] =
+                                reinterpret_cast<__half*>(dst)[idx] =
                                     __float2half_rn(__uint_as_float(r[i]));
                             else
-                                reinterpret_cast<float*>(p.probs[prob].out)[idx] =
-                                    __uint_as_float(r[i]);
+                                reinterpret_cast<float*>(dst)[idx] = __uint_as_float(r[i]);
                         }
                     }
                 }
@@ -638,7 +647,8 @@ size_t w4a16_fused_num_counters(const DeviceCtx& ctx, int num_probs, uint32_t m,
 template <int NROWS, int BKS>
 static cudaError_t launch_fused_n(const DeviceCtx& ctx, const __half* x, const DqProblem* probs,
                                   int num_probs, bool out_f16, uint32_t m, uint32_t n, uint32_t k,
-                                  void* workspace, uint32_t* counters, cudaStream_t stream)
+                                  void* workspace, uint32_t* counters, cudaStream_t stream,
+                                  const OutputCopies* copies)
 {
     using namespace w4f;
     using C = Cfg<NROWS, BKS>;
@@ -672,6 +682,12 @@ static cudaError_t launch_fused_n(const DeviceCtx& ctx, const __half* x, const D
     p.n = n;
     p.k = k;
     p.out_f16 = out_f16 ? 1 : 0;
+    if (copies != nullptr && num_probs == 1) {
+        for (uint32_t i = 0; i < copies->count && i < 8; ++i)
+            p.copies[i] = copies->ptrs[i];
+        p.num_copies = copies->count;
+        p.ld = copies->ld;
+    }
     p.status = ctx.status;
     const uint32_t tiles = ((m + NROWS - 1) / NROWS) * ((n + BN - 1) / BN) * (uint32_t)num_probs;
     uint32_t grid = tiles < (uint32_t)ctx.num_sms ? tiles : (uint32_t)ctx.num_sms;
@@ -697,19 +713,20 @@ static cudaError_t launch_fused_n(const DeviceCtx& ctx, const __half* x, const D
 
 cudaError_t launch_w4a16_fused(const DeviceCtx& ctx, const __half* x, const DqProblem* probs,
                                int num_probs, bool out_f16, uint32_t m, uint32_t n, uint32_t k,
-                               void* workspace, uint32_t* counters, cudaStream_t stream)
+                               void* workspace, uint32_t* counters, cudaStream_t stream,
+                               const OutputCopies* copies)
 {
     if (m <= 32)
         return launch_fused_n<32, 256>(ctx, x, probs, num_probs, out_f16, m, n, k, workspace,
-                                       counters, stream);
+                                       counters, stream, copies);
     if (m <= 64)
         return launch_fused_n<64, 256>(ctx, x, probs, num_probs, out_f16, m, n, k, workspace,
-                                       counters, stream);
+                                       counters, stream, copies);
     if (m <= 128)
         return launch_fused_n<128, 128>(ctx, x, probs, num_probs, out_f16, m, n, k, workspace,
-                                        counters, stream);
+                                        counters, stream, copies);
     return launch_fused_n<256, 64>(ctx, x, probs, num_probs, out_f16, m, n, k, workspace, counters,
-                                   stream);
+                                   stream, copies);
 }
 
 }  // namespace kaio
