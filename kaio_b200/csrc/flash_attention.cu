@@ -20,7 +20,7 @@
 //              softmax runs, the tensor pipe works on the other tile.
 //   warps 2-5  softmax of tile 0, warps 6-9 softmax of tile 1: thread = query row.  tcgen05.ld of
 //              the score row, block max (four independent chains), running max with lazy rescale
-//              (O and the row sum are rescaled only when the max grows by more than 2^8),
+//              (O and the row sum are rescaled only when the max grows by more than 2^13),
 //              ex2(s * log2(e)/sqrt(d) - max), row sum, P packed to f16 and stored to tensor
 //              memory; at the end O / sum -> global.  Two warps per scheduler hide each other's
 //              dependent chains; a single softmax warp-group left the tensor pipe 27 % busy.
@@ -352,11 +352,13 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
                 }
             }
             const float m_blk = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
-            // ---- lazy rescale: keep the old reference unless the max grew by more than 2^8
+            // ---- lazy rescale: keep the old reference unless the max grew by more than 2^13
+            // (P = 2^(s - m_ref) then stays below 2^13 = 8192, well inside f16, and keeps the
+            // f16 relative precision; the row sum and O are f32)
             float alpha = 1.0f;
             if (j == 0) {
                 m_ref = (m_blk == -INFINITY) ? 0.0f : m_blk;
-            } else if (m_blk > m_ref + 8.0f) {
+            } else if (m_blk > m_ref + 13.0f) {
                 alpha = ex2_approx(m_ref - m_blk);
                 m_ref = m_blk;
             }
