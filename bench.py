@@ -186,6 +186,8 @@ def main():
                     help="run only the W4A16 decode leg and print its JSON (profiling aid)")
     ap.add_argument("--qkv-attention-only", action="store_true",
                     help="run only the fused-QKV + attention leg and print its JSON (profiling aid)")
+    ap.add_argument("--ffn70b-only", action="store_true",
+                    help="run only the 70B FFN W4A16 leg and print its JSON (profiling aid)")
     ap.add_argument("--skip-extras", action="store_true",
                     help="only the headline step (no decode / e2e / cpu baseline legs)")
     args = ap.parse_args()
@@ -216,6 +218,13 @@ def main():
         return
     if args.qkv_attention_only:
         print(json.dumps({"qkv_attention": bench_qkv_attention(torch, ops, dev, peaks)}), flush=True)
+        return
+    if args.ffn70b_only:
+        res = bench_ffn70b(torch, dist, ops, sharding, dev, rank, world)
+        if rank == 0:
+            print(json.dumps({"ffn70b_w4a16": res}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
         return
 
     # ---- synthetic inputs (seeded; config 3 value ranges), resident in HBM
