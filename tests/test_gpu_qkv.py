@@ -99,6 +99,8 @@ INT4_CASES = [  # qkv_project_int4_e2e.rs:263-310
     (64, 16, 128, 0xA1), (64, 16, 256, 0xA2), (64, 16, 1024, 0xA3), (64, 64, 128, 0xA4),
     (128, 32, 128, 0xA5), (128, 128, 256, 0xA6),
     (200, 256, 1024, 0xA7), (1024, 512, 2048, 0xA8), (130, 136, 384, 0xA9),
+    # decode-like fused QKV: few column tiles and a long K (the fused-dequant kernel runs stream-K)
+    (64, 512, 4096, 0xAA), (24, 256, 8192, 0xAB),
 ]
 
 
