@@ -84,8 +84,8 @@ struct Params {
     void* copies[8];
     uint32_t num_copies;  // 0 = store to probs[prob].out with row stride n
     uint64_t ld;
-    // Stream-K (one row tile, too few column tiles to fill the SMs): the (tile, k stage) units
-    // are cut into gridDim contiguous ranges; a tile that a cut splits is summed from f32 partial
+    // Stream-K (too few tiles to fill the SMs' last round): the (tile, k stage) units are cut
+    // into gridDim contiguous ranges; a tile that a cut splits is summed from f32 partial
     // tiles in a workspace by the last CTA to arrive, in ascending CTA order (deterministic).
     int streamk;
     float4* partials;    // [grid][2][NROWS / 4][128 columns] float4 (4 rows of one column)
@@ -610,13 +610,13 @@ bool w4a16_fused_ok(const void* x, const DqProblem* probs, int num_probs, uint32
     return true;
 }
 
-// Stream-K pays when the row tile is single (every tile sees the same activations), the
-// partial tiles are small, and the column tiles leave a good part of the last round idle.
+// Stream-K pays when the tiles leave a good part of the last round idle.
 static bool fused_streamk_pays(const DeviceCtx& ctx, int num_probs, uint32_t m, uint32_t n, uint32_t k)
 {
-    if (m > 128 || k < 1024)
+    if (k < 1024)
         return false;
-    const uint32_t tiles = ((n + w4f::BN - 1) / w4f::BN) * (uint32_t)num_probs;
+    const uint32_t tiles_m = m <= 128 ? 1u : (m + 255) / 256;
+    const uint32_t tiles = tiles_m * ((n + w4f::BN - 1) / w4f::BN) * (uint32_t)num_probs;
     const uint32_t sms = (uint32_t)ctx.num_sms;
     const uint32_t rounds = (tiles + sms - 1) / sms;
     // k per SM with whole tiles against k per SM when the work is spread evenly; parking and adding
@@ -624,7 +624,8 @@ static bool fused_streamk_pays(const DeviceCtx& ctx, int num_probs, uint32_t m, 
     // even spread saves 1700 k per SM and loses)
     const uint64_t k_whole = (uint64_t)rounds * k;
     const uint64_t k_even = ((uint64_t)tiles * k + sms - 1) / sms;
-    return k_whole >= k_even + 2560;
+    // the 256-row partial tiles are four times the size: measured break-even near 4000 k per SM
+    return k_whole >= k_even + (m <= 128 ? 2560u : 4096u);
 }
 
 size_t w4a16_fused_workspace_bytes(const DeviceCtx& ctx, int num_probs, uint32_t m, uint32_t n,
@@ -632,7 +633,7 @@ size_t w4a16_fused_workspace_bytes(const DeviceCtx& ctx, int num_probs, uint32_t
 {
     if (!fused_streamk_pays(ctx, num_probs, m, n, k))
         return 0;
-    const uint32_t rows = m <= 32 ? 32 : (m <= 64 ? 64 : 128);
+    const uint32_t rows = m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256));
     return (size_t)ctx.num_sms * 2 * rows * w4f::BN * sizeof(float);
 }
 
@@ -641,7 +642,8 @@ size_t w4a16_fused_num_counters(const DeviceCtx& ctx, int num_probs, uint32_t m,
 {
     if (!fused_streamk_pays(ctx, num_probs, m, n, k))
         return 0;
-    return (size_t)((n + w4f::BN - 1) / w4f::BN) * (size_t)num_probs;
+    const size_t tiles_m = m <= 128 ? 1 : (m + 255) / 256;
+    return tiles_m * (size_t)((n + w4f::BN - 1) / w4f::BN) * (size_t)num_probs;
 }
 
 template <int NROWS, int BKS>
