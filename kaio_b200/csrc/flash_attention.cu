@@ -330,26 +330,35 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
             // test is made warp-uniform so the common blocks run mask-free code
             const bool blk_mask = __any_sync(0xffffffffu, need_mask);
 
+            // ---- the whole score row (128 f32) comes into registers once: four loads in flight,
+            // one wait; both softmax passes then run on registers
+            uint32_t r0[32], r1[32], r2[32], r3[32];
+            tmem_ld_32x32b_x32(s_tmem + 0, r0);
+            tmem_ld_32x32b_x32(s_tmem + 32, r1);
+            tmem_ld_32x32b_x32(s_tmem + 64, r2);
+            tmem_ld_32x32b_x32(s_tmem + 96, r3);
+            tmem_ld_wait();
+            if (blk_mask) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    if (col_base + i >= col_lim)
+                        r0[i] = 0xff800000u;  // -inf -> p = 0
+                    if (col_base + 32 + i >= col_lim)
+                        r1[i] = 0xff800000u;
+                    if (col_base + 64 + i >= col_lim)
+                        r2[i] = 0xff800000u;
+                    if (col_base + 96 + i >= col_lim)
+                        r3[i] = 0xff800000u;
+                }
+            }
             // ---- pass 1: block maximum of the raw scores (the scale is positive: scale after)
             float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll 1
-            for (uint32_t c = 0; c < BKV / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld_32x32b_x32(s_tmem + c * 32, r);
-                tmem_ld_wait();
-                if (blk_mask) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (col_base + c * 32 + i >= col_lim)
-                            r[i] = 0xff800000u;  // -inf
-                }
-#pragma unroll
-                for (int i = 0; i < 32; i += 4) {  // four independent chains
-                    mx0 = fmaxf(mx0, __uint_as_float(r[i]));
-                    mx1 = fmaxf(mx1, __uint_as_float(r[i + 1]));
-                    mx2 = fmaxf(mx2, __uint_as_float(r[i + 2]));
-                    mx3 = fmaxf(mx3, __uint_as_float(r[i + 3]));
-                }
+            for (int i = 0; i < 32; ++i) {  // four independent chains
+                mx0 = fmaxf(mx0, __uint_as_float(r0[i]));
+                mx1 = fmaxf(mx1, __uint_as_float(r1[i]));
+                mx2 = fmaxf(mx2, __uint_as_float(r2[i]));
+                mx3 = fmaxf(mx3, __uint_as_float(r3[i]));
             }
             const float m_blk = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
             // ---- lazy rescale: keep the old reference unless the max grew by more than 2^13
@@ -384,20 +393,9 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
                 tmem_st_wait();
             }
             // ---- pass 2: p = 2^(s * scale - m_ref), row sum, f16 pairs into tensor memory.  P
-            // overwrites the first 64 columns of S: chunk c of P covers S columns [16c, 16c+16),
-            // which this thread has already loaded (chunks ascend, the load completes first).
+            // overwrites the first 64 columns of S, which are all in registers by now.
             float ls0 = 0.0f, ls1 = 0.0f, ls2 = 0.0f, ls3 = 0.0f;
-#pragma unroll 1
-            for (uint32_t c = 0; c < BKV / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld_32x32b_x32(s_tmem + c * 32, r);
-                tmem_ld_wait();
-                if (blk_mask) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (col_base + c * 32 + i >= col_lim)
-                            r[i] = 0xff800000u;  // -inf -> p = 0
-                }
+            auto exp_chunk = [&](const uint32_t (&r)[32], uint32_t c) {
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 4) {
@@ -415,7 +413,11 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
                     pk[(i >> 1) + 1] = *reinterpret_cast<const uint32_t*>(&h23);
                 }
                 tmem_st_32x32b_x16(s_tmem + c * 16, pk);
-            }
+            };
+            exp_chunk(r0, 0);
+            exp_chunk(r1, 1);
+            exp_chunk(r2, 2);
+            exp_chunk(r3, 3);
             l_sum += (ls0 + ls1) + (ls2 + ls3);
             tmem_st_wait();
             tc_fence_before_sync();
