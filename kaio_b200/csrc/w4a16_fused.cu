@@ -16,13 +16,21 @@
 // register, one hfma2 with per-half constants makes them exact integers, one hmul2 applies the
 // group scale.
 //
-// Per CTA (448 threads), persistent over tiles (projection, 128 columns, NROWS rows):
-//   warp 0      TMA producer: per 64-k stage one box of packed weights [128 columns][32 B]
-//               (32-byte swizzle) and one box of activations [NROWS rows][64 k] (128-byte swizzle).
-//   warp 1      MMA issuer: 4 x tcgen05.mma kind::f16 M128 N=NROWS K16 per stage, A from tensor
-//               memory, B from shared memory; D in tensor memory (double buffered for NROWS <= 128).
-//   warps 2-9   dequantisers (two per lane quarter: each takes 32 of the stage's 64 k).
-//   warps 10-13 epilogue: tcgen05.ld of D^T, f16 / f32 narrow, row-wise coalesced stores.
+// Per CTA (448 threads), persistent over tiles (projection, 128 columns, NROWS rows); a stage is
+// BKS = 256 / 128 / 64 k long for NROWS <= 64 / = 128 / = 256 (what fits beside the activations):
+//   warp 0      TMA producer: per stage one box of packed weights [128 columns][BKS / 2 bytes]
+//               (swizzle = the row length), BKS / 64 boxes of activations [NROWS rows][64 k]
+//               (128-byte swizzle) and the stage's group scales, all on one barrier.
+//   warp 1      MMA issuer: BKS / 16 x tcgen05.mma kind::f16 M128 N=NROWS K16 per stage, A from
+//               tensor memory, B from shared memory; D in tensor memory (two buffers for
+//               NROWS <= 128).
+//   warps 2-9   dequantisers (two per lane quarter: each takes half of the stage's k).
+//   warps 10-13 epilogue: tcgen05.ld of D^T, f16 / f32 narrow, row-wise coalesced stores (to every
+//               destination of a sharded all-gather call).
+// When the tiles leave a good part of the SMs' last round idle, the (tile, stage) units are cut
+// into gridDim contiguous ranges instead (stream-K): a tile that a cut splits is summed from f32
+// partial tiles by the last CTA to arrive, in ascending CTA order, so the result does not depend
+// on timing.
 #include "common.cuh"
 #include "kernels.h"
 
