@@ -486,6 +486,16 @@ __host__ __device__ constexpr uint64_t make_smem_desc_sw128(uint32_t smem_addr, 
            ((uint64_t)2 << 61);
 }
 
+// The same descriptor with the 64-byte swizzle mode (operand rows of 64 bytes; 8-row groups are
+// then 512 bytes apart in a dense tile).
+__host__ __device__ constexpr uint64_t make_smem_desc_sw64(uint32_t smem_addr, uint32_t lbo_bytes,
+                                                           uint32_t sbo_bytes)
+{
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
+           ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)4 << 61);
+}
+
 // Instruction descriptor for kind::i8 / kind::f16 (dense, no negate, no saturate).
 //   bits [4,6) D format (1 = f32, 2 = s32)   bits [7,10) A format   bits [10,13) B format
 //   bit 15 A major (0 = K, 1 = MN)           bit 16 B major

@@ -20,6 +20,16 @@
 //   warps 2-5  epilogue on this CTA's 128 accumulator rows (double-buffered tensor memory):
 //              tcgen05.ld, cvt.rn.f32.s32, scale, swizzled staging, TMA bulk store; then an
 //              arrive on the leader's "accumulator free" barrier.
+//
+// Half-width tail tiles.  With T tiles on P pairs the last round is only partly filled (256
+// tiles on 74 pairs: 3 full rounds and 34 tiles).  When the left-over tiles number at most P / 2
+// each is cut into two 256 x 128 tiles (M256 N128 MMAs, each CTA staging 64 columns of B in the
+// 64-byte swizzle), so the last round has twice the tiles of half the work.  A half tile moves
+// 96 bytes of operands per clock per SM instead of 64, so it runs below the full rate, but the
+// round is still shorter than a full-tile round; no reduction across CTAs is needed and the
+// result stays bit-exact.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -45,6 +55,9 @@ constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + STG_TOTAL + NUM_BARS * 
 
 constexpr uint32_t IDESC = make_idesc(/*d=s32*/ 2, /*a=s8*/ 1, /*b=s8*/ 1, /*a K-major*/ 0,
                                       /*b MN-major*/ 1, BM, BN);
+constexpr int BN_HALF = 128;              // half-width tail tile
+constexpr int B_HALF_BYTES = BK * 64;     // 8 KiB: [BK k-rows][this CTA's 64 B of N]
+constexpr uint32_t IDESC_HALF = make_idesc(2, 1, 1, 0, 1, BM, BN_HALF);
 
 enum : uint32_t {
     SITE_EMPTY = 11, SITE_FULL = 12, SITE_PEER_FULL = 13, SITE_TMEM_EMPTY = 14, SITE_TMEM_FULL = 15
@@ -55,6 +68,7 @@ struct Params {
     const float* w_scale;
     float scale;
     uint32_t m, n, k;
+    uint32_t full_tiles;  // tiles [0, full_tiles) run whole; each later tile runs as two halves
     uint32_t* status;
 };
 
@@ -62,6 +76,7 @@ template <int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 w8a8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
                       const __grid_constant__ CUtensorMap tmap_b,
+                      const __grid_constant__ CUtensorMap tmap_b_half,
                       const __grid_constant__ CUtensorMap tmap_c, const Params p)
 {
     extern __shared__ uint8_t smem_raw[];
@@ -88,6 +103,17 @@ w8a8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t tiles_n = (p.n + BN - 1) / BN;
     const uint32_t num_tiles = tiles_m * tiles_n;
     const uint32_t num_kb = (p.k + BK - 1) / BK;
+    // work item -> (tile, which half); half = 2 means the whole tile
+    const uint32_t num_items = p.full_tiles + 2 * (num_tiles - p.full_tiles);
+    auto item_tile = [&](uint32_t item, uint32_t& tile, uint32_t& half) {
+        if (item < p.full_tiles) {
+            tile = item;
+            half = 2;
+        } else {
+            tile = p.full_tiles + ((item - p.full_tiles) >> 1);
+            half = (item - p.full_tiles) & 1u;
+        }
+    };
 
     // Tiles are walked in groups of RASTER_GM m-tiles (m fastest inside the group, then n, then
     // the next group): pairs running side by side cover a near-square patch, the group's rows of
@@ -130,11 +156,12 @@ w8a8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // ------------------------------------------------------------ TMA producer
         uint32_t s = 0, ph = 0;
         bool ok = true;
-        for (uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs) {
-            uint32_t tm, tn;
+        for (uint32_t item = pair; ok && item < num_items; item += num_pairs) {
+            uint32_t tile, half, tm, tn;
+            item_tile(item, tile, half);
             tile_origin(tile, tm, tn);
             const int32_t m0 = tm * BM + rank * BM_CTA;
-            const int32_t n0 = tn * BN + rank * 128;
+            const int32_t n0 = half == 2 ? tn * BN + rank * 128 : tn * BN + half * BN_HALF + rank * 64;
             for (uint32_t kb = 0; kb < num_kb; ++kb) {
                 if (!mbar_wait_bounded_cluster(empty_bar(s), ph ^ 1u, abort_flag, p.status,
                                                SITE_EMPTY, KERNEL_W8A8)) {
@@ -145,10 +172,12 @@ w8a8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const uint32_t stage = smem_base + s * STAGE_BYTES;
                     const int32_t k0 = kb * BK;
                     const uint32_t leader_full = mapa_shared(full_bar(s), 0);
-                    if (rank == 0)
-                        mbar_expect_tx(full_bar(s), 2 * STAGE_BYTES);  // both CTAs' boxes
+                    if (rank == 0)  // both CTAs' boxes
+                        mbar_expect_tx(full_bar(s),
+                                       2 * (A_BYTES + (half == 2 ? B_BYTES : B_HALF_BYTES)));
                     tma_load_2d_pair(stage, &tmap_a, leader_full, k0, m0);
-                    tma_load_2d_pair(stage + A_BYTES, &tmap_b, leader_full, n0, k0);
+                    tma_load_2d_pair(stage + A_BYTES, half == 2 ? &tmap_b : &tmap_b_half, leader_full,
+                                     n0, k0);
                 }
                 __syncwarp();
                 if (++s == STAGES) {
@@ -166,7 +195,8 @@ w8a8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // ------------------------------------------------------------ leader: MMA issuer
         uint32_t s = 0, ph = 0, local_tile = 0;
         bool ok = true;
-        for (uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs, ++local_tile) {
+        for (uint32_t item = pair; ok && item < num_items; item += num_pairs, ++local_tile) {
+            const bool whole = item < p.full_tiles;
             const uint32_t buf = local_tile & 1u;
             const uint32_t acc_ph = (local_tile >> 1) & 1u;
             if (!mbar_wait_bounded_cluster(tmem_empty_bar(buf), acc_ph ^ 1u, abort_flag, p.status,
@@ -186,12 +216,16 @@ w8a8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 const uint32_t stage = smem_base + s * STAGE_BYTES;
                 // the same offsets address the operands in both CTAs' shared memory
                 const uint64_t a_desc = make_smem_desc_sw128(stage, 16, 1024);
-                const uint64_t b_desc = make_smem_desc_sw128(stage + A_BYTES, 16, 1024);
+                // B rows (one per k) are 128 bytes in a whole tile, 64 bytes in a half tile
+                const uint64_t b_desc = whole ? make_smem_desc_sw128(stage + A_BYTES, 16, 1024)
+                                              : make_smem_desc_sw64(stage + A_BYTES, 16, 512);
+                const uint32_t b_row = whole ? 128u : 64u;
+                const uint32_t idesc = whole ? IDESC : IDESC_HALF;
                 if (elect_one()) {
 #pragma unroll
                     for (uint32_t kk = 0; kk < BK / UMMA_K; ++kk) {
                         umma_i8_2cta(d_tmem, a_desc + (uint64_t)((kk * UMMA_K) >> 4),
-                                     b_desc + (uint64_t)((kk * UMMA_K * 128) >> 4), IDESC,
+                                     b_desc + (uint64_t)((kk * UMMA_K * b_row) >> 4), idesc,
                                      (kb | kk) != 0 ? 1u : 0u);
                     }
                     umma_commit_2cta(empty_bar(s), 3);  // frees the stage in both CTAs
@@ -212,13 +246,15 @@ w8a8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t leader_empty0 = mapa_shared(tmem_empty_bar(0), 0);
         const uint32_t leader_empty1 = mapa_shared(tmem_empty_bar(1), 0);
         uint32_t local_tile = 0;
-        for (uint32_t tile = pair; tile < num_tiles; tile += num_pairs, ++local_tile) {
+        for (uint32_t item = pair; item < num_items; item += num_pairs, ++local_tile) {
             const uint32_t buf = local_tile & 1u;
             const uint32_t acc_ph = (local_tile >> 1) & 1u;
-            uint32_t tm, tn;
+            uint32_t tile, half, tm, tn;
+            item_tile(item, tile, half);
             tile_origin(tile, tm, tn);
             const uint32_t m0 = tm * BM + rank * BM_CTA;
-            const uint32_t n0 = tn * BN;
+            const uint32_t n0 = tn * BN + (half == 2 ? 0u : half * BN_HALF);
+            const uint32_t n_chunks = (half == 2 ? BN : BN_HALF) / 32;
             if (!mbar_wait_bounded_cluster(tmem_full_bar(buf), acc_ph, abort_flag, p.status,
                                            SITE_TMEM_FULL, KERNEL_W8A8))
                 break;
@@ -229,7 +265,7 @@ w8a8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 row_scale = __ldg(p.a_scale + row);
             const uint32_t taddr = tmem_base + buf * BN + ((quarter * 32u) << 16);
 #pragma unroll 1
-            for (uint32_t c = 0; c < BN / 32; ++c) {
+            for (uint32_t c = 0; c < n_chunks; ++c) {
                 const uint32_t col0 = n0 + c * 32;
                 if (col0 >= p.n)
                     break;  // warp-uniform
@@ -300,6 +336,16 @@ w8a8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
 }  // namespace w8a8x2
 
+// KAIO_B200_HALF_TILES=0 keeps every tile whole (tuning aid).
+static bool half_tiles_disabled()
+{
+    static const bool off = [] {
+        const char* e = getenv("KAIO_B200_HALF_TILES");
+        return e != nullptr && e[0] == '0';
+    }();
+    return off;
+}
+
 bool w8a8_2cta_ok(uint32_t m, uint32_t n, uint32_t k)
 {
     (void)n;
@@ -322,6 +368,11 @@ cudaError_t launch_w8a8_gemm_2cta(const DeviceCtx& ctx, int epi, const int8_t* a
                                CU_TENSOR_MAP_SWIZZLE_128B);
     if (err != cudaSuccess)
         return err;
+    CUtensorMap tmap_b_half;
+    err = encode_tensor_map_2d(&tmap_b_half, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, n, k, n, 64, BK,
+                               CU_TENSOR_MAP_SWIZZLE_64B);
+    if (err != cudaSuccess)
+        return err;
     err = encode_tensor_map_2d(&tmap_c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, out, n, m,
                                (uint64_t)n * 4, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B);
     if (err != cudaSuccess)
@@ -337,6 +388,11 @@ cudaError_t launch_w8a8_gemm_2cta(const DeviceCtx& ctx, int epi, const int8_t* a
     const uint32_t tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
     const uint32_t max_pairs = (uint32_t)ctx.num_sms / 2;
     const uint32_t pairs = tiles < max_pairs ? tiles : max_pairs;
+    // the left-over tiles of the last round run as halves when those fit in one round
+    const uint32_t rem = tiles % max_pairs;
+    p.full_tiles = tiles;
+    if (tiles > max_pairs && rem != 0 && 2 * rem <= max_pairs && !half_tiles_disabled())
+        p.full_tiles = tiles - rem;
 
     static bool attr_set[3][64] = {};
 #define KAIO_LAUNCH_W8A8X2(E)                                                                     \
@@ -348,8 +404,8 @@ cudaError_t launch_w8a8_gemm_2cta(const DeviceCtx& ctx, int epi, const int8_t* a
                 return err;                                                                       \
             attr_set[E][ctx.device] = true;                                                       \
         }                                                                                         \
-        w8a8_gemm_2cta_kernel<E><<<pairs * 2, NUM_THREADS, SMEM_BYTES, stream>>>(tmap_a, tmap_b,  \
-                                                                                 tmap_c, p);      \
+        w8a8_gemm_2cta_kernel<E><<<pairs * 2, NUM_THREADS, SMEM_BYTES, stream>>>(                 \
+            tmap_a, tmap_b, tmap_b_half, tmap_c, p);                                              \
     } while (0)
     switch (epi) {
     case EPI_SCALAR:

@@ -25,6 +25,8 @@ SHAPES = [
     # more tiles than SMs, several K blocks around the 4-stage ring
     (17, 16, 32, 1.0, 1), (128, 256, 128, 0.5, 2), (129, 272, 160, 0.25, 3),
     (300, 528, 1056, 0.01, 4), (1024, 1024, 1024, 0.01, 42), (2000, 4112, 96, 0.02, 5),
+    # 90 tiles on 74 pairs: the 16 left-over tiles run as 32 half-width tiles; ragged last column
+    (2304, 2560, 256, 0.01, 77), (2304, 2448, 384, 0.01, 78),
 ]
 
 
