@@ -618,40 +618,66 @@ bool w4a16_fused_ok(const void* x, const DqProblem* probs, int num_probs, uint32
     return true;
 }
 
-// Stream-K pays when the tiles leave a good part of the last round idle.
-static bool fused_streamk_pays(const DeviceCtx& ctx, int num_probs, uint32_t m, uint32_t n, uint32_t k)
+// How a call is run: rows per tile (the UMMA N) and whether the units are spread stream-K.
+struct FusedPlan {
+    uint32_t rows;
+    bool streamk;
+};
+
+// Cost model, from measurements on B200 (cycles per k of one tile's mainloop, and the cost of
+// parking + adding the cut tiles of a stream-K run, in k of mainloop):
+//   rows   32 / 64: 7.0 cycles/k (256-k stages, the dequantisation sets the pace), fix-up 2560 k
+//   rows  128     : 9.5 cycles/k (128-k stages),                                   fix-up 2560 k
+//   rows  256     : 17  cycles/k (64-k stages, dequantisation ~ tensor pipe),      fix-up 4096 k
+// More rows per tile dequantise each weight fewer times, fewer rows give more tiles to fill the
+// SMs; e.g. M = 256 runs as 256-row tiles on a whole 70B FFN matrix (224 column tiles) and as
+// 128-row tiles on one eighth of it (28 column tiles).
+static FusedPlan fused_plan(const DeviceCtx& ctx, int num_probs, uint32_t m, uint32_t n, uint32_t k)
 {
-    if (k < 1024)
-        return false;
-    const uint32_t tiles_m = m <= 128 ? 1u : (m + 255) / 256;
-    const uint32_t tiles = tiles_m * ((n + w4f::BN - 1) / w4f::BN) * (uint32_t)num_probs;
-    const uint32_t sms = (uint32_t)ctx.num_sms;
-    const uint32_t rounds = (tiles + sms - 1) / sms;
-    // k per SM with whole tiles against k per SM when the work is spread evenly; parking and adding
-    // the cut tiles costs about as much as ten 256-k stages (measured: at K = 4096, N = 11008 the
-    // even spread saves 1700 k per SM and loses)
-    const uint64_t k_whole = (uint64_t)rounds * k;
-    const uint64_t k_even = ((uint64_t)tiles * k + sms - 1) / sms;
-    // the 256-row partial tiles are four times the size: measured break-even near 4000 k per SM
-    return k_whole >= k_even + (m <= 128 ? 2560u : 4096u);
+    static const uint32_t kRows[4] = {32, 64, 128, 256};
+    static const double kCyclesPerK[4] = {7.0, 7.0, 9.5, 17.0};
+    static const double kFixupK[4] = {2560, 2560, 2560, 4096};
+    const double sms = (double)ctx.num_sms;
+    const uint32_t col_tiles = ((n + w4f::BN - 1) / w4f::BN) * (uint32_t)num_probs;
+    FusedPlan best = {256, false};
+    double best_cost = 1e300;
+    for (int i = 3; i >= 0; --i) {  // descending: a tie keeps the larger tile (fewer dequantisations)
+        const uint32_t rows = kRows[i];
+        if (rows < 256 && m > 4 * rows)
+            continue;  // more than four row tiles: the weights would be dequantised too often
+        if (rows > 32 && rows / 2 >= m)
+            continue;  // more than twice as tall as the problem
+        const uint32_t tiles = ((m + rows - 1) / rows) * col_tiles;
+        const double whole = kCyclesPerK[i] * (double)((tiles + ctx.num_sms - 1) / ctx.num_sms) * k;
+        double even = kCyclesPerK[i] * ((double)tiles * k / sms + kFixupK[i]);
+        if (k < 1024)
+            even = 1e300;
+        const double cost = whole < even ? whole : even;
+        if (cost < best_cost * 0.999) {
+            best_cost = cost;
+            best.rows = rows;
+            best.streamk = even < whole;
+        }
+    }
+    return best;
 }
 
 size_t w4a16_fused_workspace_bytes(const DeviceCtx& ctx, int num_probs, uint32_t m, uint32_t n,
                                    uint32_t k)
 {
-    if (!fused_streamk_pays(ctx, num_probs, m, n, k))
+    const FusedPlan plan = fused_plan(ctx, num_probs, m, n, k);
+    if (!plan.streamk)
         return 0;
-    const uint32_t rows = m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256));
-    return (size_t)ctx.num_sms * 2 * rows * w4f::BN * sizeof(float);
+    return (size_t)ctx.num_sms * 2 * plan.rows * w4f::BN * sizeof(float);
 }
 
 size_t w4a16_fused_num_counters(const DeviceCtx& ctx, int num_probs, uint32_t m, uint32_t n,
                                 uint32_t k)
 {
-    if (!fused_streamk_pays(ctx, num_probs, m, n, k))
+    const FusedPlan plan = fused_plan(ctx, num_probs, m, n, k);
+    if (!plan.streamk)
         return 0;
-    const size_t tiles_m = m <= 128 ? 1 : (m + 255) / 256;
-    return tiles_m * (size_t)((n + w4f::BN - 1) / w4f::BN) * (size_t)num_probs;
+    return (size_t)((m + plan.rows - 1) / plan.rows) * ((n + w4f::BN - 1) / w4f::BN) * (size_t)num_probs;
 }
 
 template <int NROWS, int BKS>
@@ -704,7 +730,7 @@ static cudaError_t launch_fused_n(const DeviceCtx& ctx, const __half* x, const D
     p.streamk = 0;
     p.partials = reinterpret_cast<float4*>(workspace);
     p.counters = counters;
-    if (workspace != nullptr && counters != nullptr && fused_streamk_pays(ctx, num_probs, m, n, k)) {
+    if (workspace != nullptr && counters != nullptr && fused_plan(ctx, num_probs, m, n, k).streamk) {
         p.streamk = 1;
         const uint32_t units = tiles * ((k + BKS - 1) / BKS);
         grid = units < (uint32_t)ctx.num_sms ? units : (uint32_t)ctx.num_sms;
@@ -726,17 +752,20 @@ cudaError_t launch_w4a16_fused(const DeviceCtx& ctx, const __half* x, const DqPr
                                void* workspace, uint32_t* counters, cudaStream_t stream,
                                const OutputCopies* copies)
 {
-    if (m <= 32)
+    switch (fused_plan(ctx, num_probs, m, n, k).rows) {
+    case 32:
         return launch_fused_n<32, 256>(ctx, x, probs, num_probs, out_f16, m, n, k, workspace,
                                        counters, stream, copies);
-    if (m <= 64)
+    case 64:
         return launch_fused_n<64, 256>(ctx, x, probs, num_probs, out_f16, m, n, k, workspace,
                                        counters, stream, copies);
-    if (m <= 128)
+    case 128:
         return launch_fused_n<128, 128>(ctx, x, probs, num_probs, out_f16, m, n, k, workspace,
                                         counters, stream, copies);
-    return launch_fused_n<256, 64>(ctx, x, probs, num_probs, out_f16, m, n, k, workspace, counters,
-                                   stream, copies);
+    default:
+        return launch_fused_n<256, 64>(ctx, x, probs, num_probs, out_f16, m, n, k, workspace,
+                                       counters, stream, copies);
+    }
 }
 
 }  // namespace kaio
