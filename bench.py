@@ -347,7 +347,7 @@ def main():
         line["w4a16_decode"] = bench_decode(torch, ops, dev, peaks, traffic)
         line["qkv_attention"] = bench_qkv_attention(torch, ops, dev, peaks)
         line["e2e"] = bench_e2e(torch, ops, dev, m, total_ops, steps=max(3, min(args.steps, 10)))
-        rows = 256
+        rows = m  # the whole step on the host cores: about 10 s with 16 threads
         o, s, threads = cpu_int8_sample(rows)
         line["cpu_baseline"] = {
             "value": o / s / 1e12, "unit": "TOPS", "cores": threads, "kind": "port",
