@@ -517,21 +517,25 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const Params p)
                 for (int i = 0; i < 4; ++i)
                     __stcg(reinterpret_cast<float4*>(mine + i * 4),
                            make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]));
-                __threadfence();
+                // One thread fences for the four warps: the barrier in front orders their parked
+                // stores before its release fence, the barrier behind orders its acquire fence
+                // before their loads (both fences are cumulative).  A fence in every thread costs
+                // about a microsecond per launch here.
                 named_barrier(2, 128);
                 const uint32_t c_first = owner_of(tile * p.num_kb, units, gridDim.x);
                 const uint32_t c_last = owner_of(tile * p.num_kb + p.num_kb - 1, units, gridDim.x);
                 if (tid == 0) {
+                    asm volatile("fence.acq_rel.gpu;" ::: "memory");
                     const uint32_t prev = atomicAdd(p.counters + tile, 1u);
                     const bool last = (prev == c_last - c_first);
                     if (last)
                         p.counters[tile] = 0;  // self-resetting for the next launch
+                    asm volatile("fence.acq_rel.gpu;" ::: "memory");
                     *last_flag = last ? 1u : 0u;
                 }
                 named_barrier(2, 128);
                 write_out = (*last_flag != 0);
                 if (write_out) {
-                    __threadfence();
 #pragma unroll
                     for (int i = 0; i < 16; ++i)
                         acc[i] = 0.0f;
