@@ -539,6 +539,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const Params p)
 #pragma unroll
                     for (int i = 0; i < 16; ++i)
                         acc[i] = 0.0f;
+#pragma unroll 2  // two contributors' loads in flight
                     for (uint32_t c = c_first; c <= c_last; ++c) {
                         const uint32_t c_tile0 = range_begin(c, units, gridDim.x) / p.num_kb;
                         const uint32_t cslot = (tile == c_tile0) ? 0u : 1u;

@@ -571,6 +571,7 @@ w4a16_fused_kernel(const __grid_constant__ TensorMaps maps, const Params p)
 #pragma unroll
                 for (int i = 0; i < 32; ++i)
                     acc[i] = 0.0f;
+#pragma unroll 2  // two contributors' loads in flight
                 for (uint32_t cc = c_first; cc <= c_last; ++cc) {  // ascending: a fixed order
                     const uint32_t cc_tile0 = range_begin(cc, units, gridDim.x) / num_kb;
                     const uint32_t cslot = (g.tile == cc_tile0) ? 0u : 1u;
