@@ -65,6 +65,20 @@ int32_t kaio_b200_matmul_int8_acc(const int8_t* a, size_t a_len, const int8_t* b
                                   int32_t* acc, size_t acc_len, uint32_t m, uint32_t n, uint32_t k,
                                   void* stream);
 
+/* ---- f16 GEMM --------------------------------------------------------------------- */
+
+/* Replaces kaio_ops::matmul_tc (kaio-ops/src/matmul_tc_kernel.rs:1583-1626) and
+ * kaio_ops::matmul_tc_async (kaio-ops/src/matmul_tc_async_kernel.rs, same signature, same
+ * validation through validate_dims_tc): a f16 [m,k] row-major, b f16 [k,n] row-major, c f32 [m,n]
+ * row-major, f32 accumulation.  k % 16 == 0; m and n are free.  Both entry points run the same
+ * kernel here (the reference's two differ only in how they stage shared memory). */
+int32_t kaio_b200_matmul_tc(const kaio_f16* a, size_t a_len, const kaio_f16* b, size_t b_len,
+                            float* c, size_t c_len, uint32_t m, uint32_t n, uint32_t k,
+                            void* stream);
+int32_t kaio_b200_matmul_tc_async(const kaio_f16* a, size_t a_len, const kaio_f16* b, size_t b_len,
+                                  float* c, size_t c_len, uint32_t m, uint32_t n, uint32_t k,
+                                  void* stream);
+
 /* ---- W4A16 ----------------------------------------------------------------------- */
 
 /* Replaces kaio_ops::matmul_int4 (kaio-ops/src/matmul_int4_kernel.rs:2126-2171).

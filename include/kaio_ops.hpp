@@ -56,6 +56,20 @@ inline void matmul_int8(const KaioDevice& device, const GpuBuffer<const int8_t>&
 }
 
 // kaio-ops/src/matmul_int4_kernel.rs:2126-2136
+// kaio_ops::matmul_tc / matmul_tc_async (kaio-ops/src/matmul_tc_kernel.rs:1583, matmul_tc_async_kernel.rs)
+inline void matmul_tc(const KaioDevice& device, const GpuBuffer<const f16>& a, const GpuBuffer<const f16>& b,
+                      GpuBuffer<float>& c, uint32_t m, uint32_t n, uint32_t k)
+{
+    check(kaio_b200_matmul_tc(a.ptr, a.len(), b.ptr, b.len(), c.ptr, c.len(), m, n, k, device.stream));
+}
+
+inline void matmul_tc_async(const KaioDevice& device, const GpuBuffer<const f16>& a,
+                            const GpuBuffer<const f16>& b, GpuBuffer<float>& c, uint32_t m, uint32_t n,
+                            uint32_t k)
+{
+    check(kaio_b200_matmul_tc_async(a.ptr, a.len(), b.ptr, b.len(), c.ptr, c.len(), m, n, k, device.stream));
+}
+
 inline void matmul_int4(const KaioDevice& device, const GpuBuffer<const f16>& a,
                         const GpuBuffer<const uint32_t>& b_packed, const GpuBuffer<const f16>& scales,
                         GpuBuffer<float>& c, uint32_t m, uint32_t n, uint32_t k, uint32_t group_size)

@@ -530,6 +530,61 @@ KAIO_API int32_t kaio_b200_matmul_int8_acc(const int8_t* a, size_t a_len, const 
                     stream);
 }
 
+// ---------------------------------------------------------------- matmul_tc (f16 x f16 -> f32)
+// Messages restate validate_dims_tc (kaio-ops/src/matmul_tc_kernel.rs:123-164).
+static int32_t run_matmul_tc(const kaio_f16* a, size_t a_len, const kaio_f16* b, size_t b_len,
+                             float* c, size_t c_len, uint32_t m, uint32_t n, uint32_t k,
+                             void* stream)
+{
+    if (m == 0 || n == 0 || k == 0)
+        INVALID("matmul_tc dimensions must be non-zero");
+    if (k % 16 != 0)
+        INVALID("matmul_tc: K must be a multiple of 16 (got %u). The mma.sync.m16n8k16 "
+                "instance shape requires K-tile size 16; K is not edge-padded inside a K-tile.",
+                k);
+    const size_t mk = (size_t)m * k, kn = (size_t)k * n, mn = (size_t)m * n;
+    if (a_len < mk)
+        INVALID("matmul_tc: A buffer too small: need %zu f16 (%u\xC3\x97%u), got %zu", mk, m, k, a_len);
+    if (b_len < kn)
+        INVALID("matmul_tc: B buffer too small: need %zu f16 (%u\xC3\x97%u), got %zu", kn, k, n, b_len);
+    if (c_len < mn)
+        INVALID("matmul_tc: C buffer too small: need %zu f32 (%u\xC3\x97%u), got %zu", mn, m, n, c_len);
+    REQUIRE_PTR(a, "matmul_tc", "A");
+    REQUIRE_PTR(b, "matmul_tc", "B");
+    REQUIRE_PTR(c, "matmul_tc", "C");
+    DeviceCtx* ctx;
+    int32_t rc;
+    if ((rc = get_ctx(&ctx)))
+        return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    DqProblem pr;
+    pr.w = b;
+    pr.scales = nullptr;
+    pr.col_scale = nullptr;
+    pr.scale = 1.0f;
+    pr.out = c;
+    const __half* x = reinterpret_cast<const __half*>(a);
+    if (dq_gemm_fast_path_ok(WFMT_F16, x, &pr, 1, false, m, n, k))
+        return finish(launch_dq_gemm(*ctx, WFMT_F16, x, &pr, 1, false, false, m, n, k, nullptr, s),
+                      "matmul_tc", "f16_tcgen05");
+    return finish(launch_dq_generic(WFMT_F16, x, &pr, 1, false, false, m, n, k, s), "matmul_tc",
+                  "f16_generic");
+}
+
+KAIO_API int32_t kaio_b200_matmul_tc(const kaio_f16* a, size_t a_len, const kaio_f16* b, size_t b_len,
+                                     float* c, size_t c_len, uint32_t m, uint32_t n, uint32_t k,
+                                     void* stream)
+{
+    return run_matmul_tc(a, a_len, b, b_len, c, c_len, m, n, k, stream);
+}
+
+KAIO_API int32_t kaio_b200_matmul_tc_async(const kaio_f16* a, size_t a_len, const kaio_f16* b,
+                                           size_t b_len, float* c, size_t c_len, uint32_t m,
+                                           uint32_t n, uint32_t k, void* stream)
+{
+    return run_matmul_tc(a, a_len, b, b_len, c, c_len, m, n, k, stream);
+}
+
 KAIO_API int32_t kaio_b200_matmul_int4(const kaio_f16* a, size_t a_len, const uint32_t* b_packed,
                                        size_t b_len, const kaio_f16* scales, size_t scales_len,
                                        float* c, size_t c_len, uint32_t m, uint32_t n, uint32_t k,

@@ -514,7 +514,10 @@ cudaError_t launch_dq_gemm(const DeviceCtx& ctx, int wfmt, const __half* x, cons
         da.scales[i] = probs[i].scales;
         da.out[i] = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(dq_workspace) + per * i);
     }
-    if (wfmt == WFMT_S4_PACKED) {
+    if (wfmt == WFMT_F16) {
+        for (int i = 0; i < num_probs; ++i)  // the weights are the f16 operand already
+            da.out[i] = const_cast<__half*>(reinterpret_cast<const __half*>(probs[i].w));
+    } else if (wfmt == WFMT_S4_PACKED) {
         dim3 grid((n + 63) / 64, (k + 63) / 64, num_probs);
         dequant_s4_kernel<<<grid, 256, 0, stream>>>(da, n, k);
     } else {

@@ -101,6 +101,8 @@ dq_generic_kernel(const __half* __restrict__ x, const DqGenericArgs args, int ou
             if (col < n && k0 + kk < k) {
                 if (WFMT == WFMT_S8_ROWMAJOR)
                     wv = (float)reinterpret_cast<const int8_t*>(pr.w)[(size_t)(k0 + kk) * n + col];
+                else if (WFMT == WFMT_F16)
+                    wv = __half2float(reinterpret_cast<const __half*>(pr.w)[(size_t)(k0 + kk) * n + col]);
                 else
                     wv = dequant_s4_ref(reinterpret_cast<const uint32_t*>(pr.w), pr.scales, k0 + kk,
                                         col, n, k_words);
@@ -136,6 +138,8 @@ cudaError_t launch_dq_generic(int wfmt, const __half* x, const DqProblem* probs,
     if (wfmt == WFMT_S8_ROWMAJOR)
         dq_generic_kernel<WFMT_S8_ROWMAJOR><<<grid, block, 0, stream>>>(x, args, out_f16, post_scale,
                                                                          m, n, k);
+    else if (wfmt == WFMT_F16)
+        dq_generic_kernel<WFMT_F16><<<grid, block, 0, stream>>>(x, args, out_f16, post_scale, m, n, k);
     else
         dq_generic_kernel<WFMT_S4_PACKED><<<grid, block, 0, stream>>>(x, args, out_f16, post_scale,
                                                                        m, n, k);

@@ -20,6 +20,7 @@ enum : int {
 enum : int {
     WFMT_S8_ROWMAJOR = 0,  // s8 [K,N] row-major (fused QKV W8A16)
     WFMT_S4_PACKED = 1,    // s4, 8 per u32 along K, words column-major, group-128 f16 scales
+    WFMT_F16 = 2,          // f16 [K,N] row-major: used as is (matmul_tc)
 };
 
 // Per-device state owned by the library.

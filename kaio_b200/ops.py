@@ -102,6 +102,18 @@ def matmul_int8_acc(device, a, b, acc, m, n, k):
 
 # ------------------------------------------------------------------ W4A16
 
+def matmul_tc(device, a, b, c, m, n, k):
+    """``kaio_ops::matmul_tc`` (kaio-ops/src/matmul_tc_kernel.rs:1583-1626): f16 x f16 -> f32."""
+    _call(device, "kaio_b200_matmul_tc", *_buf(a, torch.float16, "a"), *_buf(b, torch.float16, "b"),
+          *_buf(c, torch.float32, "c"), m, n, k)
+
+
+def matmul_tc_async(device, a, b, c, m, n, k):
+    """``kaio_ops::matmul_tc_async`` (kaio-ops/src/matmul_tc_async_kernel.rs): same contract."""
+    _call(device, "kaio_b200_matmul_tc_async", *_buf(a, torch.float16, "a"), *_buf(b, torch.float16, "b"),
+          *_buf(c, torch.float32, "c"), m, n, k)
+
+
 def matmul_int4(device, a, b_packed, scales, c, m, n, k, group_size):
     """``kaio_ops::matmul_int4`` (kaio-ops/src/matmul_int4_kernel.rs:2126-2171).
 

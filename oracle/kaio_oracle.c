@@ -117,6 +117,29 @@ KAIO_EXPORT uint16_t kaio_oracle_f32_to_f16(float f)
     return (uint16_t)(sign | out);
 }
 
+/* ------------------------------------------------------------ f16 GEMM (matmul_tc) */
+
+/* kaio-ops/tests/common/mod.rs:37-54 (cpu_matmul_f16xf16_f32): both operands widened to f32,
+ * sum += av * bv in f32, k ascending. */
+KAIO_EXPORT void kaio_oracle_matmul_f16(const uint16_t *a, const uint16_t *b, uint32_t m,
+                                        uint32_t n, uint32_t k, uint32_t row0, uint32_t row1,
+                                        float *out)
+{
+    (void)m;
+#pragma omp parallel for schedule(static)
+    for (int64_t i = row0; i < (int64_t)row1; i++) {
+        for (uint32_t j = 0; j < n; j++) {
+            float sum = 0.0f;
+            for (uint32_t p = 0; p < k; p++) {
+                float av = kaio_oracle_f16_to_f32(a[(size_t)i * k + p]);
+                float bv = kaio_oracle_f16_to_f32(b[(size_t)p * n + j]);
+                sum += av * bv;
+            }
+            out[(size_t)i * n + j] = sum;
+        }
+    }
+}
+
 /* ------------------------------------------------------------ W8A8 GEMM */
 
 /* kaio-ops/tests/matmul_int8_e2e.rs:20-34.  acc_out (may be NULL) receives the

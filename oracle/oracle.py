@@ -74,6 +74,16 @@ def f32_to_f16(x: float) -> int:
     return int(lib().kaio_oracle_f32_to_f16(C.c_float(x)))
 
 
+def matmul_f16(a, b, m, n, k, rows=None):
+    """f16 x f16 -> f32, f32 accumulation -- kaio-ops/tests/common/mod.rs:37-54."""
+    a = np.ascontiguousarray(a, dtype=np.float16)
+    b = np.ascontiguousarray(b, dtype=np.float16)
+    out = np.zeros((m, n), dtype=np.float32)
+    r0, r1 = _rows(m, rows)
+    lib().kaio_oracle_matmul_f16(_p(a), _p(b), C.c_uint32(m), C.c_uint32(n), C.c_uint32(k), r0, r1, _p(out))
+    return out
+
+
 def matmul_int8(a, b, scale, m, n, k, rows=None, want_acc=False):
     """``(acc as f32) * scale`` -- kaio-ops/tests/matmul_int8_e2e.rs:20-34."""
     a = np.ascontiguousarray(a, dtype=np.int8)

@@ -31,6 +31,21 @@ def err(lib):
     return lib.kaio_b200_last_error().decode()
 
 
+def test_matmul_tc_validation_messages(lib):
+    """validate_dims_tc, kaio-ops/src/matmul_tc_kernel.rs:123-164."""
+    for f in (lib.kaio_b200_matmul_tc, lib.kaio_b200_matmul_tc_async):
+        assert f(None, 0, None, 0, None, 0, 0, 8, 16, None) == 1
+        assert err(lib) == "matmul_tc dimensions must be non-zero"
+        assert f(None, 0, None, 0, None, 0, 16, 8, 24, None) == 1
+        assert err(lib).startswith("matmul_tc: K must be a multiple of 16 (got 24).")
+        assert f(None, 5, None, 0, None, 0, 16, 8, 16, None) == 1
+        assert err(lib) == "matmul_tc: A buffer too small: need 256 f16 (16×16), got 5"
+        assert f(None, 256, None, 7, None, 0, 16, 8, 16, None) == 1
+        assert err(lib) == "matmul_tc: B buffer too small: need 128 f16 (16×8), got 7"
+        assert f(None, 256, None, 128, None, 3, 16, 8, 16, None) == 1
+        assert err(lib) == "matmul_tc: C buffer too small: need 128 f32 (16×8), got 3"
+
+
 def test_int8_validation_messages(lib):
     assert lib.kaio_b200_matmul_int8(None, 0, None, 0, None, 0, 1.0, 16, 8, 31, None) == 1
     assert "K must be a multiple of 32 (got 31)" in err(lib)

@@ -306,3 +306,27 @@ def test_quantizers_match_numpy_restatement(oracle):
             r = np.clip(np.sign(v) * np.floor(np.abs(v) + np.float32(0.5)), -8, 7).astype(np.int8)
             assert sc[g * n + col] == np.float16(s32) and np.array_equal(qw[g * 128:(g + 1) * 128, col], r)
     assert qw.max() == 7 and qw.min() >= -8
+
+
+# ---------------------------------------------------------------- f16 GEMM (matmul_tc)
+
+def test_matmul_f16_matches_ordered_numpy(oracle):
+    """cpu_matmul_f16xf16_f32 (kaio-ops/tests/common/mod.rs:37-54): f32 multiply, f32 add, k
+    ascending -- restated here with one numpy multiply and one add per k."""
+    m, n, k = 9, 11, 48
+    a, b = oracle.patterned_f16(m * k), oracle.patterned_f16(k * n)
+    want = np.zeros((m, n), np.float32)
+    af, bf = a.reshape(m, k).astype(np.float32), b.reshape(k, n).astype(np.float32)
+    for p in range(k):
+        want = want + af[:, p:p + 1] * bf[p:p + 1, :]
+    assert np.array_equal(oracle.matmul_f16(a, b, m, n, k), want)
+
+
+def test_matmul_f16_quadrant_canary(oracle):
+    """matmul_tc_api.rs:127-170: cell (i,j) = (i+1)(j+1) K * 1e-4 up to f16 input rounding."""
+    m = n = k = 64
+    a = np.repeat(((np.arange(m) + 1) * 0.01).astype(np.float16)[:, None], k, 1)
+    b = np.repeat(((np.arange(n) + 1) * 0.01).astype(np.float16)[None, :], k, 0)
+    got = oracle.matmul_f16(a.reshape(-1), b.reshape(-1), m, n, k)
+    want = np.outer(np.arange(m) + 1, np.arange(n) + 1) * k * 1e-4
+    assert np.allclose(got, want, rtol=3e-3)
