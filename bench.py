@@ -188,6 +188,8 @@ def main():
                     help="run only the fused-QKV + attention leg and print its JSON (profiling aid)")
     ap.add_argument("--ffn70b-only", action="store_true",
                     help="run only the 70B FFN W4A16 leg and print its JSON (profiling aid)")
+    ap.add_argument("--ffn-chain-only", action="store_true",
+                    help="run only the 70B W4A16 feed-forward chain leg and print its JSON (profiling aid)")
     ap.add_argument("--skip-extras", action="store_true",
                     help="only the headline step (no decode / e2e / cpu baseline legs)")
     args = ap.parse_args()
@@ -223,6 +225,14 @@ def main():
         res = bench_ffn70b(torch, dist, ops, sharding, dev, rank, world)
         if rank == 0:
             print(json.dumps({"ffn70b_w4a16": res}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    if args.ffn_chain_only:
+        res = bench_ffn_chain(torch, dist, ops, dev, rank, world, peaks)
+        if rank == 0:
+            print(json.dumps({"ffn_chain_70b_w4a16": res}), flush=True)
         if world > 1:
             dist.destroy_process_group()
         return
@@ -293,12 +303,14 @@ def main():
     ms_per_step = total_ms / args.steps
     value = total_ops / (ms_per_step * 1e-3) / 1e12
 
-    ffn = None
+    ffn = chain = None
     if not args.skip_extras:
         for p in probs:  # free the headline buffers before the 70B-shape leg
             p.clear()
         torch.cuda.empty_cache()
         ffn = bench_ffn70b(torch, dist, ops, sharding, dev, rank, world)
+        torch.cuda.empty_cache()
+        chain = bench_ffn_chain(torch, dist, ops, dev, rank, world, peaks)
 
     if rank != 0:
         if world > 1:
@@ -343,6 +355,8 @@ def main():
 
     if ffn is not None:
         line["ffn70b_w4a16"] = ffn
+    if chain is not None:
+        line["ffn_chain_70b_w4a16"] = chain
     if not args.skip_extras and world == 1:
         line["w4a16_decode"] = bench_decode(torch, ops, dev, peaks, traffic)
         line["qkv_attention"] = bench_qkv_attention(torch, ops, dev, peaks)
@@ -587,6 +601,85 @@ def bench_ffn70b(torch, dist, ops, sharding, dev, rank, world):
                    "and the pipelined time); weight_stream_gbs = algorithmic bytes of the full GEMM / time; the "
                    "L2 is not flushed between iterations (117 MB of weights per GEMM at 1 GPU, 126 MB L2: treat "
                    "the 1-GPU decode figures as an upper bound)")
+    return res
+
+
+def bench_ffn_chain(torch, dist, ops, dev, rank, world, peaks):
+    """The W4A16 feed-forward chain at Llama-70B shapes (hidden 8192, intermediate 28672):
+    gate|up projection (one GEMM), SiLU-gate, down projection; across ranks column-parallel then
+    row-parallel, so the only exchange is the sum of the [M, 8192] f32 partial outputs.  CUDA
+    events, max over ranks.  Reported per M: the three launches alone (and each on its own), and
+    the chain with its NCCL all-reduce / reduce-scatter."""
+    from kaio_b200 import ffn as ffn_mod
+    hidden, inter = 8192, 28672
+    g = torch.Generator(device="cuda")
+    g.manual_seed(137)
+
+    def packed(k, n):
+        return torch.randint(-2 ** 31, 2 ** 31 - 1, (k // 8 * n,), dtype=torch.int32, device="cuda", generator=g)
+
+    def scales(k, n):
+        return (torch.rand(k // 128 * n, device="cuda", generator=g) * 0.015 + 0.005).half()
+
+    weights = [packed(hidden, inter), scales(hidden, inter), packed(hidden, inter), scales(hidden, inter),
+               packed(inter, hidden), scales(inter, hidden)]
+    chain = ffn_mod.FfnInt4(ops, dev, hidden, inter, *weights, world=world, rank=rank, max_m=4096, reduce="all")
+    scatter_rows = torch.empty((4096 // world) * hidden, dtype=torch.float32, device="cuda") if world > 1 else None
+    del weights
+    torch.cuda.empty_cache()
+    il = chain.i_loc
+    res = {}
+    for mm in (16, 256, 4096):
+        g.manual_seed(42)
+        x = (torch.randn(mm * hidden, device="cuda", generator=g)).half()
+        iters = 20 if mm <= 256 else 5
+
+        def gate_up():
+            ops.matmul_int4(dev, x, chain.w_gu, chain.s_gu, chain.gu, mm, 2 * il, hidden, 128)
+
+        def act():
+            ops.silu_gate_f16(dev, chain.gu, chain.gu.view(-1)[il:], chain.act, mm, il, x_ld=2 * il, gate_ld=2 * il)
+
+        def down():
+            ops.matmul_int4(dev, chain.act, chain.w_down, chain.s_down, chain.out, mm, hidden, il, 128)
+
+        def local():
+            chain.local(x, mm)
+
+        def with_all_reduce():
+            dist.all_reduce(chain.local(x, mm), op=dist.ReduceOp.SUM)
+
+        def with_reduce_scatter():
+            dist.reduce_scatter_tensor(scatter_rows[: (mm // world) * hidden], chain.local(x, mm).view(-1),
+                                       op=dist.ReduceOp.SUM)
+
+        local()
+        variant_gu = None
+        gate_up()
+        variant_gu = ops.last_variant()
+        down()
+        variant_down = ops.last_variant()
+        ts = [_time_ms(torch, f, iters) for f in (gate_up, act, down, local)]
+        ts.append(_time_ms(torch, with_all_reduce, iters) if world > 1 else ts[3])
+        ts.append(_time_ms(torch, with_reduce_scatter, iters) if world > 1 and mm % world == 0 else ts[4])
+        t = torch.tensor(ts, dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        t_gu, t_act, t_down, t_local, t_ar, t_rs = [float(v) for v in t]
+        flops = 2 * mm * hidden * inter * 3
+        wbytes = 3 * (hidden * inter // 2 + (hidden // 128) * inter * 2)
+        act_bytes = 3 * mm * il * 2  # the SiLU-gate pass of one rank: two f16 reads and one f16 write per element
+        res[f"m{mm}"] = {
+            "ms_gate_up_gemm": t_gu, "ms_silu_gate": t_act, "ms_down_gemm": t_down, "ms_three_launches": t_local,
+            "ms_with_all_reduce": t_ar, "ms_with_reduce_scatter": t_rs,
+            "tflops": flops / t_ar / 1e9, "weight_stream_gbs": wbytes / t_ar / 1e6,
+            "silu_gate_gbs": act_bytes / t_act / 1e6, "silu_gate_frac_of_hbm_peak": act_bytes / t_act / 1e6 / peaks["hbm_gbs"],
+            "variants": [variant_gu, "silu_gate_f16", variant_down]}
+        del x
+    res["note"] = ("whole-job figures over all ranks: tflops = 6*M*8192*28672 / time with the all-reduce; "
+                   "weight_stream_gbs = packed weights + scales of the three projections / that time; "
+                   "silu_gate_gbs is one rank's pass (6 bytes per element of its [M, 28672/P] shard); the L2 "
+                   "is not flushed between iterations")
     return res
 
 

@@ -202,6 +202,22 @@ int32_t kaio_b200_quantize_pack_int4(const float* w, size_t w_len, uint32_t* pac
                                      size_t packed_len, kaio_f16* scales, size_t scales_len,
                                      uint32_t k, uint32_t n, uint32_t group_size, void* stream);
 
+/* ---- gated activation (between the up/gate and the down projection of an FFN block) ---- */
+
+/* The user kernel of examples/fused_silu_gate/src/main.rs:13-21:
+ * out[i] = x[i] * (1 / (1 + exp(-x[i]))) * gate[i], f32, i < n. */
+int32_t kaio_b200_silu_gate_f32(const float* x, size_t x_len, const float* gate, size_t gate_len,
+                                float* out, size_t out_len, uint32_t n, void* stream);
+
+/* The same on f16 matrices (EXT, not in the reference): f32 arithmetic on the widened inputs,
+ * one rounding to f16.  x, gate and out are [rows, cols] with row strides x_ld, gate_ld, out_ld
+ * (elements, >= cols), so x and gate may be the two halves of one [rows, 2*cols] projection
+ * output.  Each buffer must hold (rows-1)*ld + cols elements. */
+int32_t kaio_b200_silu_gate_f16(const kaio_f16* x, size_t x_len, const kaio_f16* gate,
+                                size_t gate_len, kaio_f16* out, size_t out_len, uint32_t rows,
+                                uint32_t cols, uint32_t x_ld, uint32_t gate_ld, uint32_t out_ld,
+                                void* stream);
+
 /* ---- library state ------------------------------------------------------------------- */
 
 /* Last error message of the calling thread ("" if none). */

@@ -128,4 +128,13 @@ inline void attention_tc_causal(const KaioDevice& device, const GpuBuffer<const 
                                  seq_q, seq_k, d_k, d_v, 1, device.stream));
 }
 
+// The `fused_silu_gate` user kernel's launch wrapper (examples/fused_silu_gate/src/main.rs:13-21,
+// called as `fused_silu_gate::launch(&device, &x, &gate, &mut out, n)` at :59).
+inline void fused_silu_gate(const KaioDevice& device, const GpuBuffer<const float>& x,
+                            const GpuBuffer<const float>& gate, GpuBuffer<float>& out, uint32_t n)
+{
+    check(kaio_b200_silu_gate_f32(x.ptr, x.len(), gate.ptr, gate.len(), out.ptr, out.len(), n,
+                                  device.stream));
+}
+
 }  // namespace kaio_ops

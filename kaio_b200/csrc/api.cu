@@ -829,6 +829,72 @@ KAIO_API int32_t kaio_b200_quantize_rows_int8(const float* x, size_t x_len, int8
                   op, "quantize_rows_int8");
 }
 
+// ---------------------------------------------------------------- gated activation
+KAIO_API int32_t kaio_b200_silu_gate_f32(const float* x, size_t x_len, const float* gate,
+                                         size_t gate_len, float* out, size_t out_len, uint32_t n,
+                                         void* stream)
+{
+    const char* op = "silu_gate_f32";
+    if (n == 0)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG, "%s dimensions must be non-zero", op);
+    if (x_len < n)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG, "%s: X buffer too small: need %u f32, got %zu",
+                    op, n, x_len);
+    if (gate_len < n)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: gate buffer too small: need %u f32, got %zu", op, n, gate_len);
+    if (out_len < n)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: out buffer too small: need %u f32, got %zu", op, n, out_len);
+    REQUIRE_PTR(x, op, "X");
+    REQUIRE_PTR(gate, op, "gate");
+    REQUIRE_PTR(out, op, "out");
+    DeviceCtx* ctx;
+    int32_t rc;
+    if ((rc = get_ctx(&ctx)))
+        return rc;
+    return finish(launch_silu_gate_f32(x, gate, out, n, static_cast<cudaStream_t>(stream)), op,
+                  "silu_gate_f32");
+}
+
+KAIO_API int32_t kaio_b200_silu_gate_f16(const kaio_f16* x, size_t x_len, const kaio_f16* gate,
+                                         size_t gate_len, kaio_f16* out, size_t out_len,
+                                         uint32_t rows, uint32_t cols, uint32_t x_ld,
+                                         uint32_t gate_ld, uint32_t out_ld, void* stream)
+{
+    const char* op = "silu_gate_f16";
+    if (rows == 0 || cols == 0)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG, "%s dimensions must be non-zero", op);
+    if (x_ld < cols || gate_ld < cols || out_ld < cols)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: row strides must be at least cols (got x_ld=%u, gate_ld=%u, out_ld=%u, "
+                    "cols=%u)", op, x_ld, gate_ld, out_ld, cols);
+    const size_t need_x = (size_t)(rows - 1) * x_ld + cols;
+    const size_t need_g = (size_t)(rows - 1) * gate_ld + cols;
+    const size_t need_o = (size_t)(rows - 1) * out_ld + cols;
+    if (x_len < need_x)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG, "%s: X buffer too small: need %zu f16, got %zu",
+                    op, need_x, x_len);
+    if (gate_len < need_g)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: gate buffer too small: need %zu f16, got %zu", op, need_g, gate_len);
+    if (out_len < need_o)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: out buffer too small: need %zu f16, got %zu", op, need_o, out_len);
+    REQUIRE_PTR(x, op, "X");
+    REQUIRE_PTR(gate, op, "gate");
+    REQUIRE_PTR(out, op, "out");
+    DeviceCtx* ctx;
+    int32_t rc;
+    if ((rc = get_ctx(&ctx)))
+        return rc;
+    return finish(launch_silu_gate_f16(reinterpret_cast<const __half*>(x),
+                                       reinterpret_cast<const __half*>(gate),
+                                       reinterpret_cast<__half*>(out), rows, cols, x_ld, gate_ld,
+                                       out_ld, static_cast<cudaStream_t>(stream)),
+                  op, "silu_gate_f16");
+}
+
 KAIO_API int32_t kaio_b200_quantize_pack_int4(const float* w, size_t w_len, uint32_t* packed,
                                               size_t packed_len, kaio_f16* scales,
                                               size_t scales_len, uint32_t k, uint32_t n,

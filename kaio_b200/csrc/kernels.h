@@ -120,6 +120,13 @@ cudaError_t launch_quantize_rows_int8(const float* x, int8_t* q, float* scale, u
 cudaError_t launch_quantize_pack_s4(const float* w, uint32_t* packed, __half* scales, uint32_t k,
                                     uint32_t n, cudaStream_t stream);
 
+// ---------------------------------------------------------------- gated activation
+cudaError_t launch_silu_gate_f32(const float* x, const float* gate, float* out, size_t n,
+                                 cudaStream_t stream);
+cudaError_t launch_silu_gate_f16(const __half* x, const __half* gate, __half* out, uint32_t rows,
+                                 uint32_t cols, uint32_t x_ld, uint32_t gate_ld, uint32_t out_ld,
+                                 cudaStream_t stream);
+
 // ---------------------------------------------------------------- attention
 struct AttnParams {
     const __half *q, *k, *v;

@@ -1,0 +1,121 @@
+"""The W4A16 feed-forward chain: ``down( silu(x @ W_gate) * (x @ W_up) )``.
+
+Three launches per rank: one W4A16 GEMM over the concatenated gate|up weights (f16 out,
+``[M, 2*I]``), the SiLU-gate pass over its two halves, and the W4A16 down projection (f32 out).
+KAIO has the pieces (``matmul_int4``, kaio-ops/src/matmul_int4_kernel.rs:2126-2171; the
+``fused_silu_gate`` user kernel, examples/fused_silu_gate/src/main.rs:13-21) but no chain and no
+multi-device form; this is the caller one level above the quantized GEMMs.
+
+Across ``P`` ranks the chain is column-parallel then row-parallel: rank ``r`` owns columns
+``[r*I/P, (r+1)*I/P)`` of W_gate and W_up and the matching K-rows of W_down, so the intermediate
+never leaves the GPU (no all-gather of ``[M, I]``) and the only exchange is the sum of the
+``[M, H]`` f32 partial outputs: an all-reduce, or a reduce-scatter when each rank only needs its
+own ``M/P`` rows.
+
+The helpers at the top are layout logic and run on CPU tensors too.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from .sharding import shard_bounds, shard_group_scales, shard_packed_int4
+
+GROUP = 128
+
+
+def k_shard_bounds(k: int, world: int, rank: int) -> tuple[int, int]:
+    """K range of ``rank`` for a row-parallel W4A16 GEMM: equal shards, each a whole number of
+    128-wide scale groups."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"bad rank {rank} of {world}")
+    if k % (world * GROUP) != 0:
+        raise ValueError(f"K={k} does not split into {world} shards of whole {GROUP}-wide groups")
+    w = k // world
+    return rank * w, (rank + 1) * w
+
+
+def k_shard_packed_int4(packed: torch.Tensor, k: int, n: int, world: int, rank: int) -> torch.Tensor:
+    """Packed s4 weights keep the K words of a column contiguous (word ``k/8`` of column ``j`` at
+    ``(k/8) + j*(K/8)``), so a K range is a strided slice of every column: copied once into a
+    packed ``[N][K/P/8]`` buffer of the same layout."""
+    lo, hi = k_shard_bounds(k, world, rank)
+    return packed.view(-1)[: n * (k // 8)].view(n, k // 8)[:, lo // 8:hi // 8].contiguous().view(-1)
+
+
+def k_shard_group_scales(scales: torch.Tensor, k: int, n: int, world: int, rank: int) -> torch.Tensor:
+    """f16 ``[K/128, N]`` group scales: a K range is a contiguous range of rows (a view)."""
+    lo, hi = k_shard_bounds(k, world, rank)
+    return scales.view(-1)[: (k // GROUP) * n].view(k // GROUP, n)[lo // GROUP:hi // GROUP].reshape(-1)
+
+
+def concat_gate_up(w_gate: torch.Tensor, s_gate: torch.Tensor, w_up: torch.Tensor, s_up: torch.Tensor,
+                   k: int, n: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """Gate and up projections as ONE ``[K, 2N]`` W4A16 weight: packed columns are contiguous, so
+    the packed buffers concatenate flat; the scales concatenate along their column axis."""
+    packed = torch.cat([w_gate.view(-1)[: n * (k // 8)], w_up.view(-1)[: n * (k // 8)]])
+    g = k // GROUP
+    scales = torch.cat([s_gate.view(-1)[: g * n].view(g, n), s_up.view(-1)[: g * n].view(g, n)], dim=1)
+    return packed, scales.contiguous().view(-1)
+
+
+class FfnInt4:
+    """One rank's share of the W4A16 feed-forward block.
+
+    ``w_gate``/``w_up`` are packed ``[hidden, inter]`` weights with ``[hidden/128, inter]`` f16
+    scales; ``w_down`` is packed ``[inter, hidden]`` with ``[inter/128, hidden]`` scales, all in
+    the layout ``matmul_int4`` takes, UNSHARDED (on any device): the constructor keeps only this
+    rank's shard, on ``device``.
+
+    ``run(x, m)`` returns the f32 ``[m, hidden]`` output: complete when ``reduce="all"`` (or one
+    rank), this rank's ``m/P`` rows (``[m/P, hidden]``) when ``reduce="scatter"``, the un-reduced
+    partial when ``reduce="none"``.
+    """
+
+    def __init__(self, ops, device, hidden: int, inter: int, w_gate, s_gate, w_up, s_up, w_down, s_down,
+                 world: int = 1, rank: int = 0, group=None, max_m: int = 4096, reduce: str = "all"):
+        if reduce not in ("all", "scatter", "none"):
+            raise ValueError(f"reduce must be 'all', 'scatter' or 'none', got {reduce!r}")
+        self.ops, self.device, self.group = ops, device, group
+        self.hidden, self.inter, self.world, self.rank, self.reduce = hidden, inter, world, rank, reduce
+        lo, hi = shard_bounds(inter, world, rank, multiple=GROUP)
+        self.i_loc = hi - lo
+        dev = torch.device("cuda", device.ordinal) if hasattr(device, "ordinal") else torch.device(device)
+        wg = shard_packed_int4(w_gate, hidden, inter, world, rank)
+        wu = shard_packed_int4(w_up, hidden, inter, world, rank)
+        sg = shard_group_scales(s_gate, hidden, inter, world, rank)
+        su = shard_group_scales(s_up, hidden, inter, world, rank)
+        w_gu, s_gu = concat_gate_up(wg, sg, wu, su, hidden, self.i_loc)
+        self.w_gu, self.s_gu = w_gu.to(dev), s_gu.to(dev)
+        self.w_down = k_shard_packed_int4(w_down, inter, hidden, world, rank).to(dev)
+        self.s_down = k_shard_group_scales(s_down, inter, hidden, world, rank).contiguous().to(dev)
+        self.max_m = max_m
+        self.gu = torch.empty(max_m * 2 * self.i_loc, dtype=torch.float16, device=dev)
+        self.act = torch.empty(max_m * self.i_loc, dtype=torch.float16, device=dev)
+        self.out = torch.empty(max_m * hidden, dtype=torch.float32, device=dev)
+        self.rows = torch.empty((max_m // world) * hidden, dtype=torch.float32, device=dev) \
+            if (world > 1 and reduce == "scatter") else None
+
+    def local(self, x: torch.Tensor, m: int) -> torch.Tensor:
+        """The three launches of this rank; returns the f32 ``[m, hidden]`` partial sum."""
+        if m > self.max_m:
+            raise ValueError(f"m={m} exceeds max_m={self.max_m}")
+        ops, d, il = self.ops, self.device, self.i_loc
+        ops.matmul_int4(d, x, self.w_gu, self.s_gu, self.gu, m, 2 * il, self.hidden, GROUP)
+        # row r of gu = [gate(r, 0..il) | up(r, 0..il)]
+        ops.silu_gate_f16(d, self.gu, self.gu.view(-1)[il:], self.act, m, il, x_ld=2 * il, gate_ld=2 * il)
+        ops.matmul_int4(d, self.act, self.w_down, self.s_down, self.out, m, self.hidden, il, GROUP)
+        return self.out[: m * self.hidden].view(m, self.hidden)
+
+    def run(self, x: torch.Tensor, m: int) -> torch.Tensor:
+        part = self.local(x, m)
+        if self.world == 1 or self.reduce == "none":
+            return part
+        if self.reduce == "all":
+            dist.all_reduce(part, op=dist.ReduceOp.SUM, group=self.group)
+            return part
+        if m % self.world != 0:
+            raise ValueError(f"reduce='scatter' needs m divisible by the {self.world} ranks, got {m}")
+        rows = self.rows[: (m // self.world) * self.hidden].view(m // self.world, self.hidden)
+        dist.reduce_scatter_tensor(rows, part, op=dist.ReduceOp.SUM, group=self.group)
+        return rows

@@ -190,6 +190,22 @@ def quantize_pack_int4(device, w, packed, scales, k, n, group_size=GROUP_SIZE):
           *_buf(packed, torch.int32, "packed"), *_buf(scales, torch.float16, "scales"), k, n, group_size)
 
 
+# ------------------------------------------------------------------ gated activation
+
+def silu_gate_f32(device, x, gate, out, n):
+    """The ``fused_silu_gate`` user kernel (examples/fused_silu_gate/src/main.rs:13-21):
+    ``out[i] = x[i] * sigmoid(x[i]) * gate[i]`` on f32."""
+    _call(device, "kaio_b200_silu_gate_f32", *_buf(x, torch.float32, "x"), *_buf(gate, torch.float32, "gate"),
+          *_buf(out, torch.float32, "out"), n)
+
+
+def silu_gate_f16(device, x, gate, out, rows, cols, x_ld=None, gate_ld=None, out_ld=None):
+    """The same on f16 ``[rows, cols]`` matrices with row strides (f32 arithmetic, one rounding);
+    not in the reference.  ``x`` and ``gate`` may be views into one ``[rows, 2*cols]`` buffer."""
+    _call(device, "kaio_b200_silu_gate_f16", *_buf(x, torch.float16, "x"), *_buf(gate, torch.float16, "gate"),
+          *_buf(out, torch.float16, "out"), rows, cols, x_ld or cols, gate_ld or cols, out_ld or cols)
+
+
 # ------------------------------------------------------------------ attention
 
 def attention_tc(device, q, k, v, out, seq_q, seq_k, d_k, d_v):

@@ -367,6 +367,34 @@ KAIO_EXPORT void kaio_oracle_attention(const uint16_t *q, const uint16_t *k, con
     }
 }
 
+/* ----------------------------------------------------- gated activation */
+
+/* cpu_reference of examples/fused_silu_gate/src/main.rs:23-33: widen to f64,
+ * sig = 1 / (1 + exp(-x)), out = (x * sig * gate) as f32. */
+KAIO_EXPORT void kaio_oracle_silu_gate_f32(const float *x, const float *gate, float *out, size_t n)
+{
+    for (size_t i = 0; i < n; i++) {
+        double xi = (double)x[i], gi = (double)gate[i];
+        double sig = 1.0 / (1.0 + exp(-xi));
+        out[i] = (float)(xi * sig * gi);
+    }
+}
+
+/* The same on f16 matrices with row strides (elements): the f64 result is narrowed to f32 as
+ * above and then rounded once to f16. */
+KAIO_EXPORT void kaio_oracle_silu_gate_f16(const uint16_t *x, const uint16_t *gate, uint16_t *out,
+                                           uint32_t rows, uint32_t cols, uint32_t x_ld,
+                                           uint32_t gate_ld, uint32_t out_ld)
+{
+    for (uint32_t r = 0; r < rows; r++)
+        for (uint32_t c = 0; c < cols; c++) {
+            double xi = (double)kaio_oracle_f16_to_f32(x[(size_t)r * x_ld + c]);
+            double gi = (double)kaio_oracle_f16_to_f32(gate[(size_t)r * gate_ld + c]);
+            double sig = 1.0 / (1.0 + exp(-xi));
+            out[(size_t)r * out_ld + c] = kaio_oracle_f32_to_f16((float)(xi * sig * gi));
+        }
+}
+
 /* ----------------------------------------------------------- quantisers */
 
 /* derive_scale + quantize of examples/int8_matmul/src/main.rs:41-61, applied per row:

@@ -172,6 +172,27 @@ def attention(q, k, v, seq_q, seq_k, d_k, d_v, causal=False, strides=None, rows=
     return out
 
 
+def silu_gate_f32(x, gate):
+    """``cpu_reference`` of examples/fused_silu_gate/src/main.rs:23-33 (f64 arithmetic, f32 result)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    gate = np.ascontiguousarray(gate, dtype=np.float32)
+    out = np.zeros(x.size, dtype=np.float32)
+    lib().kaio_oracle_silu_gate_f32(_p(x), _p(gate), _p(out), C.c_size_t(x.size))
+    return out
+
+
+def silu_gate_f16(x, gate, rows, cols, x_ld=None, gate_ld=None):
+    """The f16 matrix form: the f32 result above rounded once to f16.  ``x`` and ``gate`` are flat
+    f16 arrays holding [rows, cols] with row strides ``x_ld`` / ``gate_ld``; the result is
+    contiguous [rows, cols]."""
+    x = np.ascontiguousarray(x, dtype=np.float16)
+    gate = np.ascontiguousarray(gate, dtype=np.float16)
+    out = np.zeros((rows, cols), dtype=np.float16)
+    lib().kaio_oracle_silu_gate_f16(_p(x), _p(gate), _p(out), C.c_uint32(rows), C.c_uint32(cols),
+                                    C.c_uint32(x_ld or cols), C.c_uint32(gate_ld or cols), C.c_uint32(cols))
+    return out
+
+
 def quantize_rows_int8(x, m, k):
     """Per-row ``derive_scale`` + ``quantize`` -- examples/int8_matmul/src/main.rs:41-61."""
     x = np.ascontiguousarray(x, dtype=np.float32)

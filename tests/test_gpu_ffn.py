@@ -1,0 +1,123 @@
+"""SiLU-gate kernels and the W4A16 feed-forward chain on the GPU against the CPU oracle
+(examples/fused_silu_gate/src/main.rs:23-33 for the activation; kaio-ops/tests/matmul_int4_e2e.rs
+for the GEMMs)."""
+import numpy as np
+import pytest
+import torch
+
+from kaio_b200 import InvalidConfig, ffn, ops
+from helpers import dev, device, host, max_rel
+from test_ffn_cpu import ffn_oracle, make_ffn_case
+
+pytestmark = pytest.mark.gpu
+
+F16_ULP = 2.0 ** -10  # one unit in the last place of an f16 significand, relative
+
+
+def test_silu_gate_f32_example_data(oracle):
+    """The example's own inputs and its own bar: max abs error < 1e-5 against the f64 reference
+    (examples/fused_silu_gate/src/main.rs:45-51,66-72)."""
+    n = 1 << 20
+    i = np.arange(n)
+    x = ((i % 97).astype(np.float32) / np.float32(97.0)) - np.float32(0.5)
+    g = ((i % 113).astype(np.float32) / np.float32(113.0)) - np.float32(0.5)
+    out = torch.zeros(n, device="cuda")
+    ops.silu_gate_f32(device(), dev(x), dev(g), out, n)
+    assert ops.last_variant() == "silu_gate_f32"
+    assert np.max(np.abs(host(out) - oracle.silu_gate_f32(x, g))) < 1e-5
+
+
+@pytest.mark.parametrize("n,offset", [(1, 0), (3, 0), (4, 0), (1027, 0), (4096, 1), (1 << 22, 0), ((1 << 22) + 5, 3)])
+def test_silu_gate_f32_sizes_and_alignment(oracle, n, offset):
+    """Ragged sizes (scalar tail) and buffers that do not start on a 16-byte boundary."""
+    rng = np.random.default_rng(n)
+    x = (rng.standard_normal(n) * 4).astype(np.float32)
+    g = (rng.standard_normal(n) * 2).astype(np.float32)
+    pad = np.zeros(offset, dtype=np.float32)
+    xd, gd = dev(np.concatenate([pad, x]))[offset:], dev(np.concatenate([pad, g]))[offset:]
+    out = torch.full((offset + n + 8,), 7.0, device="cuda")
+    ops.silu_gate_f32(device(), xd, gd, out[offset:], n)
+    got = host(out)
+    want = oracle.silu_gate_f32(x, g)
+    err = np.abs(got[offset:offset + n] - want) / np.maximum(np.abs(want), 1.0)
+    assert err.max() < 1e-6
+    assert np.all(got[:offset] == 7.0) and np.all(got[offset + n:] == 7.0)  # nothing outside [0, n)
+
+
+@pytest.mark.parametrize("rows,cols,strided", [(1, 8, False), (16, 3584, True), (40, 1000, True), (7, 13, False),
+                                               (300, 4096, True), (5, 21, True)])
+def test_silu_gate_f16(oracle, rows, cols, strided):
+    """f16 matrices, contiguous or as the two halves of one [rows, 2*cols] buffer; odd widths take
+    the scalar kernel.  The kernel computes in f32 and rounds once; the oracle narrows an f64
+    result: at most one f16 unit in the last place apart, equal nearly everywhere."""
+    rng = np.random.default_rng(rows * cols)
+    both = (rng.standard_normal((rows, 2 * cols)) * 3).astype(np.float16)
+    out = torch.zeros(rows * cols, device="cuda", dtype=torch.float16)
+    if strided:
+        buf = dev(both)
+        ops.silu_gate_f16(device(), buf, buf[cols:], out, rows, cols, x_ld=2 * cols, gate_ld=2 * cols)
+        want = oracle.silu_gate_f16(both.reshape(-1), both.reshape(-1)[cols:], rows, cols, 2 * cols, 2 * cols)
+    else:
+        xs, gs = np.ascontiguousarray(both[:, :cols]), np.ascontiguousarray(both[:, cols:])
+        ops.silu_gate_f16(device(), dev(xs), dev(gs), out, rows, cols)
+        want = oracle.silu_gate_f16(xs.reshape(-1), gs.reshape(-1), rows, cols)
+    assert ops.last_variant() == "silu_gate_f16"
+    got = host(out, (rows, cols)).astype(np.float64)
+    want = want.astype(np.float64)
+    assert np.all(np.abs(got - want) <= F16_ULP * np.maximum(np.abs(want), 2.0 ** -14))
+    assert np.mean(got != want) < 0.01
+
+
+def test_silu_gate_argument_errors():
+    d = device()
+    x = torch.zeros(64, device="cuda")
+    with pytest.raises(InvalidConfig, match="dimensions must be non-zero"):
+        ops.silu_gate_f32(d, x, x, x.clone(), 0)
+    with pytest.raises(InvalidConfig, match="gate buffer too small"):
+        ops.silu_gate_f32(d, x, x[:32], x.clone(), 64)
+    h = torch.zeros(64, device="cuda", dtype=torch.float16)
+    with pytest.raises(InvalidConfig, match="row strides must be at least cols"):
+        ops.silu_gate_f16(d, h, h, h.clone(), 4, 16, x_ld=8)
+    with pytest.raises(InvalidConfig, match="out buffer too small"):
+        ops.silu_gate_f16(d, h, h, h.clone()[:60], 4, 16)
+
+
+@pytest.mark.parametrize("hidden,inter,m", [(256, 384, 1), (256, 512, 16), (512, 1024, 40), (1024, 2048, 300)])
+def test_ffn_chain_stagewise_and_end_to_end(oracle, hidden, inter, m):
+    """Every stage against the oracle fed with the GPU's own input to that stage (the bars of the
+    single ops), then the whole chain against the oracle's chain."""
+    case = make_ffn_case(oracle, hidden, inter, m, seed=hidden + m)
+    weights = [case[n] for n in ("w_gate", "s_gate", "w_up", "s_up", "w_down", "s_down")]
+    chain = ffn.FfnInt4(ops, device(), hidden, inter, *weights, max_m=max(m, 16))
+    got = host(chain.run(case["x"].cuda(), m)).copy()
+    u32 = lambda t: t.numpy().view(np.uint32)
+
+    # stage 1: the concatenated gate|up projection
+    gu = host(chain.gu)[: m * 2 * inter].reshape(m, 2 * inter)
+    g_want = oracle.matmul_int4(case["x"].numpy(), u32(case["w_gate"]), case["s_gate"].numpy(), m, inter, hidden, f16_out=True)
+    u_want = oracle.matmul_int4(case["x"].numpy(), u32(case["w_up"]), case["s_up"].numpy(), m, inter, hidden, f16_out=True)
+    assert max_rel(gu[:, :inter], np.asarray(g_want).reshape(m, inter)) < 2e-3
+    assert max_rel(gu[:, inter:], np.asarray(u_want).reshape(m, inter)) < 2e-3
+    # stage 2: the activation of the GPU's own projections
+    act = host(chain.act)[: m * inter].reshape(m, inter)
+    act_want = oracle.silu_gate_f16(gu.reshape(-1), gu.reshape(-1)[inter:], m, inter, 2 * inter, 2 * inter)
+    a64, w64 = act.astype(np.float64), act_want.astype(np.float64)
+    assert np.all(np.abs(a64 - w64) <= F16_ULP * np.maximum(np.abs(w64), 2.0 ** -14))
+    # stage 3: the down projection of the GPU's own activation
+    d_want = oracle.matmul_int4(act.reshape(-1), u32(case["w_down"]), case["s_down"].numpy(), m, hidden, inter, f16_out=False)
+    assert max_rel(got, np.asarray(d_want).reshape(m, hidden)) < 1e-3
+    # the whole chain: f16 roundings of the intermediates may fall differently on the two sides
+    assert max_rel(got, ffn_oracle(oracle, case, hidden, inter, m)) < 1e-2
+
+
+def test_ffn_chain_partial_sums_add_up(oracle):
+    """Two ranks' shards run one after the other on one GPU: their partial outputs sum to the
+    unsharded chain's output (what the all-reduce does across GPUs)."""
+    hidden, inter, m = 512, 1024, 24
+    case = make_ffn_case(oracle, hidden, inter, m, seed=5)
+    weights = [case[n] for n in ("w_gate", "s_gate", "w_up", "s_up", "w_down", "s_down")]
+    x = case["x"].cuda()
+    full = host(ffn.FfnInt4(ops, device(), hidden, inter, *weights, max_m=m).run(x, m)).copy()
+    parts = [host(ffn.FfnInt4(ops, device(), hidden, inter, *weights, world=2, rank=r, max_m=m,
+                              reduce="none").run(x, m)).copy() for r in range(2)]
+    assert max_rel(parts[0] + parts[1], full) < 1e-4

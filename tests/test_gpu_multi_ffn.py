@@ -1,0 +1,66 @@
+"""Two-rank run of the W4A16 feed-forward chain (needs 2 GPUs; skipped otherwise).
+
+Each rank runs its column shard of the gate|up projection, the SiLU-gate and its K shard of the
+down projection; NCCL sums the f32 partial outputs (all-reduce, then reduce-scatter).  Both ranks
+must end with the oracle's chain output.  No rank faults or exits mid-step; NVLS is off.
+"""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, shapes, ret):
+    import torch.distributed as dist
+
+    from kaio_b200 import ffn, ops
+    from oracle import oracle as orc
+    from test_ffn_cpu import ffn_oracle, make_ffn_case
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    ok = True
+    try:
+        dev = ops.KaioDevice(rank)
+        for (hidden, inter, m) in shapes:
+            case = make_ffn_case(orc, hidden, inter, m, seed=hidden + inter + m)
+            want = ffn_oracle(orc, case, hidden, inter, m)
+            weights = [case[n] for n in ("w_gate", "s_gate", "w_up", "s_up", "w_down", "s_down")]
+            x = case["x"].cuda()
+            for reduce in ("all", "scatter"):
+                chain = ffn.FfnInt4(ops, dev, hidden, inter, *weights, world=world, rank=rank, max_m=max(m, 16),
+                                    reduce=reduce)
+                got = chain.run(x, m)
+                torch.cuda.synchronize()
+                got = got.cpu().numpy()
+                ref = want if reduce == "all" else want[rank * (m // world):(rank + 1) * (m // world)]
+                rel = np.max(np.abs(got - ref) / np.maximum(np.abs(ref), 1.0))
+                ok = ok and got.shape == ref.shape and bool(np.all(np.isfinite(got))) and rel < 1e-2
+            assert ops.device_status(dev)[0] == 0
+        ret[rank] = ok
+    finally:
+        dist.destroy_process_group()
+
+
+def test_ffn_chain_two_ranks():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    world = 2
+    shapes = [(256, 512, 16), (1024, 2048, 300)]
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_worker, args=(world, _free_port(), shapes, ret), nprocs=world, join=True)
+    assert dict(ret) == {0: True, 1: True}
