@@ -190,6 +190,9 @@ def main():
                     help="run only the 70B FFN W4A16 leg and print its JSON (profiling aid)")
     ap.add_argument("--ffn-chain-only", action="store_true",
                     help="run only the 70B W4A16 feed-forward chain leg and print its JSON (profiling aid)")
+    ap.add_argument("--graphs", action="store_true",
+                    help="with --ffn-chain-only: also time the M <= 256 chains replayed from CUDA graphs "
+                         "(device time without the Python launch overhead)")
     ap.add_argument("--skip-extras", action="store_true",
                     help="only the headline step (no decode / e2e / cpu baseline legs)")
     args = ap.parse_args()
@@ -230,7 +233,7 @@ def main():
         return
 
     if args.ffn_chain_only:
-        res = bench_ffn_chain(torch, dist, ops, dev, rank, world, peaks)
+        res = bench_ffn_chain(torch, dist, ops, dev, rank, world, peaks, graphs=args.graphs)
         if rank == 0:
             print(json.dumps({"ffn_chain_70b_w4a16": res}), flush=True)
         if world > 1:
@@ -604,7 +607,23 @@ def bench_ffn70b(torch, dist, ops, sharding, dev, rank, world):
     return res
 
 
-def bench_ffn_chain(torch, dist, ops, dev, rank, world, peaks):
+def _graph_ms(torch, fn, reps=2, replays=20):
+    """`fn` called `reps` times, captured into one CUDA graph; ms per call when the graph is replayed."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(reps):
+            fn()
+    return _time_ms(torch, graph.replay, replays) / reps
+
+
+def bench_ffn_chain(torch, dist, ops, dev, rank, world, peaks, graphs=False):
     """The W4A16 feed-forward chain at Llama-70B shapes (hidden 8192, intermediate 28672):
     gate|up projection (one GEMM), SiLU-gate, down projection; across ranks column-parallel then
     row-parallel, so the only exchange is the sum of the [M, 8192] f32 partial outputs.  CUDA
@@ -625,6 +644,8 @@ def bench_ffn_chain(torch, dist, ops, dev, rank, world, peaks):
                packed(inter, hidden), scales(inter, hidden)]
     chain = ffn_mod.FfnInt4(ops, dev, hidden, inter, *weights, world=world, rank=rank, max_m=4096, reduce="all")
     scatter_rows = torch.empty((4096 // world) * hidden, dtype=torch.float32, device="cuda") if world > 1 else None
+    if world > 1:
+        chain._init_fused(torch.device("cuda", torch.cuda.current_device()))
     del weights
     torch.cuda.empty_cache()
     il = chain.i_loc
@@ -660,24 +681,46 @@ def bench_ffn_chain(torch, dist, ops, dev, rank, world, peaks):
         down()
         variant_down = ops.last_variant()
         ts = [_time_ms(torch, f, iters) for f in (gate_up, act, down, local)]
-        ts.append(_time_ms(torch, with_all_reduce, iters) if world > 1 else ts[3])
-        ts.append(_time_ms(torch, with_reduce_scatter, iters) if world > 1 and mm % world == 0 else ts[4])
-        t = torch.tensor(ts, dtype=torch.float64, device="cuda")
+        if world > 1:
+            # the three reductions, timed in two rounds in opposite order (the GPU sits at its power
+            # cap at M = 4096, so whatever is timed last would otherwise look slowest); min of the two
+            forms = [with_all_reduce, with_reduce_scatter if mm % world == 0 else with_all_reduce,
+                     lambda: chain.run_fused(x, mm)]
+            first = [_time_ms(torch, f, iters) for f in forms]
+            second = [_time_ms(torch, f, iters) for f in reversed(forms)][::-1]
+            ts += [min(a, b) for a, b in zip(first, second)]
+        else:
+            ts += [ts[3]] * 3
+        if graphs and mm <= 256:
+            # two calls per graph: the one-step fused form alternates between two staging buffers
+            tg = [_graph_ms(torch, local)]
+            tg += [_graph_ms(torch, with_all_reduce), _graph_ms(torch, lambda: chain.run_fused(x, mm))] \
+                if world > 1 else [tg[0], tg[0]]
+        else:
+            tg = [0.0, 0.0, 0.0]
+        t = torch.tensor(ts + tg, dtype=torch.float64, device="cuda")
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        t_gu, t_act, t_down, t_local, t_ar, t_rs = [float(v) for v in t]
+        t_gu, t_act, t_down, t_local, t_ar, t_rs, t_fused, tg_local, tg_ar, tg_fused = [float(v) for v in t]
+        t_best = min(t_ar, t_fused)
         flops = 2 * mm * hidden * inter * 3
         wbytes = 3 * (hidden * inter // 2 + (hidden // 128) * inter * 2)
         act_bytes = 3 * mm * il * 2  # the SiLU-gate pass of one rank: two f16 reads and one f16 write per element
         res[f"m{mm}"] = {
             "ms_gate_up_gemm": t_gu, "ms_silu_gate": t_act, "ms_down_gemm": t_down, "ms_three_launches": t_local,
-            "ms_with_all_reduce": t_ar, "ms_with_reduce_scatter": t_rs,
-            "tflops": flops / t_ar / 1e9, "weight_stream_gbs": wbytes / t_ar / 1e6,
+            "ms_with_all_reduce": t_ar, "ms_with_reduce_scatter": t_rs, "ms_fused_all_reduce": t_fused,
+            "fused_form": "-" if world == 1 else ("one step" if mm <= chain.m_one else "two steps"),
+            "tflops": flops / t_best / 1e9, "weight_stream_gbs": wbytes / t_best / 1e6,
             "silu_gate_gbs": act_bytes / t_act / 1e6, "silu_gate_frac_of_hbm_peak": act_bytes / t_act / 1e6 / peaks["hbm_gbs"],
             "variants": [variant_gu, "silu_gate_f16", variant_down]}
+        if graphs and mm <= 256:
+            res[f"m{mm}"]["cuda_graph_replay_ms"] = {"three_launches": tg_local, "with_all_reduce": tg_ar,
+                                                    "fused_all_reduce": tg_fused}
         del x
-    res["note"] = ("whole-job figures over all ranks: tflops = 6*M*8192*28672 / time with the all-reduce; "
-                   "weight_stream_gbs = packed weights + scales of the three projections / that time; "
+    res["note"] = ("whole-job figures over all ranks: tflops = 6*M*8192*28672 / the better of the NCCL and the fused "
+                   "all-reduce time; weight_stream_gbs = packed weights + scales of the three projections / that "
+                   "time; ms_fused_all_reduce: the down projection stores its partial tiles into the ranks' "
+                   "staging slots (peer memory), then a barrier and the slot sum; "
                    "silu_gate_gbs is one rank's pass (6 bytes per element of its [M, 28672/P] shard); the L2 "
                    "is not flushed between iterations")
     return res

@@ -202,6 +202,31 @@ int32_t kaio_b200_quantize_pack_int4(const float* w, size_t w_len, uint32_t* pac
                                      size_t packed_len, kaio_f16* scales, size_t scales_len,
                                      uint32_t k, uint32_t n, uint32_t group_size, void* stream);
 
+/* ---- row-parallel (K-sharded) W4A16 with the reduction fused into the GEMM (EXT) ---------- */
+
+/* This rank's K shard of a W4A16 GEMM (a [m, k] f16, weights packed [k, n], k = this rank's
+ * part of the full K): the f32 partial product [m, n] is stored by the GEMM's epilogue into
+ * staging slot `rank` of other ranks' staging buffers, tile by tile over peer memory.
+ * slot_ptrs[d] is rank d's staging buffer as mapped in this process, f32 [world][m][cols]:
+ *   scatter == 0: cols = n, the whole partial goes to every rank (one-step all-reduce);
+ *   scatter != 0: cols = n / world, column block d goes to rank d only (reduce-scatter; n / world
+ *                 must be a multiple of 64).
+ * After all ranks have met at a barrier, kaio_b200_sum_partials_f32 adds the slots. */
+int32_t kaio_b200_matmul_int4_peer_partials(const kaio_f16* a, size_t a_len,
+                                            const uint32_t* b_packed, size_t b_len,
+                                            const kaio_f16* scales, size_t scales_len,
+                                            void* const* slot_ptrs, size_t slot_len, uint32_t world,
+                                            uint32_t rank, int32_t scatter, uint32_t m, uint32_t n,
+                                            uint32_t k, uint32_t group_size, void* stream);
+
+/* out_d[row * out_ld + out_col0 + c] = sum over s < world (ascending) of slots[s][row][c] for each
+ * of the num_out (1..8) destinations, which may be peer memory (the all-gather step of a two-step
+ * all-reduce).  slots f32 [world][rows][cols]; cols, out_ld, out_col0 multiples of 4. */
+int32_t kaio_b200_sum_partials_f32(const float* slots, size_t slots_len, uint32_t world,
+                                   uint32_t rows, uint32_t cols, void* const* out_ptrs,
+                                   uint32_t num_out, size_t out_len, uint32_t out_ld,
+                                   uint32_t out_col0, void* stream);
+
 /* ---- gated activation (between the up/gate and the down projection of an FFN block) ---- */
 
 /* The user kernel of examples/fused_silu_gate/src/main.rs:13-21:

@@ -1009,6 +1009,126 @@ KAIO_API int32_t kaio_b200_matmul_int4_allgather(const kaio_f16* a, size_t a_len
                   op, "w4a16_tcgen05_allgather");
 }
 
+// ---------------------------------------------------------------- row-parallel W4A16 + reduction
+KAIO_API int32_t kaio_b200_matmul_int4_peer_partials(const kaio_f16* a, size_t a_len,
+                                                     const uint32_t* b_packed, size_t b_len,
+                                                     const kaio_f16* scales, size_t scales_len,
+                                                     void* const* slot_ptrs, size_t slot_len,
+                                                     uint32_t world, uint32_t rank, int32_t scatter,
+                                                     uint32_t m, uint32_t n, uint32_t k,
+                                                     uint32_t group_size, void* stream)
+{
+    const char* op = "matmul_int4_peer_partials";
+    if (world == 0 || world > 8 || rank >= world)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG, "%s: world must be 1..8 and rank < world (got %u, %u)",
+                    op, world, rank);
+    if (scatter && (n == 0 || n % world != 0 || (n / world) % 64 != 0))
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: N (%u) must split into %u blocks of a multiple of 64 columns", op, n, world);
+    const uint32_t cols = scatter ? n / world : n;
+    const size_t need_slots = (size_t)world * m * cols;
+    int32_t rc = validate_int4("f32", a_len, b_len, scales_len, (size_t)m * n, m, n, k, group_size);
+    if (rc)
+        return rc;
+    if (slot_len < need_slots)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: staging buffers too small: need %zu f32 (%u\xC3\x97%u\xC3\x97%u), got %zu", op,
+                    need_slots, world, m, cols, slot_len);
+    REQUIRE_PTR(a, op, "A");
+    REQUIRE_PTR(b_packed, op, "B packed");
+    REQUIRE_PTR(scales, op, "scales");
+    REQUIRE_PTR(slot_ptrs, op, "slot_ptrs");
+    OutputCopies copies = {};
+    copies.count = world;
+    copies.ld = cols;
+    copies.scatter_cols = scatter ? cols : 0u;
+    for (uint32_t r = 0; r < world; ++r) {
+        if (slot_ptrs[r] == nullptr || (uintptr_t)slot_ptrs[r] % 16 != 0)
+            return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                        "%s: staging pointer %u is null or not 16-byte aligned", op, r);
+        copies.ptrs[r] = reinterpret_cast<float*>(slot_ptrs[r]) + (size_t)rank * m * cols;
+    }
+    DeviceCtx* ctx;
+    if ((rc = get_ctx(&ctx)))
+        return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    DqProblem pr;
+    pr.w = b_packed;
+    pr.scales = reinterpret_cast<const __half*>(scales);
+    pr.col_scale = nullptr;
+    pr.scale = 1.0f;
+    pr.out = copies.ptrs[rank];
+    const __half* x = reinterpret_cast<const __half*>(a);
+    if (w4a16_decode_ok(x, &pr, 1, m, n, k)) {
+        if ((rc = ensure_workspace(ctx, w4a16_decode_workspace_bytes(*ctx, n, k),
+                                   w4a16_decode_num_counters(n))))
+            return rc;
+        return finish(launch_w4a16_decode(*ctx, x, pr, false, m, n, k, ctx->workspace,
+                                          ctx->tile_counters, s, &copies),
+                      op, "w4a16_decode_splitk_peer_partials");
+    }
+    if (m <= fused_max_m() && w4a16_fused_ok(x, &pr, 1, m, n, k)) {
+        const size_t ws = w4a16_fused_workspace_bytes(*ctx, 1, m, n, k);
+        if (ws && (rc = ensure_workspace(ctx, ws, w4a16_fused_num_counters(*ctx, 1, m, n, k))))
+            return rc;
+        return finish(launch_w4a16_fused(*ctx, x, &pr, 1, false, m, n, k,
+                                         ws ? ctx->workspace : nullptr,
+                                         ws ? ctx->tile_counters : nullptr, s, &copies),
+                      op, "w4a16_fused_dequant_peer_partials");
+    }
+    if (!dq_gemm_fast_path_ok(WFMT_S4_PACKED, x, &pr, 1, false, m, n, k))
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: A, B packed and the staging buffers must be 16-byte aligned and N a "
+                    "multiple of 8", op);
+    if ((rc = ensure_dq_workspace(ctx, dq_gemm_workspace_bytes(1, n, k))))
+        return rc;
+    return finish(launch_dq_gemm(*ctx, WFMT_S4_PACKED, x, &pr, 1, false, false, m, n, k,
+                                 ctx->dq_workspace, s, &copies),
+                  op, "w4a16_tcgen05_peer_partials");
+}
+
+KAIO_API int32_t kaio_b200_sum_partials_f32(const float* slots, size_t slots_len, uint32_t world,
+                                            uint32_t rows, uint32_t cols, void* const* out_ptrs,
+                                            uint32_t num_out, size_t out_len, uint32_t out_ld,
+                                            uint32_t out_col0, void* stream)
+{
+    const char* op = "sum_partials_f32";
+    if (world == 0 || rows == 0 || cols == 0)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG, "%s dimensions must be non-zero", op);
+    if (num_out == 0 || num_out > 8)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG, "%s: 1..8 destinations (got %u)", op, num_out);
+    if (cols % 4 != 0 || out_ld % 4 != 0 || out_col0 % 4 != 0 || out_ld < out_col0 + cols)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: cols, out_ld and out_col0 must be multiples of 4 and out_col0 + cols <= "
+                    "out_ld (got %u, %u, %u)", op, cols, out_ld, out_col0);
+    const size_t need_slots = (size_t)world * rows * cols;
+    if (slots_len < need_slots)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: staging buffer too small: need %zu f32, got %zu", op, need_slots, slots_len);
+    const size_t need_out = (size_t)(rows - 1) * out_ld + out_col0 + cols;
+    if (out_len < need_out)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: out buffers too small: need %zu f32, got %zu", op, need_out, out_len);
+    REQUIRE_PTR(slots, op, "slots");
+    REQUIRE_PTR(out_ptrs, op, "out_ptrs");
+    float* outs[8] = {};
+    for (uint32_t d = 0; d < num_out; ++d) {
+        if (out_ptrs[d] == nullptr || (uintptr_t)out_ptrs[d] % 16 != 0)
+            return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                        "%s: output pointer %u is null or not 16-byte aligned", op, d);
+        outs[d] = reinterpret_cast<float*>(out_ptrs[d]);
+    }
+    if ((uintptr_t)slots % 16 != 0)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG, "%s: staging buffer is not 16-byte aligned", op);
+    DeviceCtx* ctx;
+    int32_t rc;
+    if ((rc = get_ctx(&ctx)))
+        return rc;
+    return finish(launch_sum_partials(slots, world, rows, cols, outs, num_out, out_ld, out_col0,
+                                      static_cast<cudaStream_t>(stream)),
+                  op, "sum_partials_f32");
+}
+
 // ---------------------------------------------------------------- allocation-free decode entry
 // Scratch of kaio_b200_matmul_int4_noalloc: split-K partial tiles, tile arrival counters and a
 // status block, in a fixed array that is part of the loaded module (every GPU that loads the

@@ -70,6 +70,7 @@ struct Params {
     Problem probs[MAX_PROBS];
     uint32_t num_probs;
     uint32_t copies;  // each output block is stored to `copies` tensor maps (out[prob*copies + r])
+    uint32_t scatter_cols;  // > 0: a block goes only to map col0 / scatter_cols (see OutputCopies)
     uint32_t m, n, k;
     int post_scale;
     uint32_t* status;
@@ -344,9 +345,17 @@ f16_gemm_kernel(const __grid_constant__ TensorMaps maps, const Params p)
                     // one store per destination: with the sharded all-gather the destinations are
                     // the [M, N] buffers of every rank (peer memory), so the transfer overlaps the
                     // GEMM tile by tile
-                    for (uint32_t r = 0; r < p.copies; ++r)
-                        tma_store_2d(omap + r, stg_base + stg_off, (int32_t)col0,
+                    if (p.scatter_cols) {
+                        // scatter_cols is a multiple of the block width: one owner per block
+                        const uint32_t r = col0 / p.scatter_cols;
+                        tma_store_2d(omap + r, stg_base + stg_off,
+                                     (int32_t)(col0 - r * p.scatter_cols),
                                      (int32_t)(m0 + quarter * 32));
+                    } else {
+                        for (uint32_t r = 0; r < p.copies; ++r)
+                            tma_store_2d(omap + r, stg_base + stg_off, (int32_t)col0,
+                                         (int32_t)(m0 + quarter * 32));
+                    }
                     tma_store_commit();
                 }
             }
@@ -559,12 +568,14 @@ cudaError_t launch_dq_gemm(const DeviceCtx& ctx, int wfmt, const __half* x, cons
             base = probs[i < num_probs ? i : 0].out;
             ld = n;
         }
+        // in the scatter form a destination holds one block of scatter_cols columns
+        const uint64_t width = (copies && copies->scatter_cols) ? copies->scatter_cols : n;
         if (out_f16)
-            err = encode_tensor_map_2d(&maps.out[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, n, m,
-                                       ld * 2, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+            err = encode_tensor_map_2d(&maps.out[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, width,
+                                       m, ld * 2, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B);
         else
-            err = encode_tensor_map_2d(&maps.out[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, base, n, m,
-                                       ld * 4, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+            err = encode_tensor_map_2d(&maps.out[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, base, width,
+                                       m, ld * 4, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B);
         if (err != cudaSuccess)
             return err;
     }
@@ -575,6 +586,7 @@ cudaError_t launch_dq_gemm(const DeviceCtx& ctx, int wfmt, const __half* x, cons
     }
     p.num_probs = (uint32_t)num_probs;
     p.copies = num_copies;
+    p.scatter_cols = copies ? copies->scatter_cols : 0u;
     p.m = m;
     p.n = n;
     p.k = k;

@@ -106,6 +106,10 @@ struct OutputCopies {
     void* ptrs[8];
     uint32_t count;
     uint64_t ld;
+    // 0: every output column is stored to every destination at its own column index.
+    // > 0: column c is stored only to destination c / scatter_cols, at column c % scatter_cols
+    // (each destination receives one block of columns: the reduce-scatter form).
+    uint32_t scatter_cols;
 };
 
 size_t dq_gemm_workspace_bytes(int num_probs, uint32_t n, uint32_t k);
@@ -119,6 +123,11 @@ cudaError_t launch_quantize_rows_int8(const float* x, int8_t* q, float* scale, u
                                       uint32_t k, cudaStream_t stream);
 cudaError_t launch_quantize_pack_s4(const float* w, uint32_t* packed, __half* scales, uint32_t k,
                                     uint32_t n, cudaStream_t stream);
+
+// ---------------------------------------------------------------- sum of partial outputs
+cudaError_t launch_sum_partials(const float* slots, uint32_t world, uint32_t rows, uint32_t cols,
+                                float* const* outs, uint32_t num_out, uint64_t out_ld,
+                                uint32_t out_col0, cudaStream_t stream);
 
 // ---------------------------------------------------------------- gated activation
 cudaError_t launch_silu_gate_f32(const float* x, const float* gate, float* out, size_t n,

@@ -1,0 +1,60 @@
+// Sum of the f32 partial outputs of a row-parallel (K-sharded) GEMM.  The GEMM kernels of every
+// rank store their partial tiles straight into staging slots of the owning rank (peer memory,
+// slot index = source rank); after the ranks have met at a barrier, this kernel adds the slots
+// in ascending rank order (so every run and every rank produces the same bits) and stores the
+// sum to one or several destinations, which may again be peer memory (the all-gather half of a
+// two-step all-reduce).  A streaming pass: (world + copies) * 4 bytes per element.
+// KAIO is single-device; there is no reference counterpart.
+#include "kernels.h"
+
+namespace kaio {
+
+struct SumOut {
+    float* ptrs[8];
+};
+
+// slots: [world][rows][cols] f32.  out_d[row * out_ld + out_col0 + c] = sum_s slots[s][row][c].
+// cols, out_ld, out_col0 are multiples of 4 and all bases 16-byte aligned.
+__global__ void __launch_bounds__(256)
+sum_partials_kernel(const float* __restrict__ slots, uint32_t world, uint32_t rows, uint32_t cols,
+                    SumOut outs, uint32_t num_out, uint64_t out_ld, uint32_t out_col0)
+{
+    const uint32_t v = blockIdx.x * blockDim.x + threadIdx.x;
+    if (v >= cols / 4)
+        return;
+    const size_t slot_f4 = (size_t)rows * cols / 4;
+    const float4* base = reinterpret_cast<const float4*>(slots) + v;
+    for (uint32_t r = blockIdx.y; r < rows; r += gridDim.y) {
+        const float4* src = base + (size_t)r * (cols / 4);
+        // the slots were written by other GPUs: read them from L2, never from a stale L1 line
+        float4 acc = __ldcg(src);
+        for (uint32_t s = 1; s < world; ++s) {
+            const float4 t = __ldcg(src + s * slot_f4);
+            acc.x += t.x;
+            acc.y += t.y;
+            acc.z += t.z;
+            acc.w += t.w;
+        }
+        const size_t o = (size_t)r * out_ld + out_col0 + (size_t)v * 4;
+        for (uint32_t d = 0; d < num_out; ++d)
+            *reinterpret_cast<float4*>(outs.ptrs[d] + o) = acc;
+    }
+}
+
+cudaError_t launch_sum_partials(const float* slots, uint32_t world, uint32_t rows, uint32_t cols,
+                                float* const* outs, uint32_t num_out, uint64_t out_ld,
+                                uint32_t out_col0, cudaStream_t stream)
+{
+    SumOut so = {};
+    for (uint32_t d = 0; d < num_out && d < 8; ++d)
+        so.ptrs[d] = outs[d];
+    const uint32_t gx = (cols / 4 + 255) / 256;
+    uint32_t gy = (148 * 8 + gx - 1) / gx;
+    gy = gy > rows ? rows : gy;
+    gy = gy < 1 ? 1 : (gy > 65535 ? 65535 : gy);
+    sum_partials_kernel<<<dim3(gx, gy, 1), 256, 0, stream>>>(slots, world, rows, cols, so, num_out,
+                                                             out_ld, out_col0);
+    return cudaGetLastError();
+}
+
+}  // namespace kaio

@@ -75,6 +75,7 @@ struct Params {
     const __half* scales;  // [K/128, N]
     void* out[8];          // destinations, f32 or f16, row stride `ld` (one entry unless sharded)
     uint32_t copies;
+    uint32_t scatter_cols;  // see OutputCopies
     uint64_t ld;
     float* partials;       // [grid][2][128*16]
     uint32_t* counters;    // [tiles]
@@ -560,11 +561,15 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const Params p)
             if (write_out) {
                 const uint32_t col = tile * BN + tid;
                 if (col < p.n) {
-                    for (uint32_t d = 0; d < p.copies; ++d) {
+                    // scatter form: this column belongs to one destination only
+                    const uint32_t d_lo = p.scatter_cols ? col / p.scatter_cols : 0u;
+                    const uint32_t d_hi = p.scatter_cols ? d_lo + 1u : p.copies;
+                    const uint32_t dcol = p.scatter_cols ? col - d_lo * p.scatter_cols : col;
+                    for (uint32_t d = d_lo; d < d_hi; ++d) {
 #pragma unroll
                         for (uint32_t r = 0; r < NROWS; ++r) {
                             if (r < p.m) {
-                                const size_t idx = (size_t)r * p.ld + col;
+                                const size_t idx = (size_t)r * p.ld + dcol;
                                 if (OUT_F16)
                                     reinterpret_cast<__half*>(p.out[d])[idx] = __float2half_rn(acc[r]);
                                 else
@@ -641,6 +646,7 @@ cudaError_t launch_w4a16_decode(const DeviceCtx& ctx, const __half* x, const DqP
         p.out[i] = copies ? copies->ptrs[(uint32_t)i < copies->count ? i : 0] : prob.out;
     p.copies = copies ? copies->count : 1u;
     p.ld = copies ? copies->ld : n;
+    p.scatter_cols = copies ? copies->scatter_cols : 0u;
     p.partials = reinterpret_cast<float*>(workspace);
     p.counters = counters;
     p.m = m;

@@ -91,6 +91,7 @@ struct Params {
     // all-gather form: every rank's output buffer, peer memory); row stride `ld` elements.
     void* copies[8];
     uint32_t num_copies;  // 0 = store to probs[prob].out with row stride n
+    uint32_t scatter_cols;  // see OutputCopies
     uint64_t ld;
     // Stream-K (too few tiles to fill the SMs' last round): the (tile, k stage) units are cut
     // into gridDim contiguous ranges; a tile that a cut splits is summed from f32 partial
@@ -484,15 +485,18 @@ w4a16_fused_kernel(const __grid_constant__ TensorMaps maps, const Params p)
             auto store_rows = [&](const uint32_t (&r)[32], uint32_t c) {
                 if (col >= p.n)
                     return;
-                const uint32_t nd = p.num_copies ? p.num_copies : 1u;
-                for (uint32_t d = 0; d < nd; ++d) {
+                // scatter form: this column belongs to one destination only
+                const uint32_t d_lo = p.scatter_cols ? col / p.scatter_cols : 0u;
+                const uint32_t d_hi = p.scatter_cols ? d_lo + 1u : (p.num_copies ? p.num_copies : 1u);
+                const uint32_t dcol = p.scatter_cols ? col - d_lo * p.scatter_cols : col;
+                for (uint32_t d = d_lo; d < d_hi; ++d) {
                     void* const dst = p.num_copies ? p.copies[d] : p.probs[prob].out;
                     const size_t ld = p.num_copies ? (size_t)p.ld : (size_t)p.n;
 #pragma unroll
                     for (uint32_t i = 0; i < 32; ++i) {
                         const uint32_t rr = m0 + c * 32 + i;
                         if (rr < p.m) {
-                            const size_t idx = (size_t)rr * ld + col;
+                            const size_t idx = (size_t)rr * ld + dcol;
                             if (p.out_f16)
                                 reinterpret_cast<__half*>(dst)[idx] =
                                     __float2half_rn(__uint_as_float(r[i]));
@@ -724,6 +728,7 @@ static cudaError_t launch_fused_n(const DeviceCtx& ctx, const __half* x, const D
             p.copies[i] = copies->ptrs[i];
         p.num_copies = copies->count;
         p.ld = copies->ld;
+        p.scatter_cols = copies->scatter_cols;
     }
     p.status = ctx.status;
     const uint32_t tiles = ((m + NROWS - 1) / NROWS) * ((n + BN - 1) / BN) * (uint32_t)num_probs;

@@ -10,7 +10,12 @@ Across ``P`` ranks the chain is column-parallel then row-parallel: rank ``r`` ow
 ``[r*I/P, (r+1)*I/P)`` of W_gate and W_up and the matching K-rows of W_down, so the intermediate
 never leaves the GPU (no all-gather of ``[M, I]``) and the only exchange is the sum of the
 ``[M, H]`` f32 partial outputs: an all-reduce, or a reduce-scatter when each rank only needs its
-own ``M/P`` rows.
+own ``M/P`` rows.  With ``reduce="fused"`` the sum does not go through NCCL: the down projection's
+epilogue stores its partial tiles straight into staging slots of the other ranks (peer memory,
+symmetric allocation), the ranks meet at a barrier, and a small kernel adds the slots in rank order
+(bit-identical on every rank and run).  Small outputs go whole to every rank (one step, one
+barrier); large ones are scattered by column block and the summed blocks are stored back to every
+rank (two steps, the traffic of a ring all-reduce).
 
 The helpers at the top are layout logic and run on CPU tensors too.
 """
@@ -74,8 +79,8 @@ class FfnInt4:
 
     def __init__(self, ops, device, hidden: int, inter: int, w_gate, s_gate, w_up, s_up, w_down, s_down,
                  world: int = 1, rank: int = 0, group=None, max_m: int = 4096, reduce: str = "all"):
-        if reduce not in ("all", "scatter", "none"):
-            raise ValueError(f"reduce must be 'all', 'scatter' or 'none', got {reduce!r}")
+        if reduce not in ("all", "scatter", "none", "fused"):
+            raise ValueError(f"reduce must be 'all', 'scatter', 'none' or 'fused', got {reduce!r}")
         self.ops, self.device, self.group = ops, device, group
         self.hidden, self.inter, self.world, self.rank, self.reduce = hidden, inter, world, rank, reduce
         lo, hi = shard_bounds(inter, world, rank, multiple=GROUP)
@@ -95,6 +100,58 @@ class FfnInt4:
         self.out = torch.empty(max_m * hidden, dtype=torch.float32, device=dev)
         self.rows = torch.empty((max_m // world) * hidden, dtype=torch.float32, device=dev) \
             if (world > 1 and reduce == "scatter") else None
+        if world > 1 and reduce == "fused":
+            self._init_fused(dev)
+
+    # ---- reduction fused into the down projection (peer stores + barrier + slot sum)
+
+    #: one step while the bytes it sends beyond a two-step all-reduce cost less than a barrier
+    ONE_STEP_EXTRA_BYTES = 6 << 20
+
+    def one_step(self, m: int) -> bool:
+        p = self.world
+        return (p - 1) * (1.0 - 2.0 / p) * m * self.hidden * 4 <= self.ONE_STEP_EXTRA_BYTES
+
+    def _init_fused(self, dev):
+        import torch.distributed._symmetric_memory as symm_mem
+        if self.hidden % (self.world * 64) != 0:
+            raise ValueError(f"hidden={self.hidden} must split into {self.world} blocks of a multiple of 64 columns")
+        group = self.group if self.group is not None else dist.group.WORLD
+        self.m_one = max([m for m in range(1, self.max_m + 1) if self.one_step(m)] or [0])
+        # [two one-step staging buffers, used alternately][the two-step staging buffer]
+        self.one_elems = self.world * self.m_one * self.hidden
+        two_elems = self.max_m * self.hidden
+        self.stage = symm_mem.empty(2 * self.one_elems + two_elems, dtype=torch.float32, device=dev)
+        self.stage_h = symm_mem.rendezvous(self.stage, group)
+        self.out_sym = symm_mem.empty(self.max_m * self.hidden, dtype=torch.float32, device=dev)
+        self.out_h = symm_mem.rendezvous(self.out_sym, group)
+        self.stage_ptrs = [int(p) for p in self.stage_h.buffer_ptrs]
+        self.out_ptrs = [int(p) for p in self.out_h.buffer_ptrs]
+        self.flip = 0
+
+    def run_fused(self, x: torch.Tensor, m: int) -> torch.Tensor:
+        """gate|up, SiLU-gate, then the down projection whose epilogue stores into the ranks' staging
+        slots, the barrier, and the slot sum.  Returns the complete f32 ``[m, hidden]``."""
+        if m > self.max_m:
+            raise ValueError(f"m={m} exceeds max_m={self.max_m}")
+        ops, d, il, h, p = self.ops, self.device, self.i_loc, self.hidden, self.world
+        ops.matmul_int4(d, x, self.w_gu, self.s_gu, self.gu, m, 2 * il, h, GROUP)
+        ops.silu_gate_f16(d, self.gu, self.gu.view(-1)[il:], self.act, m, il, x_ld=2 * il, gate_ld=2 * il)
+        if m <= self.m_one:
+            off = self.flip * self.one_elems
+            self.flip ^= 1
+            ops.matmul_int4_peer_partials(d, self.act, self.w_down, self.s_down, [q + off * 4 for q in self.stage_ptrs],
+                                          p * m * h, p, self.rank, False, m, h, il, GROUP)
+            self.stage_h.barrier()  # every rank's partial has landed in every rank's slots
+            ops.sum_partials_f32(d, self.stage[off:off + p * m * h], p, m, h, [self.out.data_ptr()], m * h, h, 0)
+            return self.out[: m * h].view(m, h)
+        off, blk = 2 * self.one_elems, h // p
+        ops.matmul_int4_peer_partials(d, self.act, self.w_down, self.s_down, [q + off * 4 for q in self.stage_ptrs],
+                                      m * h, p, self.rank, True, m, h, il, GROUP)
+        self.stage_h.barrier()  # column block r of every rank's partial has landed on rank r
+        ops.sum_partials_f32(d, self.stage[off:off + m * h], p, m, blk, self.out_ptrs, m * h, h, self.rank * blk)
+        self.out_h.barrier()  # every rank's summed block has landed in every rank's output
+        return self.out_sym[: m * h].view(m, h)
 
     def local(self, x: torch.Tensor, m: int) -> torch.Tensor:
         """The three launches of this rank; returns the f32 ``[m, hidden]`` partial sum."""
@@ -108,6 +165,8 @@ class FfnInt4:
         return self.out[: m * self.hidden].view(m, self.hidden)
 
     def run(self, x: torch.Tensor, m: int) -> torch.Tensor:
+        if self.world > 1 and self.reduce == "fused":
+            return self.run_fused(x, m)
         part = self.local(x, m)
         if self.world == 1 or self.reduce == "none":
             return part

@@ -138,6 +138,28 @@ def matmul_int4_allgather(device, a, b_packed_shard, scales_shard, out_ptrs, out
           C.cast(arr, C.c_void_p), C.c_size_t(out_numel), world, rank, m, n_total, k, group_size)
 
 
+def matmul_int4_peer_partials(device, a, b_packed, scales, slot_ptrs, slot_numel, world, rank, scatter,
+                              m, n, k, group_size=GROUP_SIZE):
+    """Extension: this rank's K shard of a W4A16 GEMM; the f32 partial ``[m, n]`` is stored by the
+    kernel into slot ``rank`` of the ranks' staging buffers (``slot_ptrs``: ``world`` device
+    addresses as mapped in this process, each f32 ``[world][m][cols]``).  ``scatter=False``: the
+    whole partial to every rank (``cols = n``); ``scatter=True``: column block ``d`` to rank ``d``
+    only (``cols = n / world``)."""
+    arr = (C.c_void_p * world)(*[C.c_void_p(int(p)) for p in slot_ptrs])
+    _call(device, "kaio_b200_matmul_int4_peer_partials", *_buf(a, torch.float16, "a"),
+          *_buf(b_packed, torch.int32, "b_packed"), *_buf(scales, torch.float16, "scales"),
+          C.cast(arr, C.c_void_p), C.c_size_t(slot_numel), world, rank, 1 if scatter else 0, m, n, k, group_size)
+
+
+def sum_partials_f32(device, slots, world, rows, cols, out_ptrs, out_numel, out_ld, out_col0=0):
+    """Extension: ``out_d[row, out_col0 + c] = sum_s slots[s][row][c]`` (ascending ``s``) for every
+    destination address in ``out_ptrs`` (f32 buffers with row stride ``out_ld``, possibly peer
+    memory)."""
+    arr = (C.c_void_p * len(out_ptrs))(*[C.c_void_p(int(p)) for p in out_ptrs])
+    _call(device, "kaio_b200_sum_partials_f32", *_buf(slots, torch.float32, "slots"), world, rows, cols,
+          C.cast(arr, C.c_void_p), len(out_ptrs), C.c_size_t(out_numel), out_ld, out_col0)
+
+
 # ------------------------------------------------------------------ fused QKV
 
 def qkv_project_int8(device, x, w_q, w_k, w_v, scale_q, scale_k, scale_v, q_out, k_out, v_out, m, n, k):

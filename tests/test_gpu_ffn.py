@@ -121,3 +121,54 @@ def test_ffn_chain_partial_sums_add_up(oracle):
     parts = [host(ffn.FfnInt4(ops, device(), hidden, inter, *weights, world=2, rank=r, max_m=m,
                               reduce="none").run(x, m)).copy() for r in range(2)]
     assert max_rel(parts[0] + parts[1], full) < 1e-4
+
+
+@pytest.mark.parametrize("m", [8, 64, 600])
+@pytest.mark.parametrize("scatter", [False, True])
+def test_peer_partials_two_ranks_emulated_on_one_gpu(oracle, m, scatter):
+    """The row-parallel GEMM with its reduction in the epilogue, both ranks run one after the other
+    on one GPU (nothing waits on anything): each "rank" stores its f32 partial into slot `rank` of
+    both staging buffers (whole, or its column blocks scattered to their owners); the slot sum then
+    gives the full-K product.  m = 8 / 64 / 600 go through the decode, fused-dequant and
+    tensor-map-store kernels."""
+    world, n, k = 2, 512, 512
+    kl, blk = k // world, n // world
+    rng = np.random.default_rng(m + scatter)
+    w = rng.integers(-8, 8, (k, n), dtype=np.int8)
+    a = rng.standard_normal((m, k)).astype(np.float16)
+    sc = rng.uniform(0.005, 0.02, (k // 128, n)).astype(np.float16)
+    want = np.asarray(oracle.matmul_int4(a.reshape(-1), oracle.pack_s4(w, k, n), sc.reshape(-1), m, n, k,
+                                         f16_out=False)).reshape(m, n)
+    d = device()
+    cols = blk if scatter else n
+    stages = [torch.full((world * m * cols,), float("nan"), device="cuda") for _ in range(world)]
+    ptrs = [s.data_ptr() for s in stages]
+    for rank in range(world):
+        a_loc = dev(np.ascontiguousarray(a[:, rank * kl:(rank + 1) * kl]))
+        w_loc = dev(oracle.pack_s4(np.ascontiguousarray(w[rank * kl:(rank + 1) * kl]), kl, n))
+        s_loc = dev(np.ascontiguousarray(sc[rank * kl // 128:(rank + 1) * kl // 128]))
+        ops.matmul_int4_peer_partials(d, a_loc, w_loc, s_loc, ptrs, world * m * cols, world, rank, scatter, m, n, kl)
+        assert ops.last_variant().endswith("_peer_partials")
+    outs = [torch.full((m * n,), float("nan"), device="cuda") for _ in range(world)]
+    optrs = [o.data_ptr() for o in outs]
+    for rank in range(world):
+        if scatter:  # the owner sums its column block and stores it to both outputs
+            ops.sum_partials_f32(d, stages[rank], world, m, blk, optrs, m * n, n, rank * blk)
+        else:
+            ops.sum_partials_f32(d, stages[rank], world, m, n, [optrs[rank]], m * n, n, 0)
+    assert ops.device_status(d)[0] == 0
+    g0, g1 = host(outs[0], (m, n)), host(outs[1], (m, n))
+    assert np.array_equal(g0, g1)
+    assert max_rel(g0, want) < 1e-3
+
+
+def test_sum_partials_argument_errors():
+    d = device()
+    s = torch.zeros(2 * 4 * 16, device="cuda")
+    o = torch.zeros(4 * 16, device="cuda")
+    with pytest.raises(InvalidConfig, match="multiples of 4"):
+        ops.sum_partials_f32(d, s, 2, 4, 14, [o.data_ptr()], o.numel(), 16, 0)
+    with pytest.raises(InvalidConfig, match="staging buffer too small"):
+        ops.sum_partials_f32(d, s[:100], 2, 4, 16, [o.data_ptr()], o.numel(), 16, 0)
+    with pytest.raises(InvalidConfig, match="out buffers too small"):
+        ops.sum_partials_f32(d, s, 2, 4, 16, [o.data_ptr()], 60, 16, 0)

@@ -1,4 +1,4 @@
-"""Two-rank run of the W4A16 feed-forward chain (needs 2 GPUs; skipped otherwise).
+"""Two- and four-rank runs of the W4A16 feed-forward chain (need 2 / 4 GPUs; skipped otherwise).
 
 Each rank runs its column shard of the gate|up projection, the SiLU-gate and its K shard of the
 down projection; NCCL sums the f32 partial outputs (all-reduce, then reduce-scatter).  Both ranks
@@ -48,19 +48,36 @@ def _worker(rank, world, port, shapes, ret):
                 ref = want if reduce == "all" else want[rank * (m // world):(rank + 1) * (m // world)]
                 rel = np.max(np.abs(got - ref) / np.maximum(np.abs(ref), 1.0))
                 ok = ok and got.shape == ref.shape and bool(np.all(np.isfinite(got))) and rel < 1e-2
+            # the reduction fused into the down projection: one step (whole partials to every rank),
+            # then two steps (column blocks scattered, summed blocks stored back), three runs each so
+            # that the staging buffers are reused; every run must give the same bits
+            for two_step in (False, True):
+                chain = ffn.FfnInt4(ops, dev, hidden, inter, *weights, world=world, rank=rank, max_m=max(m, 16),
+                                    reduce="fused")
+                if two_step:
+                    chain.m_one = 0
+                runs = []
+                for _ in range(3):
+                    got = chain.run(x, m)
+                    torch.cuda.synchronize()
+                    runs.append(got.cpu().numpy().copy())
+                rel = np.max(np.abs(runs[0] - want) / np.maximum(np.abs(want), 1.0))
+                same = all(np.array_equal(runs[0], r) for r in runs[1:])
+                ok = ok and runs[0].shape == want.shape and bool(np.all(np.isfinite(runs[0]))) and rel < 1e-2 and same
+                dist.barrier()
             assert ops.device_status(dev)[0] == 0
         ret[rank] = ok
     finally:
         dist.destroy_process_group()
 
 
-def test_ffn_chain_two_ranks():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
+@pytest.mark.parametrize("world", [2, 4])
+def test_ffn_chain_ranks(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
-    world = 2
     shapes = [(256, 512, 16), (1024, 2048, 300)]
     mgr = mp.Manager()
     ret = mgr.dict()
     mp.spawn(_worker, args=(world, _free_port(), shapes, ret), nprocs=world, join=True)
-    assert dict(ret) == {0: True, 1: True}
+    assert dict(ret) == {r: True for r in range(world)}
