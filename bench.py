@@ -306,14 +306,22 @@ def main():
     ms_per_step = total_ms / args.steps
     value = total_ops / (ms_per_step * 1e-3) / 1e12
 
-    ffn = chain = None
+    ffn = chain = decode = qkv_attn = None
     if not args.skip_extras:
-        for p in probs:  # free the headline buffers before the 70B-shape leg
+        for p in probs:  # free the headline buffers before the other legs
             p.clear()
         torch.cuda.empty_cache()
+        if world == 1:
+            # The latency-sensitive decode leg runs before the legs that allocate and free gigabytes:
+            # after them the same kernel on freshly allocated buffers measures 10-40 % slower (18 us
+            # alone or straight after the headline, 20-27 us after the 70B-shape legs).
+            decode = bench_decode(torch, ops, dev, peaks, load_traffic())
+            qkv_attn = bench_qkv_attention(torch, ops, dev, peaks)
+            torch.cuda.empty_cache()
         ffn = bench_ffn70b(torch, dist, ops, sharding, dev, rank, world)
         torch.cuda.empty_cache()
         chain = bench_ffn_chain(torch, dist, ops, dev, rank, world, peaks)
+        torch.cuda.empty_cache()
 
     if rank != 0:
         if world > 1:
@@ -361,8 +369,8 @@ def main():
     if chain is not None:
         line["ffn_chain_70b_w4a16"] = chain
     if not args.skip_extras and world == 1:
-        line["w4a16_decode"] = bench_decode(torch, ops, dev, peaks, traffic)
-        line["qkv_attention"] = bench_qkv_attention(torch, ops, dev, peaks)
+        line["w4a16_decode"] = decode
+        line["qkv_attention"] = qkv_attn
         line["e2e"] = bench_e2e(torch, ops, dev, m, total_ops, steps=max(3, min(args.steps, 10)))
         rows = m  # the whole step on the host cores: about 10 s with 16 threads
         o, s, threads = cpu_int8_sample(rows)
