@@ -652,8 +652,16 @@ def bench_ffn_chain(torch, dist, ops, dev, rank, world, peaks, graphs=False):
                packed(inter, hidden), scales(inter, hidden)]
     chain = ffn_mod.FfnInt4(ops, dev, hidden, inter, *weights, world=world, rank=rank, max_m=4096, reduce="all")
     scatter_rows = torch.empty((4096 // world) * hidden, dtype=torch.float32, device="cuda") if world > 1 else None
+    fused_ok = world > 1
     if world > 1:
-        chain._init_fused(torch.device("cuda", torch.cuda.current_device()))
+        try:  # symmetric memory may be unavailable: then only the NCCL forms are timed
+            chain._init_fused(torch.device("cuda", torch.cuda.current_device()))
+        except Exception as exc:  # noqa: BLE001
+            fused_ok = False
+            print(f"fused all-reduce unavailable on rank {rank}: {exc!r}", file=sys.stderr, flush=True)
+        flag = torch.tensor([1 if fused_ok else 0], device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)  # every rank or none
+        fused_ok = bool(flag.item())
     del weights
     torch.cuda.empty_cache()
     il = chain.i_loc
@@ -693,7 +701,7 @@ def bench_ffn_chain(torch, dist, ops, dev, rank, world, peaks, graphs=False):
             # the three reductions, timed in two rounds in opposite order (the GPU sits at its power
             # cap at M = 4096, so whatever is timed last would otherwise look slowest); min of the two
             forms = [with_all_reduce, with_reduce_scatter if mm % world == 0 else with_all_reduce,
-                     lambda: chain.run_fused(x, mm)]
+                     (lambda: chain.run_fused(x, mm)) if fused_ok else with_all_reduce]
             first = [_time_ms(torch, f, iters) for f in forms]
             second = [_time_ms(torch, f, iters) for f in reversed(forms)][::-1]
             ts += [min(a, b) for a, b in zip(first, second)]
@@ -702,8 +710,8 @@ def bench_ffn_chain(torch, dist, ops, dev, rank, world, peaks, graphs=False):
         if graphs and mm <= 256:
             # two calls per graph: the one-step fused form alternates between two staging buffers
             tg = [_graph_ms(torch, local)]
-            tg += [_graph_ms(torch, with_all_reduce), _graph_ms(torch, lambda: chain.run_fused(x, mm))] \
-                if world > 1 else [tg[0], tg[0]]
+            tg += [_graph_ms(torch, with_all_reduce),
+                   _graph_ms(torch, lambda: chain.run_fused(x, mm)) if fused_ok else 0.0] if world > 1 else [tg[0], tg[0]]
         else:
             tg = [0.0, 0.0, 0.0]
         t = torch.tensor(ts + tg, dtype=torch.float64, device="cuda")
@@ -717,7 +725,7 @@ def bench_ffn_chain(torch, dist, ops, dev, rank, world, peaks, graphs=False):
         res[f"m{mm}"] = {
             "ms_gate_up_gemm": t_gu, "ms_silu_gate": t_act, "ms_down_gemm": t_down, "ms_three_launches": t_local,
             "ms_with_all_reduce": t_ar, "ms_with_reduce_scatter": t_rs, "ms_fused_all_reduce": t_fused,
-            "fused_form": "-" if world == 1 else ("one step" if mm <= chain.m_one else "two steps"),
+            "fused_form": "-" if not fused_ok else ("one step" if mm <= chain.m_one else "two steps"),
             "tflops": flops / t_best / 1e9, "weight_stream_gbs": wbytes / t_best / 1e6,
             "silu_gate_gbs": act_bytes / t_act / 1e6, "silu_gate_frac_of_hbm_peak": act_bytes / t_act / 1e6 / peaks["hbm_gbs"],
             "variants": [variant_gu, "silu_gate_f16", variant_down]}

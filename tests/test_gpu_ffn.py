@@ -125,13 +125,14 @@ def test_ffn_chain_partial_sums_add_up(oracle):
 
 @pytest.mark.parametrize("m", [8, 64, 600])
 @pytest.mark.parametrize("scatter", [False, True])
-def test_peer_partials_two_ranks_emulated_on_one_gpu(oracle, m, scatter):
-    """The row-parallel GEMM with its reduction in the epilogue, both ranks run one after the other
+@pytest.mark.parametrize("world", [2, 8])
+def test_peer_partials_ranks_emulated_on_one_gpu(oracle, m, scatter, world):
+    """The row-parallel GEMM with its reduction in the epilogue, all ranks run one after the other
     on one GPU (nothing waits on anything): each "rank" stores its f32 partial into slot `rank` of
-    both staging buffers (whole, or its column blocks scattered to their owners); the slot sum then
+    all staging buffers (whole, or its column blocks scattered to their owners); the slot sum then
     gives the full-K product.  m = 8 / 64 / 600 go through the decode, fused-dequant and
     tensor-map-store kernels."""
-    world, n, k = 2, 512, 512
+    n, k = 512, 1024
     kl, blk = k // world, n // world
     rng = np.random.default_rng(m + scatter)
     w = rng.integers(-8, 8, (k, n), dtype=np.int8)
@@ -152,14 +153,14 @@ def test_peer_partials_two_ranks_emulated_on_one_gpu(oracle, m, scatter):
     outs = [torch.full((m * n,), float("nan"), device="cuda") for _ in range(world)]
     optrs = [o.data_ptr() for o in outs]
     for rank in range(world):
-        if scatter:  # the owner sums its column block and stores it to both outputs
+        if scatter:  # the owner sums its column block and stores it to every output
             ops.sum_partials_f32(d, stages[rank], world, m, blk, optrs, m * n, n, rank * blk)
         else:
             ops.sum_partials_f32(d, stages[rank], world, m, n, [optrs[rank]], m * n, n, 0)
     assert ops.device_status(d)[0] == 0
-    g0, g1 = host(outs[0], (m, n)), host(outs[1], (m, n))
-    assert np.array_equal(g0, g1)
-    assert max_rel(g0, want) < 1e-3
+    got = [host(o, (m, n)) for o in outs]
+    assert all(np.array_equal(got[0], g) for g in got[1:])
+    assert max_rel(got[0], want) < 1e-3
 
 
 def test_sum_partials_argument_errors():
