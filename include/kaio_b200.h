@@ -16,7 +16,16 @@
  *   - `stream` is a CUstream / cudaStream_t (NULL = the legacy default stream).  Work is
  *     enqueued on it and the call returns without synchronising, like the reference
  *     (kaio-ops/src/matmul_int8_kernel.rs:1497-1511);
- *   - the device is the calling thread's current CUDA device;
+ *   - the device is the calling thread's current CUDA device, and the output buffer must live
+ *     on it: the entry points of the drop-in ops look the pointer's device up
+ *     (cudaPointerGetAttributes) and return KAIO_B200_ERR_INVALID_CONFIG on a mismatch, where the
+ *     reference compares the buffer's device ordinal with the KaioDevice's;
+ *   - scratch the kernels need beyond the caller's buffers (split-K partial tiles, arrival
+ *     counters, dequantised weights) is owned by the library, one set per (device, stream), so
+ *     calls on different streams may overlap; it grows on demand with cudaFree + cudaMalloc,
+ *     which synchronises the device.  Growth is refused (KAIO_B200_ERR_INVALID_CONFIG) while the
+ *     stream is being captured into a CUDA graph, and a graph captured earlier keeps the old
+ *     address: run every op once at its largest shape before capturing;
  *   - return value: KAIO_B200_OK or an error code; kaio_b200_last_error() returns the
  *     calling thread's last message.  For KAIO_B200_ERR_INVALID_CONFIG the message is
  *     the text the reference puts into KaioError::InvalidConfig;
@@ -97,16 +106,21 @@ int32_t kaio_b200_matmul_int4_f16out(const kaio_f16* a, size_t a_len, const uint
                                      uint32_t group_size, void* stream);
 
 /* No counterpart in the reference.  kaio_b200_matmul_int4 for decode shapes (m <= 16) that
- * allocates nothing: same arguments, same result, but the split-K scratch (partial tiles,
- * arrival counters, status words) lives in a fixed ~2.6 MB array inside the library instead of a
- * cudaMalloc'd workspace.  It is for callers that cannot allocate at call time: a host runtime
- * whose memory pool already owns all device memory (a later cudaMalloc would fail), or a
+ * allocates nothing: same arguments, same result bit for bit, but the split-K scratch (partial
+ * tiles, arrival counters, status words) lives in a fixed ~2.6 MB array inside the library instead
+ * of a cudaMalloc'd workspace.  It is for callers that cannot allocate at call time: a host
+ * runtime whose memory pool already owns all device memory (a later cudaMalloc would fail), or a
  * latency-critical loop that must not hit the device-wide synchronisation an allocation implies.
  * Limits (rejected with KAIO_B200_ERR_INVALID_CONFIG): m <= 16, n <= 524288, a device with at
- * most 160 SMs, 16-byte aligned a / b_packed.  The first call on each device looks up the
- * array's device address; make that call before any stream capture.  Every call on a device
- * shares the one array, so calls that may overlap on the GPU (different streams) race: order
- * them.  The call clears the counters and status words it needs on `stream` before launching. */
+ * most 160 SMs, 16-byte aligned a / b_packed.
+ * The first call on each device looks up the array's device address.  With CUDA's lazy module
+ * loading that look-up is also what places the array in device memory, so the first call can
+ * still claim those ~2.6 MB: make it before a pool reserves the rest of the device and before any
+ * stream capture.  Later calls allocate nothing.
+ * Every call on a device shares the one array, so calls that may overlap on the GPU (different
+ * streams) race: order them.  The call clears the arrival counters on `stream` before launching;
+ * the status words persist until kaio_b200_device_status() (which allocates nothing either) has
+ * reported them. */
 int32_t kaio_b200_matmul_int4_noalloc(const kaio_f16* a, size_t a_len, const uint32_t* b_packed,
                                       size_t b_len, const kaio_f16* scales, size_t scales_len,
                                       float* c, size_t c_len, uint32_t m, uint32_t n, uint32_t k,
@@ -248,10 +262,20 @@ int32_t kaio_b200_silu_gate_f16(const kaio_f16* x, size_t x_len, const kaio_f16*
 /* Last error message of the calling thread ("" if none). */
 const char* kaio_b200_last_error(void);
 
-/* Synchronises `stream` and reads the current device's status block: code[0] = 0 when no
- * kernel reported a problem, else {code, reporting block, site, kernel id}; the block is
- * cleared.  Returns KAIO_B200_ERR_TIMEOUT when code[0] != 0. */
+/* Synchronises `stream` and reads the current device's status blocks (the regular entry points'
+ * and the allocation-free entry point's): code[0] = 0 when no kernel reported a problem, else
+ * {code, reporting block, site, kernel id} of the first report; that block is cleared and the
+ * device's split-K arrival counters are reset, so the next call starts clean.  Returns
+ * KAIO_B200_ERR_TIMEOUT when code[0] != 0.  Allocates nothing.
+ * No counterpart in the reference, whose kernels have no device-side waits
+ * (kaio-runtime/src/error.rs:4-37 has no timeout variant). */
 int32_t kaio_b200_device_status(void* stream, uint32_t code[4]);
+
+/* Test hook (no counterpart in the reference): launches one CTA that waits `budget_us`
+ * microseconds on a barrier nothing arrives at, gives up and returns normally; the next
+ * kaio_b200_device_status() then reports KAIO_B200_ERR_TIMEOUT.  This is the path every kernel of
+ * the library takes when a device-side wait runs out: a status code, never a hang or a trap. */
+int32_t kaio_b200_selftest_bounded_wait(uint32_t budget_us, void* stream);
 
 /* Name of the kernel variant the last call on this thread dispatched to (for tests and
  * traces): e.g. "w8a8_tcgen05", "int8_generic". */

@@ -10,8 +10,10 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 #include <string>
+#include <vector>
 
 #include "../../include/kaio_b200.h"
 #include "kernels.h"
@@ -62,12 +64,46 @@ static EncodeTiledFn get_encode_fn()
     return fn;
 }
 
+// Encoded tensor maps are a pure function of (type, base, extents, stride, box, swizzle), so the
+// calling thread keeps the maps of its recent calls: a decode loop that launches the same few
+// GEMMs over and over pays for cuTensorMapEncodeTiled once per operand, not once per launch.
+struct TensorMapKey {
+    const void* base;
+    uint64_t inner, outer, stride;
+    uint32_t dtype, box_inner, box_outer, swizzle;
+};
+struct TensorMapSlot {
+    TensorMapKey key;
+    CUtensorMap map;
+    bool used;
+};
+constexpr int TMAP_CACHE_SLOTS = 128;  // direct-mapped
+static thread_local TensorMapSlot g_tmap_cache[TMAP_CACHE_SLOTS];
+
 cudaError_t encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t elem_bytes,
                                  const void* base, uint64_t inner, uint64_t outer,
                                  uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer,
                                  CUtensorMapSwizzle swizzle)
 {
     (void)elem_bytes;
+    TensorMapKey key;
+    memset(&key, 0, sizeof(key));
+    key.base = base;
+    key.inner = inner;
+    key.outer = outer;
+    key.stride = row_stride_bytes;
+    key.dtype = (uint32_t)dtype;
+    key.box_inner = box_inner;
+    key.box_outer = box_outer;
+    key.swizzle = (uint32_t)swizzle;
+    uint64_t h = (uint64_t)(uintptr_t)base * 0x9E3779B97F4A7C15ull;
+    h ^= (inner * 0xC2B2AE3D27D4EB4Full) ^ (outer * 0x165667B19E3779F9ull) ^
+         ((uint64_t)box_inner << 40) ^ ((uint64_t)box_outer << 24) ^ ((uint64_t)swizzle << 8) ^ dtype;
+    TensorMapSlot& slot = g_tmap_cache[(h >> 32) % TMAP_CACHE_SLOTS];
+    if (slot.used && memcmp(&slot.key, &key, sizeof(key)) == 0) {
+        *map = slot.map;
+        return cudaSuccess;
+    }
     EncodeTiledFn fn = get_encode_fn();
     if (!fn)
         return cudaErrorNotSupported;
@@ -78,7 +114,12 @@ cudaError_t encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, ui
     CUresult r = fn(map, dtype, 2, const_cast<void*>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+    if (r != CUDA_SUCCESS)
+        return cudaErrorInvalidValue;
+    slot.key = key;
+    slot.map = *map;
+    slot.used = true;
+    return cudaSuccess;
 }
 
 // ---------------------------------------------------------------- per-device context
@@ -86,7 +127,25 @@ constexpr int MAX_DEVICES = 64;
 static DeviceCtx g_ctx[MAX_DEVICES];
 static std::mutex g_ctx_mutex;
 
-static int32_t get_ctx(DeviceCtx** out)
+// Scratch the kernels need beyond the caller's buffers, one set per (device, stream): calls on
+// different streams may overlap on the GPU, so they must not share split-K partial tiles,
+// arrival counters or the dequantised-weight buffer.  Calls on one stream run in order and
+// share a set.
+struct StreamScratch {
+    cudaStream_t stream = nullptr;
+    void* workspace = nullptr;          // split-K partial sums
+    size_t workspace_bytes = 0;
+    uint32_t* tile_counters = nullptr;  // split-K arrival counters (self-resetting)
+    size_t num_tile_counters = 0;
+    void* dq_workspace = nullptr;       // dequantised f16 weights / quantised activations
+    size_t dq_workspace_bytes = 0;
+};
+static std::vector<StreamScratch*> g_scratch[MAX_DEVICES];
+
+// The device's context.  `device_ptr`, when given, must be memory of the current device: a
+// caller that holds buffers of several devices gets an error instead of a launch on the wrong
+// one (the reference checks the buffer's device ordinal the same way).
+static int32_t get_ctx(DeviceCtx** out, const void* device_ptr = nullptr)
 {
     int dev = -1;
     cudaError_t err = cudaGetDevice(&dev);
@@ -94,6 +153,18 @@ static int32_t get_ctx(DeviceCtx** out)
         return fail_cuda(err, "cudaGetDevice");
     if (dev < 0 || dev >= MAX_DEVICES)
         return fail(KAIO_B200_ERR_CUDA, "device ordinal %d out of range", dev);
+    if (device_ptr != nullptr) {
+        cudaPointerAttributes attr;
+        err = cudaPointerGetAttributes(&attr, device_ptr);
+        if (err != cudaSuccess)
+            return fail_cuda(err, "cudaPointerGetAttributes");
+        if ((attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged) &&
+            attr.device != dev)
+            return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                        "buffer lives on device %d but the calling thread's current device is %d; "
+                        "make the buffer's device current before the call",
+                        attr.device, dev);
+    }
     std::lock_guard<std::mutex> lock(g_ctx_mutex);
     DeviceCtx& c = g_ctx[dev];
     if (c.device < 0) {
@@ -120,52 +191,92 @@ static int32_t get_ctx(DeviceCtx** out)
     return KAIO_B200_OK;
 }
 
-// Grows the split-K workspace / counters of a device.  Growth frees the old block with
-// cudaFree (which synchronises the device), so it is safe against work still in flight.
-static int32_t ensure_workspace(DeviceCtx* c, size_t bytes, size_t counters)
+// The scratch set of (c->device, stream), created empty on first use.  Caller holds no lock.
+static StreamScratch* scratch_for(DeviceCtx* c, cudaStream_t stream)
 {
     std::lock_guard<std::mutex> lock(g_ctx_mutex);
-    if (bytes > c->workspace_bytes) {
-        if (c->workspace)
-            cudaFree(c->workspace);
-        c->workspace = nullptr;
-        c->workspace_bytes = 0;
-        cudaError_t err = cudaMalloc(&c->workspace, bytes);
+    for (StreamScratch* sc : g_scratch[c->device])
+        if (sc->stream == stream)
+            return sc;
+    StreamScratch* sc = new StreamScratch();
+    sc->stream = stream;
+    g_scratch[c->device].push_back(sc);
+    return sc;
+}
+
+// Growing a scratch block frees the old one with cudaFree, which waits for the work in flight
+// on the device, and allocates: neither is allowed while the stream is being captured into a
+// CUDA graph, and a graph captured earlier keeps the old address.  So growth during a capture
+// is refused; callers warm every op at its largest shape before they capture.
+static int32_t refuse_growth_in_capture(cudaStream_t stream, const char* what)
+{
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &st) == cudaSuccess && st != cudaStreamCaptureStatusNone)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s would have to be allocated while the stream is being captured; run the op "
+                    "once at its largest shape before capturing",
+                    what);
+    return KAIO_B200_OK;
+}
+
+static int32_t ensure_workspace(DeviceCtx* c, cudaStream_t stream, size_t bytes, size_t counters,
+                                StreamScratch** out)
+{
+    StreamScratch* sc = scratch_for(c, stream);
+    *out = sc;
+    if (bytes <= sc->workspace_bytes && counters <= sc->num_tile_counters)
+        return KAIO_B200_OK;
+    int32_t rc = refuse_growth_in_capture(stream, "split-K scratch");
+    if (rc)
+        return rc;
+    std::lock_guard<std::mutex> lock(g_ctx_mutex);
+    if (bytes > sc->workspace_bytes) {
+        if (sc->workspace)
+            cudaFree(sc->workspace);
+        sc->workspace = nullptr;
+        sc->workspace_bytes = 0;
+        cudaError_t err = cudaMalloc(&sc->workspace, bytes);
         if (err != cudaSuccess)
             return fail_cuda(err, "cudaMalloc(workspace)");
-        c->workspace_bytes = bytes;
+        sc->workspace_bytes = bytes;
     }
-    if (counters > c->num_tile_counters) {
-        if (c->tile_counters)
-            cudaFree(c->tile_counters);
-        c->tile_counters = nullptr;
-        c->num_tile_counters = 0;
-        cudaError_t err = cudaMalloc(&c->tile_counters, counters * sizeof(uint32_t));
+    if (counters > sc->num_tile_counters) {
+        if (sc->tile_counters)
+            cudaFree(sc->tile_counters);
+        sc->tile_counters = nullptr;
+        sc->num_tile_counters = 0;
+        cudaError_t err = cudaMalloc(&sc->tile_counters, counters * sizeof(uint32_t));
         if (err != cudaSuccess)
             return fail_cuda(err, "cudaMalloc(counters)");
-        err = cudaMemset(c->tile_counters, 0, counters * sizeof(uint32_t));
+        err = cudaMemset(sc->tile_counters, 0, counters * sizeof(uint32_t));
         if (err != cudaSuccess)
             return fail_cuda(err, "cudaMemset(counters)");
-        c->num_tile_counters = counters;
+        sc->num_tile_counters = counters;
     }
     return KAIO_B200_OK;
 }
 
-// The dequantised-weight workspace is written and read by every dequantising GEMM call on the
-// device, in stream order.  Growth frees the old block with cudaFree, which synchronises.
-static int32_t ensure_dq_workspace(DeviceCtx* c, size_t bytes)
+// The dequantised-weight workspace is written and read by the dequantising GEMM calls of one
+// stream, in stream order.
+static int32_t ensure_dq_workspace(DeviceCtx* c, cudaStream_t stream, size_t bytes,
+                                   StreamScratch** out)
 {
+    StreamScratch* sc = scratch_for(c, stream);
+    *out = sc;
+    if (bytes <= sc->dq_workspace_bytes)
+        return KAIO_B200_OK;
+    int32_t rc = refuse_growth_in_capture(stream, "the dequantised-weight workspace");
+    if (rc)
+        return rc;
     std::lock_guard<std::mutex> lock(g_ctx_mutex);
-    if (bytes > c->dq_workspace_bytes) {
-        if (c->dq_workspace)
-            cudaFree(c->dq_workspace);
-        c->dq_workspace = nullptr;
-        c->dq_workspace_bytes = 0;
-        cudaError_t err = cudaMalloc(&c->dq_workspace, bytes);
-        if (err != cudaSuccess)
-            return fail_cuda(err, "cudaMalloc(dequantised weights)");
-        c->dq_workspace_bytes = bytes;
-    }
+    if (sc->dq_workspace)
+        cudaFree(sc->dq_workspace);
+    sc->dq_workspace = nullptr;
+    sc->dq_workspace_bytes = 0;
+    cudaError_t err = cudaMalloc(&sc->dq_workspace, bytes);
+    if (err != cudaSuccess)
+        return fail_cuda(err, "cudaMalloc(dequantised weights)");
+    sc->dq_workspace_bytes = bytes;
     return KAIO_B200_OK;
 }
 
@@ -372,7 +483,7 @@ static int32_t run_int8(int epi, const int8_t* a, size_t a_len, const int8_t* b,
     REQUIRE_PTR(b, "matmul_int8", "B");
     REQUIRE_PTR(c, "matmul_int8", "C");
     DeviceCtx* ctx;
-    if ((rc = get_ctx(&ctx)))
+    if ((rc = get_ctx(&ctx, c)))
         return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool scales_aligned = epi != EPI_ROWCOL || ((uintptr_t)w_scale % 16 == 0);
@@ -416,9 +527,10 @@ static int32_t run_int4(const kaio_f16* a, size_t a_len, const uint32_t* b, size
     REQUIRE_PTR(scales, "matmul_int4", "scales");
     REQUIRE_PTR(c, "matmul_int4", "C");
     DeviceCtx* ctx;
-    if ((rc = get_ctx(&ctx)))
+    if ((rc = get_ctx(&ctx, c)))
         return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    StreamScratch* sc = nullptr;
     DqProblem pr;
     pr.w = b;
     pr.scales = reinterpret_cast<const __half*>(scales);
@@ -428,26 +540,26 @@ static int32_t run_int4(const kaio_f16* a, size_t a_len, const uint32_t* b, size
     const __half* x = reinterpret_cast<const __half*>(a);
     if (w4a16_decode_ok(x, &pr, 1, m, n, k)) {
         const size_t ws = w4a16_decode_workspace_bytes(*ctx, n, k);
-        if ((rc = ensure_workspace(ctx, ws, w4a16_decode_num_counters(n))))
+        if ((rc = ensure_workspace(ctx, s, ws, w4a16_decode_num_counters(n), &sc)))
             return rc;
-        return finish(launch_w4a16_decode(*ctx, x, pr, out_f16, m, n, k, ctx->workspace,
-                                          ctx->tile_counters, s),
+        return finish(launch_w4a16_decode(*ctx, x, pr, out_f16, m, n, k, sc->workspace,
+                                          sc->tile_counters, s),
                       "matmul_int4", "w4a16_decode_splitk");
     }
     if (m <= fused_max_m() && w4a16_fused_ok(x, &pr, 1, m, n, k)) {
         const size_t ws = w4a16_fused_workspace_bytes(*ctx, 1, m, n, k);
-        if (ws && (rc = ensure_workspace(ctx, ws, w4a16_fused_num_counters(*ctx, 1, m, n, k))))
+        if (ws && (rc = ensure_workspace(ctx, s, ws, w4a16_fused_num_counters(*ctx, 1, m, n, k), &sc)))
             return rc;
         return finish(launch_w4a16_fused(*ctx, x, &pr, 1, out_f16, m, n, k,
-                                         ws ? ctx->workspace : nullptr,
-                                         ws ? ctx->tile_counters : nullptr, s),
+                                         ws ? sc->workspace : nullptr,
+                                         ws ? sc->tile_counters : nullptr, s),
                       "matmul_int4", ws ? "w4a16_fused_dequant_splitk" : "w4a16_fused_dequant");
     }
     if (dq_gemm_fast_path_ok(WFMT_S4_PACKED, x, &pr, 1, out_f16, m, n, k)) {
-        if ((rc = ensure_dq_workspace(ctx, dq_gemm_workspace_bytes(1, n, k))))
+        if ((rc = ensure_dq_workspace(ctx, s, dq_gemm_workspace_bytes(1, n, k), &sc)))
             return rc;
         return finish(launch_dq_gemm(*ctx, WFMT_S4_PACKED, x, &pr, 1, out_f16, false, m, n, k,
-                                     ctx->dq_workspace, s),
+                                     sc->dq_workspace, s),
                       "matmul_int4", "w4a16_tcgen05");
     }
     return finish(launch_dq_generic(WFMT_S4_PACKED, x, &pr, 1, out_f16, false, m, n, k, s),
@@ -464,24 +576,25 @@ static int32_t run_qkv(int wfmt, const char* op, const __half* x, DqProblem prob
                             "%s: the three output buffers must be distinct allocations", op);
     DeviceCtx* ctx;
     int32_t rc;
-    if ((rc = get_ctx(&ctx)))
+    if ((rc = get_ctx(&ctx, probs[0].out)))
         return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    StreamScratch* sc = nullptr;
     if (wfmt == WFMT_S4_PACKED && !post_scale && m <= fused_max_m() &&
         w4a16_fused_ok(x, probs, 3, m, n, k)) {
         const size_t ws = w4a16_fused_workspace_bytes(*ctx, 3, m, n, k);
-        if (ws && (rc = ensure_workspace(ctx, ws, w4a16_fused_num_counters(*ctx, 3, m, n, k))))
+        if (ws && (rc = ensure_workspace(ctx, s, ws, w4a16_fused_num_counters(*ctx, 3, m, n, k), &sc)))
             return rc;
         return finish(launch_w4a16_fused(*ctx, x, probs, 3, true, m, n, k,
-                                         ws ? ctx->workspace : nullptr,
-                                         ws ? ctx->tile_counters : nullptr, s),
+                                         ws ? sc->workspace : nullptr,
+                                         ws ? sc->tile_counters : nullptr, s),
                       op, ws ? "qkv_w4a16_fused_dequant_splitk" : "qkv_w4a16_fused_dequant");
     }
     if (dq_gemm_fast_path_ok(wfmt, x, probs, 3, true, m, n, k)) {
-        if ((rc = ensure_dq_workspace(ctx, dq_gemm_workspace_bytes(3, n, k))))
+        if ((rc = ensure_dq_workspace(ctx, s, dq_gemm_workspace_bytes(3, n, k), &sc)))
             return rc;
         return finish(launch_dq_gemm(*ctx, wfmt, x, probs, 3, true, post_scale, m, n, k,
-                                     ctx->dq_workspace, s),
+                                     sc->dq_workspace, s),
                       op, wfmt == WFMT_S8_ROWMAJOR ? "qkv_w8a16_tcgen05" : "qkv_w4a16_tcgen05");
     }
     return finish(launch_dq_generic(wfmt, x, probs, 3, true, post_scale, m, n, k, s), op,
@@ -554,7 +667,7 @@ static int32_t run_matmul_tc(const kaio_f16* a, size_t a_len, const kaio_f16* b,
     REQUIRE_PTR(c, "matmul_tc", "C");
     DeviceCtx* ctx;
     int32_t rc;
-    if ((rc = get_ctx(&ctx)))
+    if ((rc = get_ctx(&ctx, c)))
         return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     DqProblem pr;
@@ -711,7 +824,7 @@ KAIO_API int32_t kaio_b200_attention_tc(const kaio_f16* q, size_t q_len, const k
     REQUIRE_PTR(v, "attention_tc", "V");
     REQUIRE_PTR(out, "attention_tc", "out");
     DeviceCtx* ctx;
-    if ((rc = get_ctx(&ctx)))
+    if ((rc = get_ctx(&ctx, out)))
         return rc;
     AttnParams p = {};
     p.q = reinterpret_cast<const __half*>(q);
@@ -773,7 +886,7 @@ KAIO_API int32_t kaio_b200_attention_mha_f16(const kaio_f16* q, size_t q_len, co
     REQUIRE_PTR(out, op, "out");
     DeviceCtx* ctx;
     int32_t rc;
-    if ((rc = get_ctx(&ctx)))
+    if ((rc = get_ctx(&ctx, out)))
         return rc;
     AttnParams p = {};
     p.q = reinterpret_cast<const __half*>(q);
@@ -975,6 +1088,7 @@ KAIO_API int32_t kaio_b200_matmul_int4_allgather(const kaio_f16* a, size_t a_len
     if ((rc = get_ctx(&ctx)))
         return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    StreamScratch* sc = nullptr;
     DqProblem pr;
     pr.w = b_packed_shard;
     pr.scales = reinterpret_cast<const __half*>(scales_shard);
@@ -983,29 +1097,29 @@ KAIO_API int32_t kaio_b200_matmul_int4_allgather(const kaio_f16* a, size_t a_len
     pr.out = copies.ptrs[rank];
     const __half* x = reinterpret_cast<const __half*>(a);
     if (w4a16_decode_ok(x, &pr, 1, m, n_loc, k)) {
-        if ((rc = ensure_workspace(ctx, w4a16_decode_workspace_bytes(*ctx, n_loc, k),
-                                   w4a16_decode_num_counters(n_loc))))
+        if ((rc = ensure_workspace(ctx, s, w4a16_decode_workspace_bytes(*ctx, n_loc, k),
+                                   w4a16_decode_num_counters(n_loc), &sc)))
             return rc;
-        return finish(launch_w4a16_decode(*ctx, x, pr, true, m, n_loc, k, ctx->workspace,
-                                          ctx->tile_counters, s, &copies),
+        return finish(launch_w4a16_decode(*ctx, x, pr, true, m, n_loc, k, sc->workspace,
+                                          sc->tile_counters, s, &copies),
                       op, "w4a16_decode_splitk_allgather");
     }
     if (m <= fused_max_m() && w4a16_fused_ok(x, &pr, 1, m, n_loc, k)) {
         const size_t ws = w4a16_fused_workspace_bytes(*ctx, 1, m, n_loc, k);
-        if (ws && (rc = ensure_workspace(ctx, ws, w4a16_fused_num_counters(*ctx, 1, m, n_loc, k))))
+        if (ws && (rc = ensure_workspace(ctx, s, ws, w4a16_fused_num_counters(*ctx, 1, m, n_loc, k), &sc)))
             return rc;
         return finish(launch_w4a16_fused(*ctx, x, &pr, 1, true, m, n_loc, k,
-                                         ws ? ctx->workspace : nullptr,
-                                         ws ? ctx->tile_counters : nullptr, s, &copies),
+                                         ws ? sc->workspace : nullptr,
+                                         ws ? sc->tile_counters : nullptr, s, &copies),
                       op, "w4a16_fused_dequant_allgather");
     }
     if (!dq_gemm_fast_path_ok(WFMT_S4_PACKED, x, &pr, 1, true, m, n_loc, k))
         return fail(KAIO_B200_ERR_INVALID_CONFIG,
                     "%s: A, B packed and the outputs must be 16-byte aligned", op);
-    if ((rc = ensure_dq_workspace(ctx, dq_gemm_workspace_bytes(1, n_loc, k))))
+    if ((rc = ensure_dq_workspace(ctx, s, dq_gemm_workspace_bytes(1, n_loc, k), &sc)))
         return rc;
     return finish(launch_dq_gemm(*ctx, WFMT_S4_PACKED, x, &pr, 1, true, false, m, n_loc, k,
-                                 ctx->dq_workspace, s, &copies),
+                                 sc->dq_workspace, s, &copies),
                   op, "w4a16_tcgen05_allgather");
 }
 
@@ -1052,6 +1166,7 @@ KAIO_API int32_t kaio_b200_matmul_int4_peer_partials(const kaio_f16* a, size_t a
     if ((rc = get_ctx(&ctx)))
         return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    StreamScratch* sc = nullptr;
     DqProblem pr;
     pr.w = b_packed;
     pr.scales = reinterpret_cast<const __half*>(scales);
@@ -1060,30 +1175,30 @@ KAIO_API int32_t kaio_b200_matmul_int4_peer_partials(const kaio_f16* a, size_t a
     pr.out = copies.ptrs[rank];
     const __half* x = reinterpret_cast<const __half*>(a);
     if (w4a16_decode_ok(x, &pr, 1, m, n, k)) {
-        if ((rc = ensure_workspace(ctx, w4a16_decode_workspace_bytes(*ctx, n, k),
-                                   w4a16_decode_num_counters(n))))
+        if ((rc = ensure_workspace(ctx, s, w4a16_decode_workspace_bytes(*ctx, n, k),
+                                   w4a16_decode_num_counters(n), &sc)))
             return rc;
-        return finish(launch_w4a16_decode(*ctx, x, pr, false, m, n, k, ctx->workspace,
-                                          ctx->tile_counters, s, &copies),
+        return finish(launch_w4a16_decode(*ctx, x, pr, false, m, n, k, sc->workspace,
+                                          sc->tile_counters, s, &copies),
                       op, "w4a16_decode_splitk_peer_partials");
     }
     if (m <= fused_max_m() && w4a16_fused_ok(x, &pr, 1, m, n, k)) {
         const size_t ws = w4a16_fused_workspace_bytes(*ctx, 1, m, n, k);
-        if (ws && (rc = ensure_workspace(ctx, ws, w4a16_fused_num_counters(*ctx, 1, m, n, k))))
+        if (ws && (rc = ensure_workspace(ctx, s, ws, w4a16_fused_num_counters(*ctx, 1, m, n, k), &sc)))
             return rc;
         return finish(launch_w4a16_fused(*ctx, x, &pr, 1, false, m, n, k,
-                                         ws ? ctx->workspace : nullptr,
-                                         ws ? ctx->tile_counters : nullptr, s, &copies),
+                                         ws ? sc->workspace : nullptr,
+                                         ws ? sc->tile_counters : nullptr, s, &copies),
                       op, "w4a16_fused_dequant_peer_partials");
     }
     if (!dq_gemm_fast_path_ok(WFMT_S4_PACKED, x, &pr, 1, false, m, n, k))
         return fail(KAIO_B200_ERR_INVALID_CONFIG,
                     "%s: A, B packed and the staging buffers must be 16-byte aligned and N a "
                     "multiple of 8", op);
-    if ((rc = ensure_dq_workspace(ctx, dq_gemm_workspace_bytes(1, n, k))))
+    if ((rc = ensure_dq_workspace(ctx, s, dq_gemm_workspace_bytes(1, n, k), &sc)))
         return rc;
     return finish(launch_dq_gemm(*ctx, WFMT_S4_PACKED, x, &pr, 1, false, false, m, n, k,
-                                 ctx->dq_workspace, s, &copies),
+                                 sc->dq_workspace, s, &copies),
                   op, "w4a16_tcgen05_peer_partials");
 }
 
@@ -1210,6 +1325,8 @@ KAIO_API int32_t kaio_b200_matmul_int4_noalloc(const kaio_f16* a, size_t a_len,
             err = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch);
             if (err != cudaSuccess || ptr == nullptr)
                 return fail_cuda(err, "cudaGetSymbolAddress(noalloc scratch)");
+            // a __device__ array without an initialiser starts as zeros, so the status words
+            // need no clearing here
             g_noalloc_sms[dev] = sms;
             g_noalloc_ptr[dev] = ptr;
         }
@@ -1224,9 +1341,10 @@ KAIO_API int32_t kaio_b200_matmul_int4_noalloc(const kaio_f16* a, size_t a_len,
                     "%s: this device needs %zu bytes of split-K scratch, the fixed array holds %zu",
                     op, w4a16_decode_workspace_bytes(ctx, n, k), NOALLOC_PARTIAL_BYTES);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    // The array keeps whatever the previous call left: counters and status must start at zero.
-    err = cudaMemsetAsync(base + NOALLOC_PARTIAL_BYTES, 0,
-                          NOALLOC_COUNTER_BYTES + NOALLOC_STATUS_BYTES, s);
+    // The array keeps whatever the previous call left: the arrival counters must start at zero.
+    // The status words are left alone, so that a wait that gave up in an earlier call stays
+    // readable until kaio_b200_device_status() has reported and cleared it.
+    err = cudaMemsetAsync(base + NOALLOC_PARTIAL_BYTES, 0, NOALLOC_COUNTER_BYTES, s);
     if (err != cudaSuccess)
         return fail_cuda(err, "cudaMemsetAsync(noalloc scratch)");
     return finish(launch_w4a16_decode(ctx, x, pr, false, m, n, k, base,
@@ -1244,30 +1362,91 @@ KAIO_API const char* kaio_b200_last_variant(void)
     return g_last_variant;
 }
 
+// Reads and clears one status block; returns its four words in `host`.
+static cudaError_t read_status_block(uint32_t* dev_block, uint32_t host[4])
+{
+    cudaError_t err = cudaMemcpy(host, dev_block, 4 * sizeof(uint32_t), cudaMemcpyDeviceToHost);
+    if (err == cudaSuccess && host[0] != 0)
+        err = cudaMemset(dev_block, 0, 4 * sizeof(uint32_t));
+    return err;
+}
+
 KAIO_API int32_t kaio_b200_device_status(void* stream, uint32_t code[4])
 {
-    DeviceCtx* ctx;
-    int32_t rc;
-    if ((rc = get_ctx(&ctx)))
-        return rc;
+    // Allocates nothing: it only reads blocks that earlier calls created (the cudaMalloc'd
+    // block of the regular entry points, the fixed array of the allocation-free one).
+    int dev = -1;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess)
+        return fail_cuda(err, "cudaGetDevice");
+    if (dev < 0 || dev >= MAX_DEVICES)
+        return fail(KAIO_B200_ERR_CUDA, "device ordinal %d out of range", dev);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    cudaError_t err = cudaStreamSynchronize(s);
+    err = cudaStreamSynchronize(s);
     if (err != cudaSuccess)
         return fail_cuda(err, "cudaStreamSynchronize");
+    uint32_t* regular = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_ctx_mutex);
+        if (g_ctx[dev].device >= 0)
+            regular = g_ctx[dev].status;
+    }
+    unsigned char* fixed = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        fixed = g_noalloc_ptr[dev];
+    }
     uint32_t host[4] = {0, 0, 0, 0};
-    err = cudaMemcpy(host, ctx->status, sizeof(host), cudaMemcpyDeviceToHost);
-    if (err != cudaSuccess)
-        return fail_cuda(err, "cudaMemcpy(status)");
+    const char* where = "";
+    if (regular != nullptr) {
+        err = read_status_block(regular, host);
+        if (err != cudaSuccess)
+            return fail_cuda(err, "cudaMemcpy(status)");
+    }
+    if (host[0] == 0 && fixed != nullptr) {
+        err = read_status_block(
+            reinterpret_cast<uint32_t*>(fixed + NOALLOC_PARTIAL_BYTES + NOALLOC_COUNTER_BYTES), host);
+        if (err != cudaSuccess)
+            return fail_cuda(err, "cudaMemcpy(status of the allocation-free entry)");
+        where = " (allocation-free entry point)";
+    }
     if (code)
         for (int i = 0; i < 4; ++i)
             code[i] = host[i];
     if (host[0] != 0) {
-        cudaMemset(ctx->status, 0, sizeof(host));
+        // A launch that gave up may have left split-K arrival counters half counted; the next
+        // split-K launch would then miscount.  Every stream of the device was idle or is
+        // suspect now, so all counters of the device go back to zero.
+        {
+            std::lock_guard<std::mutex> lock(g_ctx_mutex);
+            for (StreamScratch* sc : g_scratch[dev])
+                if (sc->tile_counters)
+                    cudaMemset(sc->tile_counters, 0, sc->num_tile_counters * sizeof(uint32_t));
+        }
+        if (fixed != nullptr)
+            cudaMemset(fixed + NOALLOC_PARTIAL_BYTES, 0, NOALLOC_COUNTER_BYTES);
         return fail(KAIO_B200_ERR_TIMEOUT,
-                    "device-side bounded wait gave up: code %u, block %u, site %u, kernel %u",
-                    host[0], host[1], host[2], host[3]);
+                    "device-side bounded wait gave up%s: code %u, block %u, site %u, kernel %u",
+                    where, host[0], host[1], host[2], host[3]);
     }
     return KAIO_B200_OK;
+}
+
+// Test hook: one CTA waits, with a budget of `budget_us` microseconds (at 2 GHz), on an
+// mbarrier that nothing ever arrives at, gives up, records the timeout in the device's status
+// block and returns normally -- the path every kernel of the library takes when a wait runs
+// out, exercised without a fault.
+KAIO_API int32_t kaio_b200_selftest_bounded_wait(uint32_t budget_us, void* stream)
+{
+    if (budget_us == 0 || budget_us > 100000)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "selftest_bounded_wait: budget must be 1..100000 microseconds (got %u)", budget_us);
+    DeviceCtx* ctx;
+    int32_t rc;
+    if ((rc = get_ctx(&ctx)))
+        return rc;
+    return finish(launch_selftest_bounded_wait(*ctx, budget_us, static_cast<cudaStream_t>(stream)),
+                  "selftest_bounded_wait", "selftest_bounded_wait");
 }
 
 KAIO_API void kaio_b200_shutdown(void)
@@ -1282,12 +1461,16 @@ KAIO_API void kaio_b200_shutdown(void)
         cudaSetDevice(d);
         if (c.status)
             cudaFree(c.status);
-        if (c.workspace)
-            cudaFree(c.workspace);
-        if (c.tile_counters)
-            cudaFree(c.tile_counters);
-        if (c.dq_workspace)
-            cudaFree(c.dq_workspace);
+        for (StreamScratch* sc : g_scratch[d]) {
+            if (sc->workspace)
+                cudaFree(sc->workspace);
+            if (sc->tile_counters)
+                cudaFree(sc->tile_counters);
+            if (sc->dq_workspace)
+                cudaFree(sc->dq_workspace);
+            delete sc;
+        }
+        g_scratch[d].clear();
         c = DeviceCtx();
     }
     if (cur >= 0)
@@ -1296,5 +1479,5 @@ KAIO_API void kaio_b200_shutdown(void)
 
 KAIO_API int32_t kaio_b200_version(void)
 {
-    return 1000;
+    return 1001;
 }

@@ -29,6 +29,7 @@ enum : uint32_t {
     KERNEL_W4A16_DECODE = 2,
     KERNEL_DQ_GEMM = 3,
     KERNEL_FLASH_ATTN = 4,
+    KERNEL_SELFTEST = 5,
 };
 
 __device__ __forceinline__ void report_status(uint32_t* status, uint32_t code, uint32_t site,
@@ -128,11 +129,18 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity
 constexpr uint32_t WAIT_HINT_NS = 20000;
 constexpr uint32_t WAIT_POLL_LIMIT = 1u << 20;
 
-// One lane's wait.  Returns true when the phase completed; false when this wait (or another
-// thread of the CTA, through *abort_flag) gave up.
-__device__ __forceinline__ bool mbar_wait_lane(uint32_t bar, uint32_t parity,
-                                               volatile uint32_t* abort_flag, uint32_t* status,
-                                               uint32_t site, uint32_t kernel_id)
+// ~1 s at 2 GHz: the bound of every wait in the shipped kernels.
+constexpr unsigned long long WAIT_CYCLE_LIMIT = 2000000000ull;
+
+// One lane's wait with an explicit cycle budget.  Returns true when the phase completed; false
+// when this wait (or another thread of the CTA, through *abort_flag) gave up.  Giving up raises
+// the abort flag, records {DEV_TIMEOUT, block, site, kernel} in the status block and returns:
+// no trap, the kernel runs to its normal end.
+__device__ __forceinline__ bool mbar_wait_lane_budget(uint32_t bar, uint32_t parity,
+                                                      volatile uint32_t* abort_flag,
+                                                      uint32_t* status, uint32_t site,
+                                                      uint32_t kernel_id,
+                                                      unsigned long long max_cycles)
 {
     if (mbar_try_wait(bar, parity))
         return true;
@@ -142,14 +150,23 @@ __device__ __forceinline__ bool mbar_wait_lane(uint32_t bar, uint32_t parity,
             return true;
         if (*abort_flag)
             return false;
-        // ~1 s at 2 GHz: polls that return early (hint not honoured) must not shorten or
-        // lengthen the bound by orders of magnitude
-        if (clock64() - t_start > 2000000000ull)
+        // polls that return early (hint not honoured) must not shorten or lengthen the bound
+        // by orders of magnitude
+        if (clock64() - t_start > max_cycles)
             break;
     }
     *abort_flag = 1;
     report_status(status, DEV_TIMEOUT, site, kernel_id);
     return false;
+}
+
+// One lane's wait with the library's standard bound.
+__device__ __forceinline__ bool mbar_wait_lane(uint32_t bar, uint32_t parity,
+                                               volatile uint32_t* abort_flag, uint32_t* status,
+                                               uint32_t site, uint32_t kernel_id)
+{
+    return mbar_wait_lane_budget(bar, parity, abort_flag, status, site, kernel_id,
+                                 WAIT_CYCLE_LIMIT);
 }
 
 // WARP-COLLECTIVE wait: all 32 lanes of a warp call it together.  Lanes can leave the polling
@@ -378,7 +395,7 @@ __device__ __forceinline__ bool mbar_wait_lane_cluster(uint32_t bar, uint32_t pa
             return true;
         if (*abort_flag)
             return false;
-        if (clock64() - t_start > 2000000000ull)
+        if (clock64() - t_start > WAIT_CYCLE_LIMIT)
             break;
     }
     *abort_flag = 1;

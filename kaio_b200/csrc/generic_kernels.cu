@@ -38,6 +38,9 @@ int8_generic_kernel(const int8_t* __restrict__ a, const int8_t* __restrict__ b, 
             reinterpret_cast<int32_t*>(out)[idx] = acc;
         } else if (EPI == EPI_SCALAR) {
             reinterpret_cast<float*>(out)[idx] = __fmul_rn(__int2float_rn(acc), scale);
+        } else if (EPI == EPI_ROWCOL_F16) {
+            reinterpret_cast<__half*>(out)[idx] = __float2half_rn(
+                __fmul_rn(__fmul_rn(__int2float_rn(acc), a_scale[row]), w_scale[col]));
         } else {
             reinterpret_cast<float*>(out)[idx] =
                 __fmul_rn(__fmul_rn(__int2float_rn(acc), a_scale[row]), w_scale[col]);
@@ -56,6 +59,9 @@ cudaError_t launch_int8_generic(int epi, const int8_t* a, const int8_t* b, void*
     else if (epi == EPI_ROWCOL)
         int8_generic_kernel<EPI_ROWCOL><<<grid, block, 0, stream>>>(a, b, out, scale, a_scale,
                                                                      w_scale, m, n, k);
+    else if (epi == EPI_ROWCOL_F16)
+        int8_generic_kernel<EPI_ROWCOL_F16><<<grid, block, 0, stream>>>(a, b, out, scale, a_scale,
+                                                                         w_scale, m, n, k);
     else
         int8_generic_kernel<EPI_S32><<<grid, block, 0, stream>>>(a, b, out, scale, a_scale, w_scale,
                                                                   m, n, k);

@@ -14,6 +14,7 @@ enum : int {
     EPI_SCALAR = 0,  // f32 out = (acc as f32) * scale
     EPI_ROWCOL = 1,  // f32 out = ((acc as f32) * a_scale[i]) * w_scale[j]
     EPI_S32 = 2,     // s32 out = acc
+    EPI_ROWCOL_F16 = 3,  // f16 out = f16_rn(((acc as f32) * a_scale[i]) * w_scale[j])
 };
 
 // Weight encodings of the dequantising GEMM (f16 activations).
@@ -29,12 +30,6 @@ struct DeviceCtx {
     int num_sms = 0;
     int cc_major = 0, cc_minor = 0;
     uint32_t* status = nullptr;       // uint32[4] status block, zero = no error
-    void* workspace = nullptr;        // split-K partial sums
-    size_t workspace_bytes = 0;
-    uint32_t* tile_counters = nullptr;  // split-K arrival counters (self-resetting)
-    size_t num_tile_counters = 0;
-    void* dq_workspace = nullptr;     // dequantised f16 weights of the call in flight
-    size_t dq_workspace_bytes = 0;
 };
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time libcuda).
@@ -54,6 +49,12 @@ cudaError_t launch_w8a8_gemm_2cta(const DeviceCtx& ctx, int epi, const int8_t* a
                                   void* out, float scale, const float* a_scale,
                                   const float* w_scale, uint32_t m, uint32_t n, uint32_t k,
                                   cudaStream_t stream);
+// Fused W8A8 QKV projection on CTA pairs (m > 128): xq s8 [m,k] with per-row scales, three s8
+// [k,n] weights with per-column scales, three f16 [m,n] outputs, one launch.
+cudaError_t launch_w8a8_qkv_2cta(const DeviceCtx& ctx, const int8_t* xq, const float* x_scale,
+                                 const int8_t* const w[3], const float* const col_scale[3],
+                                 void* const out[3], uint32_t m, uint32_t n, uint32_t k,
+                                 cudaStream_t stream);
 cudaError_t launch_int8_generic(int epi, const int8_t* a, const int8_t* b, void* out, float scale,
                                 const float* a_scale, const float* w_scale, uint32_t m, uint32_t n,
                                 uint32_t k, cudaStream_t stream);
@@ -121,6 +122,9 @@ cudaError_t launch_dq_gemm(const DeviceCtx& ctx, int wfmt, const __half* x, cons
 // ---------------------------------------------------------------- quantisers
 cudaError_t launch_quantize_rows_int8(const float* x, int8_t* q, float* scale, uint32_t m,
                                       uint32_t k, cudaStream_t stream);
+// The same quantiser on f16 activations (widened to f32 exactly, then the same arithmetic).
+cudaError_t launch_quantize_rows_int8_f16(const __half* x, int8_t* q, float* scale, uint32_t m,
+                                          uint32_t k, cudaStream_t stream);
 cudaError_t launch_quantize_pack_s4(const float* w, uint32_t* packed, __half* scales, uint32_t k,
                                     uint32_t n, cudaStream_t stream);
 
@@ -135,6 +139,10 @@ cudaError_t launch_silu_gate_f32(const float* x, const float* gate, float* out, 
 cudaError_t launch_silu_gate_f16(const __half* x, const __half* gate, __half* out, uint32_t rows,
                                  uint32_t cols, uint32_t x_ld, uint32_t gate_ld, uint32_t out_ld,
                                  cudaStream_t stream);
+
+// ---------------------------------------------------------------- self-test of the bounded wait
+cudaError_t launch_selftest_bounded_wait(const DeviceCtx& ctx, uint32_t budget_us,
+                                         cudaStream_t stream);
 
 // ---------------------------------------------------------------- attention
 struct AttnParams {

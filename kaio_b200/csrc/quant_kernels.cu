@@ -40,6 +40,75 @@ quantize_rows_int8_kernel(const float* __restrict__ x, int8_t* __restrict__ q,
     }
 }
 
+// The same quantiser on f16 activations (the input of the W8A8 fused QKV projection): every f16
+// widens to f32 exactly, after which the arithmetic is the one above.  One block per row; a row
+// of up to 4096 values stays in registers between the max pass and the quantising pass, longer
+// rows are read a second time (from L1/L2).  16-byte loads, 8-byte stores.
+__global__ void __launch_bounds__(256)
+quantize_rows_int8_f16_kernel(const __half* __restrict__ x, int8_t* __restrict__ q,
+                              float* __restrict__ scale, uint32_t m, uint32_t k)
+{
+    __shared__ float red[8];
+    const uint32_t row = blockIdx.x;
+    if (row >= m)
+        return;
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * k);
+    const uint32_t nvec = k >> 3;
+    constexpr uint32_t CACHED = 2;
+    uint4 cache[CACHED];
+    __half2 mx2 = __float2half2_rn(0.0f);
+#pragma unroll
+    for (uint32_t j = 0; j < CACHED; ++j) {
+        const uint32_t i = threadIdx.x + j * 256;
+        cache[j] = make_uint4(0, 0, 0, 0);
+        if (i < nvec)
+            cache[j] = __ldg(xr + i);
+        const __half2* h = reinterpret_cast<const __half2*>(&cache[j]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            mx2 = __hmax2(mx2, __habs2(h[e]));
+    }
+    for (uint32_t i = threadIdx.x + CACHED * 256; i < nvec; i += 256) {
+        const uint4 v = __ldg(xr + i);
+        const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            mx2 = __hmax2(mx2, __habs2(h[e]));
+    }
+    float mx = fmaxf(__low2float(mx2), __high2float(mx2));  // max of |f16| values: exact
+    for (int o = 16; o > 0; o >>= 1)
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if ((threadIdx.x & 31) == 0)
+        red[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    mx = red[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w)
+        mx = fmaxf(mx, red[w]);
+    const float s = (mx == 0.0f) ? 1.0f : __fdiv_rn(mx, 127.0f);
+    if (threadIdx.x == 0)
+        scale[row] = s;
+    uint2* qr = reinterpret_cast<uint2*>(q + (size_t)row * k);
+    auto quantise8 = [&](const uint4& v) {
+        const __half* h = reinterpret_cast<const __half*>(&v);
+        uint32_t out[2] = {0, 0};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float f = fminf(fmaxf(roundf(__fdiv_rn(__half2float(h[e]), s)), -127.0f), 127.0f);
+            out[e >> 2] |= ((uint32_t)(int)f & 0xFFu) << (8 * (e & 3));
+        }
+        return make_uint2(out[0], out[1]);
+    };
+#pragma unroll
+    for (uint32_t j = 0; j < CACHED; ++j) {
+        const uint32_t i = threadIdx.x + j * 256;
+        if (i < nvec)
+            qr[i] = quantise8(cache[j]);
+    }
+    for (uint32_t i = threadIdx.x + CACHED * 256; i < nvec; i += 256)
+        qr[i] = quantise8(__ldg(xr + i));
+}
+
 // One warp per (column, group of 128 k): scale = max|w| / 7 (1 if zero) stored as f16;
 // q = clamp(round(w / scale_f32), -8, 7) packed 8 per u32 at word (k/8) + col*(K/8).
 __global__ void __launch_bounds__(256)
@@ -82,6 +151,14 @@ cudaError_t launch_quantize_rows_int8(const float* x, int8_t* q, float* scale, u
                                       uint32_t k, cudaStream_t stream)
 {
     quantize_rows_int8_kernel<<<m, 256, 0, stream>>>(x, q, scale, m, k);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_quantize_rows_int8_f16(const __half* x, int8_t* q, float* scale, uint32_t m,
+                                          uint32_t k, cudaStream_t stream)
+{
+    // k % 8 == 0 and 16-byte aligned x, 8-byte aligned q: checked by the caller
+    quantize_rows_int8_f16_kernel<<<m, 256, 0, stream>>>(x, q, scale, m, k);
     return cudaGetLastError();
 }
 

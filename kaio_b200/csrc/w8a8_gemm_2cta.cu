@@ -28,6 +28,12 @@
 // 96 bytes of operands per clock per SM instead of 64, so it runs below the full rate, but the
 // round is still shorter than a full-tile round; no reduction across CTAs is needed and the
 // result stays bit-exact.
+//
+// Grouped form (NP = 3): the fused W8A8 QKV projection.  The three weight matrices share A (the
+// activations quantised to s8 per row) and are walked as one [K, 3N] problem -- a column tile's
+// index selects the projection's B and C tensor maps and its per-column scales -- so the rows of
+// A a rasterisation group holds in L2 serve all three projections.  Its epilogue narrows to f16:
+// out = f16_rn(((acc as f32) * a_scale[i]) * w_scale_P[j]), 64 columns per staged block.
 #include <cstdlib>
 
 #include "common.cuh"
@@ -65,20 +71,28 @@ enum : uint32_t {
 
 struct Params {
     const float* a_scale;
-    const float* w_scale;
+    const float* w_scale[3];  // per problem
     float scale;
-    uint32_t m, n, k;
+    uint32_t m, n, k;     // n = columns of ONE problem
     uint32_t full_tiles;  // tiles [0, full_tiles) run whole; each later tile runs as two halves
     uint32_t* status;
 };
 
-template <int EPI>
+// Tensor maps of a launch: A, and per problem B (whole and half-width boxes) and C.
+template <int NP>
+struct alignas(64) TensorMaps {
+    CUtensorMap a;
+    CUtensorMap b[NP];
+    CUtensorMap b_half[NP];
+    CUtensorMap c[NP];
+};
+
+template <int EPI, int NP>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
-w8a8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                      const __grid_constant__ CUtensorMap tmap_b,
-                      const __grid_constant__ CUtensorMap tmap_b_half,
-                      const __grid_constant__ CUtensorMap tmap_c, const Params p)
+w8a8_gemm_2cta_kernel(const __grid_constant__ TensorMaps<NP> maps, const Params p)
 {
+    constexpr bool OUT_F16 = (EPI == EPI_ROWCOL_F16);
+    constexpr uint32_t CHUNK = OUT_F16 ? 64u : 32u;  // columns per staged 128-byte-row block
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -100,7 +114,8 @@ w8a8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t num_pairs = gridDim.x >> 1;
 
     const uint32_t tiles_m = (p.m + BM - 1) / BM;
-    const uint32_t tiles_n = (p.n + BN - 1) / BN;
+    const uint32_t tiles_n1 = (p.n + BN - 1) / BN;  // column tiles of one problem
+    const uint32_t tiles_n = tiles_n1 * NP;         // of all problems side by side
     const uint32_t num_tiles = tiles_m * tiles_n;
     const uint32_t num_kb = (p.k + BK - 1) / BK;
     // work item -> (tile, which half); half = 2 means the whole tile
@@ -138,9 +153,9 @@ w8a8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         *abort_flag = 0;
         fence_barrier_init();
-        tma_prefetch_desc(&tmap_a);
-        tma_prefetch_desc(&tmap_b);
-        tma_prefetch_desc(&tmap_c);
+        tma_prefetch_desc(&maps.a);
+        tma_prefetch_desc(&maps.b[0]);
+        tma_prefetch_desc(&maps.c[0]);
     }
     if (warp == 1) {
         tmem_alloc_2cta<TMEM_COLS>(smem_u32(const_cast<uint32_t*>(tmem_slot)));
@@ -160,8 +175,11 @@ w8a8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
             uint32_t tile, half, tm, tn;
             item_tile(item, tile, half);
             tile_origin(tile, tm, tn);
+            const uint32_t prob = NP == 1 ? 0u : tn / tiles_n1;
+            tn -= prob * tiles_n1;
             const int32_t m0 = tm * BM + rank * BM_CTA;
             const int32_t n0 = half == 2 ? tn * BN + rank * 128 : tn * BN + half * BN_HALF + rank * 64;
+            const CUtensorMap* map_b = half == 2 ? &maps.b[prob] : &maps.b_half[prob];
             for (uint32_t kb = 0; kb < num_kb; ++kb) {
                 if (!mbar_wait_bounded_cluster(empty_bar(s), ph ^ 1u, abort_flag, p.status,
                                                SITE_EMPTY, KERNEL_W8A8)) {
@@ -175,9 +193,8 @@ w8a8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     if (rank == 0)  // both CTAs' boxes
                         mbar_expect_tx(full_bar(s),
                                        2 * (A_BYTES + (half == 2 ? B_BYTES : B_HALF_BYTES)));
-                    tma_load_2d_pair(stage, &tmap_a, leader_full, k0, m0);
-                    tma_load_2d_pair(stage + A_BYTES, half == 2 ? &tmap_b : &tmap_b_half, leader_full,
-                                     n0, k0);
+                    tma_load_2d_pair(stage, &maps.a, leader_full, k0, m0);
+                    tma_load_2d_pair(stage + A_BYTES, map_b, leader_full, n0, k0);
                 }
                 __syncwarp();
                 if (++s == STAGES) {
@@ -252,24 +269,54 @@ w8a8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
             uint32_t tile, half, tm, tn;
             item_tile(item, tile, half);
             tile_origin(tile, tm, tn);
+            const uint32_t prob = NP == 1 ? 0u : tn / tiles_n1;
+            tn -= prob * tiles_n1;
+            const float* const w_scale = p.w_scale[prob];
+            const CUtensorMap* const map_c = &maps.c[prob];
             const uint32_t m0 = tm * BM + rank * BM_CTA;
             const uint32_t n0 = tn * BN + (half == 2 ? 0u : half * BN_HALF);
-            const uint32_t n_chunks = (half == 2 ? BN : BN_HALF) / 32;
+            const uint32_t n_chunks = (half == 2 ? BN : BN_HALF) / CHUNK;
             if (!mbar_wait_bounded_cluster(tmem_full_bar(buf), acc_ph, abort_flag, p.status,
                                            SITE_TMEM_FULL, KERNEL_W8A8))
                 break;
             tc_fence_after_sync();
             const uint32_t row = m0 + quarter * 32 + lane;
             float row_scale = 1.0f;
-            if (EPI == EPI_ROWCOL && row < p.m)
+            if ((EPI == EPI_ROWCOL || OUT_F16) && row < p.m)
                 row_scale = __ldg(p.a_scale + row);
             const uint32_t taddr = tmem_base + buf * BN + ((quarter * 32u) << 16);
 #pragma unroll 1
             for (uint32_t c = 0; c < n_chunks; ++c) {
-                const uint32_t col0 = n0 + c * 32;
+                const uint32_t col0 = n0 + c * CHUNK;
                 if (col0 >= p.n)
                     break;  // warp-uniform
                 uint32_t r[32];
+                if (OUT_F16) {
+                    // 64 columns: two tensor-memory loads, scaled and narrowed to 32 f16 pairs
+                    uint32_t lo[32], hi[32];
+                    tmem_ld_32x32b_x32(taddr + c * 64, lo);
+                    tmem_ld_32x32b_x32(taddr + c * 64 + 32, hi);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int part = 0; part < 2; ++part) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            const uint32_t* src = part == 0 ? lo : hi;
+                            const uint32_t cc = col0 + part * 32 + j;
+                            float4 ws = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (cc < p.n)  // N % 16 == 0: whole vector in or out
+                                ws = __ldg(reinterpret_cast<const float4*>(w_scale + cc));
+                            const float f0 = __fmul_rn(__fmul_rn(__int2float_rn((int32_t)src[j + 0]), row_scale), ws.x);
+                            const float f1 = __fmul_rn(__fmul_rn(__int2float_rn((int32_t)src[j + 1]), row_scale), ws.y);
+                            const float f2 = __fmul_rn(__fmul_rn(__int2float_rn((int32_t)src[j + 2]), row_scale), ws.z);
+                            const float f3 = __fmul_rn(__fmul_rn(__int2float_rn((int32_t)src[j + 3]), row_scale), ws.w);
+                            const __half2 h01 = __floats2half2_rn(f0, f1);
+                            const __half2 h23 = __floats2half2_rn(f2, f3);
+                            r[part * 16 + j / 2] = *reinterpret_cast<const uint32_t*>(&h01);
+                            r[part * 16 + j / 2 + 1] = *reinterpret_cast<const uint32_t*>(&h23);
+                        }
+                    }
+                } else {
                 tmem_ld_32x32b_x32(taddr + c * 32, r);
                 tmem_ld_wait();
                 if (EPI != EPI_S32) {
@@ -287,7 +334,7 @@ w8a8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         } else {
                             float4 ws = make_float4(0.f, 0.f, 0.f, 0.f);
                             if (col0 + j < p.n)  // N % 16 == 0: whole vector in or out
-                                ws = __ldg(reinterpret_cast<const float4*>(p.w_scale + col0 + j));
+                                ws = __ldg(reinterpret_cast<const float4*>(w_scale + col0 + j));
                             f0 = __fmul_rn(__fmul_rn(f0, row_scale), ws.x);
                             f1 = __fmul_rn(__fmul_rn(f1, row_scale), ws.y);
                             f2 = __fmul_rn(__fmul_rn(f2, row_scale), ws.z);
@@ -298,6 +345,7 @@ w8a8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         r[j + 2] = __float_as_uint(f2);
                         r[j + 3] = __float_as_uint(f3);
                     }
+                }
                 }
                 if (lane == 0)
                     tma_store_wait_read<1>();  // the buffer used two blocks ago has been read out
@@ -310,7 +358,7 @@ w8a8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
-                    tma_store_2d(&tmap_c, stg_base + stg_off, (int32_t)col0,
+                    tma_store_2d(map_c, stg_base + stg_off, (int32_t)col0,
                                  (int32_t)(m0 + quarter * 32));
                     tma_store_commit();
                 }
@@ -353,39 +401,49 @@ bool w8a8_2cta_ok(uint32_t m, uint32_t n, uint32_t k)
     return m > 128;
 }
 
-cudaError_t launch_w8a8_gemm_2cta(const DeviceCtx& ctx, int epi, const int8_t* a, const int8_t* b,
-                                  void* out, float scale, const float* a_scale,
-                                  const float* w_scale, uint32_t m, uint32_t n, uint32_t k,
-                                  cudaStream_t stream)
+// Encodes the maps and launches; NP problems share A and the shape.
+template <int EPI, int NP>
+static cudaError_t launch_pair_kernel(const DeviceCtx& ctx, const int8_t* a,
+                                      const int8_t* const* b, void* const* out, float scale,
+                                      const float* a_scale, const float* const* w_scale,
+                                      uint32_t m, uint32_t n, uint32_t k, cudaStream_t stream)
 {
     using namespace w8a8x2;
-    CUtensorMap tmap_a, tmap_b, tmap_c;
-    cudaError_t err = encode_tensor_map_2d(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, k, m, k,
+    constexpr bool OUT_F16 = (EPI == EPI_ROWCOL_F16);
+    TensorMaps<NP> maps;
+    cudaError_t err = encode_tensor_map_2d(&maps.a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, k, m, k,
                                            BK, BM_CTA, CU_TENSOR_MAP_SWIZZLE_128B);
     if (err != cudaSuccess)
         return err;
-    err = encode_tensor_map_2d(&tmap_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, n, k, n, 128, BK,
-                               CU_TENSOR_MAP_SWIZZLE_128B);
-    if (err != cudaSuccess)
-        return err;
-    CUtensorMap tmap_b_half;
-    err = encode_tensor_map_2d(&tmap_b_half, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, n, k, n, 64, BK,
-                               CU_TENSOR_MAP_SWIZZLE_64B);
-    if (err != cudaSuccess)
-        return err;
-    err = encode_tensor_map_2d(&tmap_c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, out, n, m,
-                               (uint64_t)n * 4, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (err != cudaSuccess)
-        return err;
+    for (int i = 0; i < NP; ++i) {
+        err = encode_tensor_map_2d(&maps.b[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b[i], n, k, n, 128,
+                                   BK, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (err != cudaSuccess)
+            return err;
+        err = encode_tensor_map_2d(&maps.b_half[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b[i], n, k, n,
+                                   64, BK, CU_TENSOR_MAP_SWIZZLE_64B);
+        if (err != cudaSuccess)
+            return err;
+        // one staged block = 32 rows x 128 bytes: 32 f32 / s32 columns or 64 f16 columns
+        err = OUT_F16 ? encode_tensor_map_2d(&maps.c[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, out[i],
+                                             n, m, (uint64_t)n * 2, 64, 32,
+                                             CU_TENSOR_MAP_SWIZZLE_128B)
+                      : encode_tensor_map_2d(&maps.c[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, out[i],
+                                             n, m, (uint64_t)n * 4, 32, 32,
+                                             CU_TENSOR_MAP_SWIZZLE_128B);
+        if (err != cudaSuccess)
+            return err;
+    }
     Params p;
     p.a_scale = a_scale;
-    p.w_scale = w_scale;
+    for (int i = 0; i < 3; ++i)
+        p.w_scale[i] = (w_scale != nullptr && i < NP) ? w_scale[i] : nullptr;
     p.scale = scale;
     p.m = m;
     p.n = n;
     p.k = k;
     p.status = ctx.status;
-    const uint32_t tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
+    const uint32_t tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN) * NP;
     const uint32_t max_pairs = (uint32_t)ctx.num_sms / 2;
     const uint32_t pairs = tiles < max_pairs ? tiles : max_pairs;
     // the left-over tiles of the last round run as halves when those fit in one round
@@ -394,32 +452,43 @@ cudaError_t launch_w8a8_gemm_2cta(const DeviceCtx& ctx, int epi, const int8_t* a
     if (tiles > max_pairs && rem != 0 && 2 * rem <= max_pairs && !half_tiles_disabled())
         p.full_tiles = tiles - rem;
 
-    static bool attr_set[3][64] = {};
-#define KAIO_LAUNCH_W8A8X2(E)                                                                     \
-    do {                                                                                          \
-        if (!attr_set[E][ctx.device]) {                                                           \
-            err = cudaFuncSetAttribute(w8a8_gemm_2cta_kernel<E>,                                  \
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);  \
-            if (err != cudaSuccess)                                                               \
-                return err;                                                                       \
-            attr_set[E][ctx.device] = true;                                                       \
-        }                                                                                         \
-        w8a8_gemm_2cta_kernel<E><<<pairs * 2, NUM_THREADS, SMEM_BYTES, stream>>>(                 \
-            tmap_a, tmap_b, tmap_b_half, tmap_c, p);                                              \
-    } while (0)
+    static bool attr_set[64] = {};
+    if (!attr_set[ctx.device]) {
+        err = cudaFuncSetAttribute(w8a8_gemm_2cta_kernel<EPI, NP>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (err != cudaSuccess)
+            return err;
+        attr_set[ctx.device] = true;
+    }
+    w8a8_gemm_2cta_kernel<EPI, NP><<<pairs * 2, NUM_THREADS, SMEM_BYTES, stream>>>(maps, p);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_w8a8_gemm_2cta(const DeviceCtx& ctx, int epi, const int8_t* a, const int8_t* b,
+                                  void* out, float scale, const float* a_scale,
+                                  const float* w_scale, uint32_t m, uint32_t n, uint32_t k,
+                                  cudaStream_t stream)
+{
+    const int8_t* bs[1] = {b};
+    void* outs[1] = {out};
+    const float* ws[1] = {w_scale};
     switch (epi) {
     case EPI_SCALAR:
-        KAIO_LAUNCH_W8A8X2(EPI_SCALAR);
-        break;
+        return launch_pair_kernel<EPI_SCALAR, 1>(ctx, a, bs, outs, scale, a_scale, ws, m, n, k, stream);
     case EPI_ROWCOL:
-        KAIO_LAUNCH_W8A8X2(EPI_ROWCOL);
-        break;
+        return launch_pair_kernel<EPI_ROWCOL, 1>(ctx, a, bs, outs, scale, a_scale, ws, m, n, k, stream);
     default:
-        KAIO_LAUNCH_W8A8X2(EPI_S32);
-        break;
+        return launch_pair_kernel<EPI_S32, 1>(ctx, a, bs, outs, scale, a_scale, ws, m, n, k, stream);
     }
-#undef KAIO_LAUNCH_W8A8X2
-    return cudaGetLastError();
+}
+
+cudaError_t launch_w8a8_qkv_2cta(const DeviceCtx& ctx, const int8_t* xq, const float* x_scale,
+                                 const int8_t* const w[3], const float* const col_scale[3],
+                                 void* const out[3], uint32_t m, uint32_t n, uint32_t k,
+                                 cudaStream_t stream)
+{
+    return launch_pair_kernel<EPI_ROWCOL_F16, 3>(ctx, xq, w, out, 1.0f, x_scale, col_scale, m, n, k,
+                                                 stream);
 }
 
 }  // namespace kaio

@@ -79,6 +79,12 @@ def device_status(device: KaioDevice):
     return list(code)
 
 
+def selftest_bounded_wait(device: KaioDevice, budget_us: int = 5):
+    """Launch the library's one-CTA self-test whose device-side wait runs out after
+    ``budget_us`` microseconds; the next :func:`device_status` raises ``DeviceTimeout``."""
+    _call(device, "kaio_b200_selftest_bounded_wait", C.c_uint32(budget_us))
+
+
 # ------------------------------------------------------------------ W8A8
 
 def matmul_int8(device, a, b, c, scale, m, n, k):

@@ -24,7 +24,7 @@ def test_exports_every_declared_symbol(lib):
 
 
 def test_version(lib):
-    assert lib.kaio_b200_version() == 1000
+    assert lib.kaio_b200_version() == 1001
 
 
 def err(lib):

@@ -58,6 +58,52 @@ def test_mha_f16(oracle, b, h, s, d, causal):
     assert_attention_close(host(out, (b * s, stride)).astype(np.float32), want.astype(np.float32))
 
 
+# Scores with a standard deviation near 20 in log2 units: with q, k ~ N(0, sigma^2) the scaled
+# score q.k / sqrt(d) has standard deviation sigma^2, i.e. sigma^2 * log2(e) in the exponent of
+# 2 the kernel works in.  The running row maximum then keeps growing through the first KV
+# blocks, which is the regime in which the kernel postpones rescaling its accumulators (it lets
+# P reach 2^13 before it rescales) -- and the regime real projection outputs put it in.
+HOT_SIGMA = float(np.sqrt(20.0 / np.log2(np.e)))
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("b,h,s,d", [(1, 2, 512, 128), (1, 1, 1152, 128)])
+def test_mha_f16_scores_with_large_spread(oracle, b, h, s, d, causal):
+    rng = np.random.default_rng(77 + s)
+    stride = h * d
+    q = (rng.standard_normal((b * s, stride)) * HOT_SIGMA).astype(np.float16)
+    k = (rng.standard_normal((b * s, stride)) * HOT_SIGMA).astype(np.float16)
+    v = rng.standard_normal((b * s, stride)).astype(np.float16)
+    want = np.zeros((b * s, stride), np.float16)
+    for bi in range(b):
+        for hi in range(h):
+            off = bi * s * stride + hi * d
+            oracle.attention(q.reshape(-1)[off:], k.reshape(-1)[off:], v.reshape(-1)[off:], s, s, d, d,
+                             causal=causal, strides=(stride,) * 4, f16_out=True, out=want.reshape(-1)[off:])
+    out = torch.full((b * s * stride,), float("nan"), device="cuda", dtype=torch.float16)
+    ops.attention_mha_f16(device(), dev(q), dev(k), dev(v), out, b, h, s, s, d, stride, causal)
+    assert ops.last_variant() == "flash_tcgen05"
+    assert ops.device_status(device())[0] == 0
+    assert_attention_close(host(out, (b * s, stride)).astype(np.float32), want.astype(np.float32))
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_attention_tc_f32_scores_with_large_spread(oracle, causal):
+    """The single-head drop-in form (f32 output) in the same regime, at the reference's largest
+    shape (seq_k = 384, d = 128)."""
+    sq, sk, d = 128, 384, 128
+    rng = np.random.default_rng(5)
+    q = (rng.standard_normal(sq * d) * HOT_SIGMA).astype(np.float16)
+    k = (rng.standard_normal(sk * d) * HOT_SIGMA).astype(np.float16)
+    v = rng.standard_normal(sk * d).astype(np.float16)
+    want = oracle.attention(q, k, v, sq, sk, d, d, causal=causal)
+    out = torch.full((sq * d,), float("nan"), device="cuda", dtype=torch.float32)
+    fn = ops.attention_tc_causal if causal else ops.attention_tc
+    fn(device(), dev(q), dev(k), dev(v), out, sq, sk, d, d)
+    assert ops.device_status(device())[0] == 0
+    assert_attention_close(host(out, (sq, d)), want)
+
+
 def test_rejects_bad_arguments():
     d = device()
     t = torch.zeros(16 * 16, device="cuda", dtype=torch.float16)

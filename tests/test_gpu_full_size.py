@@ -65,7 +65,7 @@ def test_qkv_config4_sampled_rows(oracle):
     rows = [0, 127, 128, 8191, 16383] + rng.integers(0, m, 3).tolist()
     # W8A16 with per-column scales
     w8 = [rng.integers(-127, 128, (k, n), dtype=np.int8) for _ in range(3)]
-    cs = [rng.uniform(0.0001, 0.001, n).astype(np.float32) for _ in range(3)]
+    cs = [rng.uniform(0.001, 0.01, n).astype(np.float32) for _ in range(3)]
     ops.qkv_project_int8(d, xd, *[dev(w) for w in w8], *[dev(c) for c in cs], *outs, m, n, k)
     assert ops.last_variant() == "qkv_w8a16_tcgen05"
     for o, w, c in zip(outs, w8, cs):
@@ -109,7 +109,34 @@ def test_attention_config4_sampled_heads(oracle):
     assert torch.allclose(o4[:, 0].float(), v4[:, 0].float(), atol=2e-3)
 
 
-@pytest.mark.parametrize("m,k,n", [(256, 8192, 28672), (4096, 28672, 8192)])
+def test_attention_config4_projection_like_inputs(oracle):
+    """Config 4 with q and k as a W4A16 projection of unit-variance activations produces them
+    (standard deviation ~3.7, scores spread over ~20 powers of two): the regime the attention
+    kernel's postponed rescaling is tuned in, causal and full, on sampled heads and rows."""
+    b, h, s, hd = 8, 32, 2048, 128
+    stride = h * hd
+    sigma = float(np.sqrt(20.0 / np.log2(np.e)))
+    g = torch.Generator(device="cuda")
+    g.manual_seed(4)
+    q, k = [(torch.randn(b * s * stride, device="cuda", generator=g) * sigma).half() for _ in range(2)]
+    v = torch.randn(b * s * stride, device="cuda", generator=g).half()
+    o = torch.empty(b * s * stride, device="cuda", dtype=torch.float16)
+    for causal in (True, False):
+        ops.attention_mha_f16(device(), q, k, v, o, b, h, s, s, hd, stride, causal)
+        assert ops.last_variant() == "flash_tcgen05"
+        assert ops.device_status(device())[0] == 0
+        for (bi, hi) in [(0, 0), (5, 9), (7, 31)]:
+            sl = lambda t: np.ascontiguousarray(host(t.view(b, s, h, hd)[bi, :, hi, :]))
+            qh, kh, vh = sl(q), sl(k), sl(v)
+            got = sl(o).astype(np.float32)
+            for rows in [(0, 140), (1000, 1100), (1960, 2048)]:
+                want = oracle.attention(qh.reshape(-1), kh.reshape(-1), vh.reshape(-1), s, s, hd, hd,
+                                        causal=causal, rows=rows)
+                assert_attention_close(got[rows[0]:rows[1]], want[rows[0]:rows[1]])
+
+
+@pytest.mark.parametrize("m,k,n", [(16, 8192, 28672), (16, 28672, 8192), (256, 8192, 28672), (256, 28672, 8192),
+                                   (4096, 8192, 28672), (4096, 28672, 8192)])
 def test_w4a16_ffn70b_config5_sampled_rows(oracle, m, k, n):
     rng = np.random.default_rng(5)
     w = rng.integers(-8, 8, (k, n), dtype=np.int8)
@@ -119,8 +146,11 @@ def test_w4a16_ffn70b_config5_sampled_rows(oracle, m, k, n):
     del w
     c = torch.empty(m * n, device="cuda", dtype=torch.float16)
     ops.matmul_int4(device(), dev(a), dev(packed), dev(s), c, m, n, k, G)
-    # M <= 512 dequantises inside the GEMM; larger M dequantises once, then runs the f16 GEMM
-    assert ops.last_variant().startswith("w4a16_fused_dequant" if m <= 512 else "w4a16_tcgen05")
+    # M <= 16 streams the weights through the split-K decode kernel, M <= 512 dequantises inside
+    # the GEMM; larger M dequantises once, then runs the f16 GEMM
+    assert ops.last_variant().startswith("w4a16_decode" if m <= 16 else
+                                         "w4a16_fused_dequant" if m <= 512 else "w4a16_tcgen05")
+    assert ops.device_status(device())[0] == 0
     rows = [0, m // 2, m - 1]
     want = oracle.matmul_int4(a[rows], packed, s, len(rows), n, k, f16_out=True)
     assert max_rel(host(c.view(m, n)[rows]), want) < 2e-2
