@@ -164,6 +164,22 @@ int32_t kaio_b200_qkv_project_int8_colscale(const kaio_f16* x, size_t x_len, con
                                             size_t k_len, kaio_f16* v_out, size_t v_len,
                                             uint32_t m, uint32_t n, uint32_t k, void* stream);
 
+/* Extension (no reference counterpart: the reference's INT8 QKV op is W8A16,
+ * kaio-ops/src/qkv_project_int8_kernel.rs:1965-1985): the W8A8 form.  x is quantised per row on
+ * the fly with the reference's symmetric quantiser (examples/int8_matmul/src/main.rs:41-61:
+ * s_x[i] = max_k |x[i,k]| / 127, 1 for an all-zero row; xq = clamp(round(x / s_x), -127, 127),
+ * round half away from zero), the products accumulate exactly in s32 on the INT8 tensor pipe, and
+ * out_P[i,j] = f16((((sum_k xq[i,k] * w_P[k,j]) as f32) * s_x[i]) * scale_P[j]).
+ * x f16 [m,k] (16-byte aligned); w_P s8 [k,n] row-major; scale_P f32 [n]; outputs f16 [m,n],
+ * three distinct buffers; k % 32 == 0, n even. */
+int32_t kaio_b200_qkv_project_w8a8(const kaio_f16* x, size_t x_len, const int8_t* w_q,
+                                   size_t w_q_len, const int8_t* w_k, size_t w_k_len,
+                                   const int8_t* w_v, size_t w_v_len, const float* scale_q,
+                                   const float* scale_k, const float* scale_v, size_t scale_len,
+                                   kaio_f16* q_out, size_t q_len, kaio_f16* k_out, size_t k_len,
+                                   kaio_f16* v_out, size_t v_len, uint32_t m, uint32_t n,
+                                   uint32_t k, void* stream);
+
 /* Replaces kaio_ops::qkv_project_int4 (kaio-ops/src/qkv_project_int4_kernel.rs:1495-1555),
  * W4A16: three matmul_int4-style products sharing x, outputs f16 = f16(acc), no post-scale;
  * packed weights and group scales laid out as for kaio_b200_matmul_int4; n even. */

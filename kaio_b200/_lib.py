@@ -33,6 +33,8 @@ SIGNATURES = {
                                    _VP, _SZ, _VP, _SZ, _VP, _SZ, _U32, _U32, _U32, _VP],
     "kaio_b200_qkv_project_int8_colscale": [_VP, _SZ, _VP, _SZ, _VP, _SZ, _VP, _SZ, _VP, _VP, _VP, _SZ,
                                             _VP, _SZ, _VP, _SZ, _VP, _SZ, _U32, _U32, _U32, _VP],
+    "kaio_b200_qkv_project_w8a8": [_VP, _SZ, _VP, _SZ, _VP, _SZ, _VP, _SZ, _VP, _VP, _VP, _SZ,
+                                   _VP, _SZ, _VP, _SZ, _VP, _SZ, _U32, _U32, _U32, _VP],
     "kaio_b200_qkv_project_int4": [_VP, _SZ, _VP, _SZ, _VP, _SZ, _VP, _SZ, _VP, _SZ, _VP, _SZ, _VP, _SZ,
                                    _VP, _SZ, _VP, _SZ, _VP, _SZ, _U32, _U32, _U32, _U32, _VP],
     "kaio_b200_attention_tc": [_VP, _SZ, _VP, _SZ, _VP, _SZ, _VP, _SZ, _U32, _U32, _U32, _U32, _I32, _VP],

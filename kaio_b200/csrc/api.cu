@@ -778,6 +778,76 @@ KAIO_API int32_t kaio_b200_qkv_project_int8_colscale(
     return qkv_int8_common(x, x_len, w, wl, nullptr, col, out, ol, m, n, k, stream);
 }
 
+// W8A8 form of the fused QKV projection: x is quantised per row to s8 on the fly, the three
+// products run on the INT8 tensor pipe, the per-row and per-column scales are applied to the
+// exact s32 accumulators.  Validation follows validate_dims_qkv_int8 (the reference's W8A16
+// op), with K a multiple of 32 as kind::i8 needs.
+KAIO_API int32_t kaio_b200_qkv_project_w8a8(
+    const kaio_f16* x, size_t x_len, const int8_t* w_q, size_t w_q_len, const int8_t* w_k,
+    size_t w_k_len, const int8_t* w_v, size_t w_v_len, const float* scale_q, const float* scale_k,
+    const float* scale_v, size_t scale_len, kaio_f16* q_out, size_t q_len, kaio_f16* k_out,
+    size_t k_len, kaio_f16* v_out, size_t v_len, uint32_t m, uint32_t n, uint32_t k, void* stream)
+{
+    const char* op = "qkv_project_w8a8";
+    const size_t wl[3] = {w_q_len, w_k_len, w_v_len};
+    const size_t ol[3] = {q_len, k_len, v_len};
+    int32_t rc = validate_qkv_int8(x_len, wl, ol, m, n, k);
+    if (rc)
+        return rc;
+    if (k % 32 != 0)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: K must be a multiple of 32 (got %u): the INT8 tensor-core instruction "
+                    "consumes 32 k per step and K is not edge-padded", op, k);
+    if (scale_q == nullptr || scale_k == nullptr || scale_v == nullptr)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG, "%s: scale pointer is null", op);
+    if (scale_len < n)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: scale buffers too small: need %u f32, got %zu", op, n, scale_len);
+    REQUIRE_PTR(x, op, "X");
+    const int8_t* w[3] = {w_q, w_k, w_v};
+    const float* col[3] = {scale_q, scale_k, scale_v};
+    void* out[3] = {q_out, k_out, v_out};
+    for (int i = 0; i < 3; ++i) {
+        REQUIRE_PTR(w[i], op, "W");
+        REQUIRE_PTR(out[i], op, "output");
+    }
+    for (int i = 0; i < 3; ++i)
+        for (int j = i + 1; j < 3; ++j)
+            if (out[i] == out[j])
+                return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                            "%s: the three output buffers must be distinct allocations", op);
+    if ((uintptr_t)x % 16 != 0)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG, "%s: X must be 16-byte aligned", op);
+    DeviceCtx* ctx;
+    if ((rc = get_ctx(&ctx, q_out)))
+        return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // scratch: the quantised activations (m*k s8, rounded up to 256 bytes) and their row scales
+    const size_t xq_bytes = (((size_t)m * k + 255) / 256) * 256;
+    StreamScratch* sc = nullptr;
+    if ((rc = ensure_dq_workspace(ctx, s, xq_bytes + (size_t)m * sizeof(float), &sc)))
+        return rc;
+    int8_t* xq = reinterpret_cast<int8_t*>(sc->dq_workspace);
+    float* x_scale = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sc->dq_workspace) + xq_bytes);
+    cudaError_t err = launch_quantize_rows_int8_f16(reinterpret_cast<const __half*>(x), xq, x_scale,
+                                                    m, k, s);
+    if (err != cudaSuccess)
+        return fail_cuda(err, op);
+    bool fast = m > 128 && (n % 16 == 0);
+    for (int i = 0; i < 3; ++i)
+        fast = fast && ((uintptr_t)w[i] % 16 == 0) && ((uintptr_t)out[i] % 16 == 0) &&
+               ((uintptr_t)col[i] % 16 == 0);
+    if (fast)
+        return finish(launch_w8a8_qkv_2cta(*ctx, xq, x_scale, w, col, out, m, n, k, s), op,
+                      "qkv_w8a8_tcgen05_2cta");
+    for (int i = 0; i < 3; ++i) {
+        err = launch_int8_generic(EPI_ROWCOL_F16, xq, w[i], out[i], 1.0f, x_scale, col[i], m, n, k, s);
+        if (err != cudaSuccess)
+            return fail_cuda(err, op);
+    }
+    return finish(cudaSuccess, op, "qkv_w8a8_generic");
+}
+
 KAIO_API int32_t kaio_b200_qkv_project_int4(
     const kaio_f16* x, size_t x_len, const uint32_t* w_q_packed, size_t w_q_len,
     const uint32_t* w_k_packed, size_t w_k_len, const uint32_t* w_v_packed, size_t w_v_len,

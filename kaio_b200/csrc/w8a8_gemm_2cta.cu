@@ -89,7 +89,8 @@ struct alignas(64) TensorMaps {
 
 template <int EPI, int NP>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
-w8a8_gemm_2cta_kernel(const __grid_constant__ TensorMaps<NP> maps, const Params p)
+w8a8_gemm_2cta_kernel(const __grid_constant__ TensorMaps<NP> maps,
+                      const __grid_constant__ Params p)
 {
     constexpr bool OUT_F16 = (EPI == EPI_ROWCOL_F16);
     constexpr uint32_t CHUNK = OUT_F16 ? 64u : 32u;  // columns per staged 128-byte-row block
@@ -297,11 +298,9 @@ w8a8_gemm_2cta_kernel(const __grid_constant__ TensorMaps<NP> maps, const Params 
                     tmem_ld_32x32b_x32(taddr + c * 64, lo);
                     tmem_ld_32x32b_x32(taddr + c * 64 + 32, hi);
                     tmem_ld_wait();
-#pragma unroll
-                    for (int part = 0; part < 2; ++part) {
+                    auto narrow = [&](const uint32_t (&src)[32], const int part) {
 #pragma unroll
                         for (int j = 0; j < 32; j += 4) {
-                            const uint32_t* src = part == 0 ? lo : hi;
                             const uint32_t cc = col0 + part * 32 + j;
                             float4 ws = make_float4(0.f, 0.f, 0.f, 0.f);
                             if (cc < p.n)  // N % 16 == 0: whole vector in or out
@@ -315,7 +314,9 @@ w8a8_gemm_2cta_kernel(const __grid_constant__ TensorMaps<NP> maps, const Params 
                             r[part * 16 + j / 2] = *reinterpret_cast<const uint32_t*>(&h01);
                             r[part * 16 + j / 2 + 1] = *reinterpret_cast<const uint32_t*>(&h23);
                         }
-                    }
+                    };
+                    narrow(lo, 0);
+                    narrow(hi, 1);
                 } else {
                 tmem_ld_32x32b_x32(taddr + c * 32, r);
                 tmem_ld_wait();

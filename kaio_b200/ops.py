@@ -191,6 +191,20 @@ def qkv_project_int8(device, x, w_q, w_k, w_v, scale_q, scale_k, scale_v, q_out,
           *_buf(v_out, torch.float16, "v_out"), m, n, k)
 
 
+def qkv_project_w8a8(device, x, w_q, w_k, w_v, scale_q, scale_k, scale_v, q_out, k_out, v_out, m, n, k):
+    """Extension: the W8A8 fused QKV projection -- ``x`` (f16) quantised per row to s8 on the fly,
+    s32 accumulation on the INT8 tensor pipe, per-row x per-column scales, f16 outputs.
+    ``scale_*`` are float32 tensors of length ``n``."""
+    sq, _ = _buf(scale_q, torch.float32, "scale_q")
+    sk, _ = _buf(scale_k, torch.float32, "scale_k")
+    sv, _ = _buf(scale_v, torch.float32, "scale_v")
+    sl = C.c_size_t(min(scale_q.numel(), scale_k.numel(), scale_v.numel()))
+    _call(device, "kaio_b200_qkv_project_w8a8", *_buf(x, torch.float16, "x"),
+          *_buf(w_q, torch.int8, "w_q"), *_buf(w_k, torch.int8, "w_k"), *_buf(w_v, torch.int8, "w_v"),
+          sq, sk, sv, sl, *_buf(q_out, torch.float16, "q_out"), *_buf(k_out, torch.float16, "k_out"),
+          *_buf(v_out, torch.float16, "v_out"), m, n, k)
+
+
 def qkv_project_int4(device, x, w_q_packed, w_k_packed, w_v_packed, scales_q, scales_k, scales_v,
                      q_out, k_out, v_out, m, n, k, group_size):
     """``kaio_ops::qkv_project_int4`` (kaio-ops/src/qkv_project_int4_kernel.rs:1495-1555)."""

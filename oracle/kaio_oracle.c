@@ -297,6 +297,55 @@ KAIO_EXPORT void kaio_oracle_qkv_int8(const uint16_t *x, const int8_t *w, float 
     }
 }
 
+/* One projection of the W8A8 fused QKV op (extended: the reference's INT8 QKV op is W8A16, so
+ * parity is unpinned by reference tests).  Built from two reference pieces: the symmetric
+ * per-tensor quantiser of examples/int8_matmul/src/main.rs:41-61 applied to each row of x
+ * (s_x = max|x| / 127, 1 for an all-zero row; xq = clamp(round(x / s_x), -127, 127), round half
+ * away from zero, x widened from f16 to f32 exactly) and cpu_reference of
+ * kaio-ops/tests/matmul_int8_e2e.rs:20-34 (exact s32 accumulation, one cast, then f32
+ * multiplies): out = f16_rn(((acc as f32) * s_x[i]) * col_scale[j]).  acc_out (may be NULL)
+ * receives the s32 accumulators, xq_out / sx_out (may be NULL) the quantised row. */
+KAIO_EXPORT void kaio_oracle_qkv_w8a8(const uint16_t *x, const int8_t *w, const float *col_scale,
+                                      uint32_t m, uint32_t n, uint32_t k, uint32_t row0,
+                                      uint32_t row1, uint16_t *out, int32_t *acc_out,
+                                      int8_t *xq_out, float *sx_out)
+{
+    (void)m;
+#pragma omp parallel for schedule(static)
+    for (int64_t i = row0; i < (int64_t)row1; i++) {
+        int32_t *acc = (int32_t *)calloc(n, sizeof(int32_t));
+        int8_t *xq = (int8_t *)malloc(k);
+        float mx = 0.0f;
+        for (uint32_t kk = 0; kk < k; kk++) {
+            float a = fabsf(kaio_oracle_f16_to_f32(x[(size_t)i * k + kk]));
+            mx = a > mx ? a : mx;
+        }
+        float s = (mx == 0.0f) ? 1.0f : mx / 127.0f;
+        for (uint32_t kk = 0; kk < k; kk++) {
+            float v = roundf(kaio_oracle_f16_to_f32(x[(size_t)i * k + kk]) / s);
+            v = v < -127.0f ? -127.0f : (v > 127.0f ? 127.0f : v);
+            xq[kk] = (int8_t)v;
+        }
+        for (uint32_t kk = 0; kk < k; kk++) {
+            const int32_t xv = xq[kk];
+            const int8_t *wrow = w + (size_t)kk * n;
+            for (uint32_t j = 0; j < n; j++)
+                acc[j] += xv * (int32_t)wrow[j];
+        }
+        for (uint32_t j = 0; j < n; j++) {
+            out[(size_t)i * n + j] = kaio_oracle_f32_to_f16(((float)acc[j] * s) * col_scale[j]);
+            if (acc_out)
+                acc_out[(size_t)i * n + j] = acc[j];
+        }
+        if (xq_out)
+            memcpy(xq_out + (size_t)i * k, xq, k);
+        if (sx_out)
+            sx_out[i] = s;
+        free(xq);
+        free(acc);
+    }
+}
+
 /* One projection of kaio-ops/tests/qkv_project_int4_e2e.rs:70-100. */
 KAIO_EXPORT void kaio_oracle_qkv_int4(const uint16_t *x, const uint32_t *w_packed,
                                       const uint16_t *scales, uint32_t m, uint32_t n, uint32_t k,

@@ -143,6 +143,24 @@ def qkv_int8(x, w, scale, m, n, k, col_scale=None, rows=None):
     return out
 
 
+def qkv_w8a8(x, w, col_scale, m, n, k, rows=None, want_acc=False):
+    """One W8A8 projection (extended; no reference counterpart): per-row symmetric quantisation of
+    ``x`` (examples/int8_matmul/src/main.rs:41-61), exact s32 accumulation
+    (kaio-ops/tests/matmul_int8_e2e.rs:20-34), ``f16(((acc as f32) * s_x[i]) * col_scale[j])``.
+    With ``want_acc`` also returns the s32 accumulators, the quantised rows and their scales."""
+    x = np.ascontiguousarray(x, dtype=np.float16)
+    w = np.ascontiguousarray(w, dtype=np.int8)
+    cs = np.ascontiguousarray(col_scale, dtype=np.float32)
+    out = np.zeros((m, n), dtype=np.float16)
+    acc = np.zeros((m, n), dtype=np.int32) if want_acc else None
+    xq = np.zeros((m, k), dtype=np.int8) if want_acc else None
+    sx = np.zeros(m, dtype=np.float32) if want_acc else None
+    r0, r1 = _rows(m, rows)
+    lib().kaio_oracle_qkv_w8a8(_p(x), _p(w), _p(cs), C.c_uint32(m), C.c_uint32(n), C.c_uint32(k), r0, r1,
+                               _p(out), _p(acc), _p(xq), _p(sx))
+    return (out, acc, xq, sx) if want_acc else out
+
+
 def qkv_int4(x, packed, scales, m, n, k, group_size=128, rows=None):
     """One W4A16 projection -- kaio-ops/tests/qkv_project_int4_e2e.rs:70-100."""
     return matmul_int4(x, packed, scales, m, n, k, group_size, rows=rows, f16_out=True)

@@ -72,6 +72,13 @@ def test_qkv_config4_sampled_rows(oracle):
         got = host(o.view(m, n)[rows])
         want = oracle.qkv_int8(x[rows], w, 0.0, len(rows), n, k, col_scale=c)
         assert max_rel(got, want) < 1e-3
+    # W8A8: x quantised per row on the fly, INT8 tensor pipe; every step is exact or rounded once
+    ops.qkv_project_w8a8(d, xd, *[dev(w) for w in w8], *[dev(c) for c in cs], *outs, m, n, k)
+    assert ops.last_variant() == "qkv_w8a8_tcgen05_2cta"
+    for o, w, c in zip(outs, w8, cs):
+        got = host(o.view(m, n)[rows])
+        want = oracle.qkv_w8a8(x[rows], w, c, len(rows), n, k)
+        assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
     # W4A16
     w4 = [rng.integers(-8, 8, (k, n), dtype=np.int8) for _ in range(3)]
     sc = [rng.uniform(0.005, 0.02, (k // G) * n).astype(np.float16) for _ in range(3)]

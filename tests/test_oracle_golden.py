@@ -330,3 +330,22 @@ def test_matmul_f16_quadrant_canary(oracle):
     got = oracle.matmul_f16(a.reshape(-1), b.reshape(-1), m, n, k)
     want = np.outer(np.arange(m) + 1, np.arange(n) + 1) * k * 1e-4
     assert np.allclose(got, want, rtol=3e-3)
+
+
+def test_qkv_w8a8_is_the_quantiser_followed_by_the_int8_reference(oracle):
+    """The W8A8 QKV oracle (no reference counterpart) composes two restated reference functions:
+    its s32 accumulators must equal matmul_int8 on the rows quantise_rows_int8 produces, and its
+    outputs the two f32 multiplies + one f16 rounding of those accumulators."""
+    rng = np.random.default_rng(21)
+    m, n, k = 9, 24, 96
+    x = rng.standard_normal((m, k)).astype(np.float16)
+    x[3] = 0
+    w = rng.integers(-127, 128, (k, n), dtype=np.int8)
+    cs = rng.uniform(0.001, 0.01, n).astype(np.float32)
+    out, acc, xq, sx = oracle.qkv_w8a8(x, w, cs, m, n, k, want_acc=True)
+    q_ref, s_ref = oracle.quantize_rows_int8(x.astype(np.float32), m, k)
+    assert np.array_equal(xq, q_ref) and np.array_equal(sx, s_ref) and sx[3] == 1.0
+    _, acc_ref = oracle.matmul_int8(q_ref, w, 1.0, m, n, k, want_acc=True)
+    assert np.array_equal(acc, acc_ref)
+    want = ((acc.astype(np.float32) * sx[:, None]).astype(np.float32) * cs[None, :]).astype(np.float32)
+    assert np.array_equal(out, want.astype(np.float16))
