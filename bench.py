@@ -402,8 +402,10 @@ def bench_decode(torch, ops, dev, peaks, traffic):
     for mm in DECODE_MS:
         a = torch.randn(mm * k, device="cuda", generator=g).half()
         c = torch.zeros(mm * n, dtype=torch.float16, device="cuda")
-        for i in range(nb):  # warm-up + workspace allocation before capture
-            ops.matmul_int4(dev, a, ws[i], sc[i], c, mm, n, k, 128)
+        torch.cuda.synchronize()
+        with torch.cuda.stream(stream):  # warm-up + the stream's scratch allocation, before capture
+            for i in range(nb):
+                ops.matmul_int4(sdev, a, ws[i], sc[i], c, mm, n, k, 128)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         reps = 4

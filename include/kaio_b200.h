@@ -107,7 +107,7 @@ int32_t kaio_b200_matmul_int4_f16out(const kaio_f16* a, size_t a_len, const uint
 
 /* No counterpart in the reference.  kaio_b200_matmul_int4 for decode shapes (m <= 16) that
  * allocates nothing: same arguments, same result bit for bit, but the split-K scratch (partial
- * tiles, arrival counters, status words) lives in a fixed ~2.6 MB array inside the library instead
+ * tiles, arrival counters, status words) lives in a fixed ~5.3 MB array inside the library instead
  * of a cudaMalloc'd workspace.  It is for callers that cannot allocate at call time: a host
  * runtime whose memory pool already owns all device memory (a later cudaMalloc would fail), or a
  * latency-critical loop that must not hit the device-wide synchronisation an allocation implies.
@@ -115,7 +115,7 @@ int32_t kaio_b200_matmul_int4_f16out(const kaio_f16* a, size_t a_len, const uint
  * most 160 SMs, 16-byte aligned a / b_packed.
  * The first call on each device looks up the array's device address.  With CUDA's lazy module
  * loading that look-up is also what places the array in device memory, so the first call can
- * still claim those ~2.6 MB: make it before a pool reserves the rest of the device and before any
+ * still claim those ~5.3 MB: make it before a pool reserves the rest of the device and before any
  * stream capture.  Later calls allocate nothing.
  * Every call on a device shares the one array, so calls that may overlap on the GPU (different
  * streams) race: order them.  The call clears the arrival counters on `stream` before launching;
@@ -292,6 +292,13 @@ int32_t kaio_b200_device_status(void* stream, uint32_t code[4]);
  * kaio_b200_device_status() then reports KAIO_B200_ERR_TIMEOUT.  This is the path every kernel of
  * the library takes when a device-side wait runs out: a status code, never a hang or a trap. */
 int32_t kaio_b200_selftest_bounded_wait(uint32_t budget_us, void* stream);
+
+/* Diagnostic (no counterpart in the reference): enqueues a probe of the INT8 tensor-pipe rate on
+ * `stream` -- one CTA per SM, each issuing `iters` back-to-back tcgen05.mma kind::i8 M128 N256 K32
+ * on zeroed shared-memory operands, no loads, no epilogue -- and stores in *ops the integer
+ * operations it stands for (2 * 128 * 256 * 32 * iters * SMs).  The caller times it with events:
+ * ops / time is the INT8 tensor peak a GEMM on this device can be measured against. */
+int32_t kaio_b200_probe_int8_mma_rate(uint32_t iters, uint64_t* ops, void* stream);
 
 /* Name of the kernel variant the last call on this thread dispatched to (for tests and
  * traces): e.g. "w8a8_tcgen05", "int8_generic". */

@@ -49,6 +49,7 @@ SIGNATURES = {
     "kaio_b200_silu_gate_f16": [_VP, _SZ, _VP, _SZ, _VP, _SZ, _U32, _U32, _U32, _U32, _U32, _VP],
     "kaio_b200_device_status": [_VP, C.POINTER(_U32)],
     "kaio_b200_selftest_bounded_wait": [_U32, _VP],
+    "kaio_b200_probe_int8_mma_rate": [_U32, C.POINTER(C.c_uint64), _VP],
 }
 
 

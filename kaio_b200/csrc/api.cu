@@ -1317,9 +1317,9 @@ KAIO_API int32_t kaio_b200_sum_partials_f32(const float* slots, size_t slots_len
 // ---------------------------------------------------------------- allocation-free decode entry
 // Scratch of kaio_b200_matmul_int4_noalloc: split-K partial tiles, tile arrival counters and a
 // status block, in a fixed array that is part of the loaded module (every GPU that loads the
-// library holds these ~2.6 MB until the process exits).
+// library holds these ~5.3 MB until the process exits).
 namespace kaio {
-constexpr size_t NOALLOC_MAX_CTAS = 160;         // one CTA per SM; B200 has 148
+constexpr size_t NOALLOC_MAX_CTAS = 320;         // two CTAs per SM; B200 has 148 SMs
 constexpr size_t NOALLOC_MAX_TILES = 4096;       // column tiles of 128 -> N <= 524288
 constexpr size_t NOALLOC_PARTIAL_BYTES = NOALLOC_MAX_CTAS * 2 * 16 * 128 * sizeof(float);
 constexpr size_t NOALLOC_COUNTER_BYTES = NOALLOC_MAX_TILES * sizeof(uint32_t);
@@ -1517,6 +1517,23 @@ KAIO_API int32_t kaio_b200_selftest_bounded_wait(uint32_t budget_us, void* strea
         return rc;
     return finish(launch_selftest_bounded_wait(*ctx, budget_us, static_cast<cudaStream_t>(stream)),
                   "selftest_bounded_wait", "selftest_bounded_wait");
+}
+
+// Diagnostic: enqueues the INT8 tensor-pipe rate probe (one CTA per SM, `iters` back-to-back
+// M128 N256 K32 MMAs each) and reports the work it represents; the caller times it with events.
+KAIO_API int32_t kaio_b200_probe_int8_mma_rate(uint32_t iters, uint64_t* ops, void* stream)
+{
+    if (iters == 0 || iters > (1u << 24))
+        return fail(KAIO_B200_ERR_INVALID_CONFIG, "probe_int8_mma_rate: iters must be 1..2^24 (got %u)",
+                    iters);
+    DeviceCtx* ctx;
+    int32_t rc;
+    if ((rc = get_ctx(&ctx)))
+        return rc;
+    if (ops)
+        *ops = 2ull * 128 * 256 * 32 * (uint64_t)iters * (uint64_t)ctx->num_sms;
+    return finish(launch_int8_mma_rate(*ctx, iters, static_cast<cudaStream_t>(stream)),
+                  "probe_int8_mma_rate", "int8_mma_rate_probe");
 }
 
 KAIO_API void kaio_b200_shutdown(void)

@@ -22,6 +22,7 @@ namespace kaio {
 enum : uint32_t {
     DEV_OK = 0,
     DEV_TIMEOUT = 1,
+    DEV_BAD_LAYOUT = 2,  // a kernel found its shared-memory window laid out unexpectedly
 };
 
 enum : uint32_t {
@@ -126,7 +127,10 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity
 
 // Each poll may park for up to WAIT_HINT_NS; WAIT_POLL_LIMIT polls bound a wait to about one
 // second (the hint is an upper bound, so the limit also counts polls that return early).
-constexpr uint32_t WAIT_HINT_NS = 20000;
+#ifndef KAIO_WAIT_HINT_NS
+#define KAIO_WAIT_HINT_NS 20000
+#endif
+constexpr uint32_t WAIT_HINT_NS = KAIO_WAIT_HINT_NS;
 constexpr uint32_t WAIT_POLL_LIMIT = 1u << 20;
 
 // ~1 s at 2 GHz: the bound of every wait in the shipped kernels.
@@ -167,6 +171,52 @@ __device__ __forceinline__ bool mbar_wait_lane(uint32_t bar, uint32_t parity,
 {
     return mbar_wait_lane_budget(bar, parity, abort_flag, status, site, kernel_id,
                                  WAIT_CYCLE_LIMIT);
+}
+
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred P;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, P;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// WARP-COLLECTIVE polling wait for the few warps whose reaction time bounds a pipeline (a TMA
+// producer, an MMA issuer): it polls with the non-blocking test_wait instead of parking in
+// try_wait, so it sees the phase flip within tens of cycles.  Same bound and same give-up
+// protocol as mbar_wait_bounded.  Only lane 0 polls; the outcome is broadcast.
+__device__ __forceinline__ bool mbar_wait_polling(uint32_t bar, uint32_t parity,
+                                                  volatile uint32_t* abort_flag, uint32_t* status,
+                                                  uint32_t site, uint32_t kernel_id)
+{
+    bool ok = true;
+    if ((threadIdx.x & 31u) == 0) {
+        ok = mbar_test_wait(bar, parity);
+        if (!ok) {
+            const unsigned long long t_start = clock64();
+            for (;;) {
+                if (mbar_test_wait(bar, parity)) {
+                    ok = true;
+                    break;
+                }
+                if (*abort_flag)
+                    break;
+                if (clock64() - t_start > WAIT_CYCLE_LIMIT) {
+                    *abort_flag = 1;
+                    report_status(status, DEV_TIMEOUT, site, kernel_id);
+                    break;
+                }
+            }
+        }
+    }
+    return __all_sync(0xffffffffu, ok);
 }
 
 // WARP-COLLECTIVE wait: all 32 lanes of a warp call it together.  Lanes can leave the polling

@@ -144,6 +144,10 @@ cudaError_t launch_silu_gate_f16(const __half* x, const __half* gate, __half* ou
 cudaError_t launch_selftest_bounded_wait(const DeviceCtx& ctx, uint32_t budget_us,
                                          cudaStream_t stream);
 
+// ---------------------------------------------------------------- tensor-pipe rate probe
+// One CTA per SM issues `iters` back-to-back tcgen05.mma kind::i8 M128 N256 K32.
+cudaError_t launch_int8_mma_rate(const DeviceCtx& ctx, uint32_t iters, cudaStream_t stream);
+
 // ---------------------------------------------------------------- attention
 struct AttnParams {
     const __half *q, *k, *v;

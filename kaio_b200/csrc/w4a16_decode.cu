@@ -11,31 +11,48 @@
 //     D^T[128 weight columns, 16 activation rows] += W^T[128, k] * A^T[k, 16]
 // with the dequantised weights as the 128-row operand in TENSOR MEMORY (tcgen05.st from the
 // dequantising threads, no shared-memory round trip) and the activations as the K-major
-// shared-memory operand.  (mma.sync runs at 256 FMA/clk/SM on this part and was the bound of
-// an earlier version of this kernel.)
+// shared-memory operand.  An M128 N16 K16 MMA with its 128-row operand in tensor memory costs
+// ~10 cycles, so the 16 MMAs of a 16 KiB weight block take ~150 cycles against ~700 cycles of
+// HBM time: the tensor pipe is nearly idle, the instruction budget belongs to the
+// dequantisation (13 ALU / f16x2 instructions per packed word of 8 weights).
 //
 // Work decomposition (stream-K, deterministic):
 //   unit  = (column tile of 128, K block of 256); units are numbered tile-major and cut into
-//           gridDim.x contiguous ranges, so every SM streams the same number of bytes (+-1 unit).
+//           gridDim.x contiguous ranges, so every CTA streams the same number of bytes (+-1 unit).
 //   A CTA that covers a tile's whole K range writes the output directly.  Otherwise each
 //   contributor writes its f32 partial tile to a workspace slot and bumps the tile's counter;
 //   the last one to arrive sums the partials in ascending CTA order -- a fixed order, so the
 //   result does not depend on timing -- and writes the output.
 //
-// CTA = 18 warps:
-//   warp 0       TMA producer: one box [128 columns][128 B = 256 k] of packed weights per stage,
-//                128-byte swizzle, L2 evict-first, 6-stage ring.
-//   warp 1       MMA issuer: 16 x tcgen05.mma kind::f16 (M128 N16 K16) per stage, A from tensor
-//                memory, B (activations) from shared memory; D double-buffered in tensor memory.
-//   warps 2,3,16,17  loaders: the stage's activation slice, written in the UMMA K-major
-//                128-byte-swizzle layout with each group of 8 k permuted to the order the
-//                dequantiser emits, and the stage's 2 x 128 group scales.
-//   warps 4-11   dequantisers: thread = weight column = tensor-memory lane (two warps per
-//                lane quarter, each taking one 128-k scale group of the stage).  16-byte
+// Two CTAs per SM (each <= 113 KB of shared memory and 256 tensor-memory columns): the two
+// pipelines cover each other's bubbles, the split-K fix-up of one overlaps the streaming of the
+// other, and 16 dequantising warps per SM keep the half-rate ALU / f16x2 pipes busy.
+//
+// CTA = 16 warps (64 registers per thread, so that two CTAs fit one SM):
+//   warp 0       TMA producer of the weight ring: one box [128 columns][128 B = 256 k] of packed
+//                weights per stage (128-byte swizzle, L2 evict-first), freed by the dequantisers
+//                as soon as they have consumed it.
+//   warps 1-8    dequantisers: thread = weight column = tensor-memory lane; warps 1-4 take the
+//                first 128 k (= scale group) of every stage, warps 5-8 the second.  16-byte
 //                conflict-free reads of the packed nibbles, 0x6400 magic-number conversion
-//                (exact), hmul2 by the group scale (the reference's rounding), tcgen05.st.
-//   warps 12-15  epilogue: tcgen05.ld of D^T (thread = column, 16 rows), split-K fix-up,
-//                coalesced stores.
+//                (exact), hmul2 by the group scale (the reference's rounding), tcgen05.st into
+//                a ring of three 128-k blocks.  The conversion emits each group of 8 k in the
+//                order [0,4,1,5,2,6,3,7]; the same threads apply that order to their half of the
+//                activation slice IN PLACE (a permutation inside every 16-byte chunk, so the
+//                swizzled layout is untouched).  The group scale is fetched two units ahead.
+//   warps 9-12   epilogue: tcgen05.ld of both k-halves' D^T (thread = column, 16 rows), their
+//                sum, split-K fix-up, stores.
+//   warps 13,14  MMA issuers, one per k-half: 8 tcgen05.mma kind::f16 (M128 N16 K16, A from
+//                tensor memory, B = activations from shared memory) per unit into the half's own
+//                accumulator; the commits free the tensor-memory block and the activation slice
+//                and hand D to the epilogue.
+//   warp 15      TMA producer of the activation ring: four boxes [16 rows][64 k] per stage
+//                (K-major 128-byte-swizzle sub-tiles from L2, rows >= M zero-filled by the
+//                tensor map); a slot is freed by the commits of the MMAs that read it.  Nothing
+//                on the way in goes through a register-level global load, and neither ring waits
+//                for the other.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -45,33 +62,40 @@ namespace w4dec {
 constexpr int BN = 128;   // weight columns per tile = UMMA M
 constexpr int BKK = 256;  // k per stage (128 bytes of nibbles per column)
 constexpr int NROWS = 16; // activation rows = UMMA N
-constexpr int STAGES = 6;
-constexpr int A_SLOTS = 3;              // tensor-memory ring of dequantised weight blocks
-constexpr int W_BYTES = BN * 128;       // 16 KiB packed weights
+constexpr int W_STAGES = 5;               // ring of packed-weight boxes (HBM latency)
+constexpr int X_STAGES = 4;               // ring of activation slices (L2 latency)
+constexpr int A_SLOTS = 3;                // tensor-memory ring of dequantised 128-k blocks
+constexpr int W_BYTES = BN * 128;         // 16 KiB packed weights
 constexpr int X_BYTES = NROWS * BKK * 2;  // 8 KiB activations, 4 sub-tiles [16 rows][128 B]
-constexpr int S_BYTES = 2 * BN * 2;     // 512 B: 2 groups x 128 columns f16
-constexpr int STAGE_BYTES = 25 * 1024;  // W | X | scales, padded to keep W and X 1024-aligned
-constexpr int NUM_LOADER_WARPS = 4;
+constexpr int X_SUB_BYTES = NROWS * 128;  // one sub-tile of 64 k
+constexpr int X_RING_OFF = W_STAGES * W_BYTES;
+constexpr int RING_BYTES = W_STAGES * W_BYTES + X_STAGES * X_BYTES;
 constexpr int NUM_DEQUANT_WARPS = 8;
-constexpr int NUM_WARPS = 18;
+constexpr int NUM_WARPS = 16;
 constexpr int NUM_THREADS = NUM_WARPS * 32;
-constexpr int NUM_BARRIERS = 3 * STAGES + A_SLOTS + 4;
-constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + NUM_BARRIERS * 8 + 64;
+constexpr int NUM_BARRIERS = 2 * W_STAGES + 2 * X_STAGES + 4 * A_SLOTS + 4;
+// The barriers and flags live in the first KiB of the dynamic allocation, the rings start at
+// the next 1024-byte boundary (the 128-byte swizzle needs it): two CTAs then fill an SM's
+// 228 KiB exactly (2 x (113 KiB + 1 KiB reserved by the system)).
+constexpr int HEAD_BYTES = 1024;
+constexpr int SMEM_BYTES = HEAD_BYTES + RING_BYTES;
+static_assert(NUM_BARRIERS * 8 + 64 <= HEAD_BYTES, "barriers must fit the head");
 constexpr int PARTIAL_FLOATS = NROWS * BN;  // one partial tile, [column][row]
-constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t TMEM_D_COL = 0;      // 2 x 16 columns
-constexpr uint32_t TMEM_A_COL = 128;    // A_SLOTS x 128 columns (256 k of f16 pairs)
+constexpr uint32_t TMEM_COLS = 256;
+constexpr uint32_t TMEM_A_COL = 0;      // A_SLOTS x 64 columns (128 k of f16 pairs each)
+constexpr uint32_t TMEM_D_COL = 192;    // 2 buffers x 2 k-halves x 16 columns
+constexpr int CTAS_PER_SM = 2;
+static_assert(2 * (SMEM_BYTES + 1024) <= 228 * 1024, "two CTAs must fit one SM");
 
 constexpr uint32_t IDESC = make_idesc(/*d=f32*/ 1, /*a=f16*/ 0, /*b=f16*/ 0, /*a K-major*/ 0,
                                       /*b K-major*/ 0, BN, NROWS);
 
 enum : uint32_t {
-    SITE_W_EMPTY = 1, SITE_W_FULL = 2, SITE_X_EMPTY = 3, SITE_A_EMPTY = 5,
+    SITE_W_EMPTY = 1, SITE_W_FULL = 2, SITE_X_EMPTY = 3, SITE_X_FULL = 4, SITE_A_EMPTY = 5,
     SITE_A_FULL = 6, SITE_D_EMPTY = 7, SITE_D_FULL = 8
 };
 
 struct Params {
-    const __half* a;       // [M,K]
     const __half* scales;  // [K/128, N]
     void* out[8];          // destinations, f32 or f16, row stride `ld` (one entry unless sharded)
     uint32_t copies;
@@ -88,6 +112,38 @@ struct Params {
 __device__ __forceinline__ void named_barrier(uint32_t id, uint32_t count)
 {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
+// Programmatic dependent launch.  launch_dependents: the next kernel of the stream may start
+// launching its CTAs (they still cannot pass their own wait before this grid has completed).
+// wait: returns once every kernel this launch depends on has completed and its writes are
+// visible; a no-op when the kernel was launched without the programmatic attribute.
+__device__ __forceinline__ void pdl_launch_dependents()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+__device__ __forceinline__ void pdl_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// Named barrier over `count` threads that also ORs a flag across them: every participant
+// receives the same answer, so a group of warps can agree to leave a loop together.
+__device__ __forceinline__ bool named_barrier_or(uint32_t id, uint32_t count, bool flag)
+{
+    uint32_t res;
+    asm volatile(
+        "{\n"
+        ".reg .pred p, q;\n"
+        "setp.ne.u32 q, %1, 0;\n"
+        "bar.red.or.pred p, %2, %3, q;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(res)
+        : "r"((uint32_t)flag), "r"(id), "r"(count)
+        : "memory");
+    return res != 0;
 }
 
 __device__ __forceinline__ uint32_t h2_as_u32(__half2 h)
@@ -179,69 +235,141 @@ __device__ __forceinline__ uint32_t owner_of(uint32_t u, uint32_t units, uint32_
     return (uint32_t)((((uint64_t)u + 1) * grid - 1) / units);
 }
 
+// The producer and the MMA issuer poll (their reaction time is on the critical path of every
+// stage); the many dequantising and epilogue warps park in try_wait and leave the issue slots
+// to the arithmetic.
+#ifdef KAIO_PARKED_WAITS
+#define KAIO_FAST_WAIT mbar_wait_bounded
+#else
+#define KAIO_FAST_WAIT mbar_wait_polling
+#endif
+
 #ifdef KAIO_TRACE
 // Development aid (never compiled into the shipped library): per-CTA cycle stamps of the
-// pipeline hand-offs, [cta][unit][8].
+// pipeline hand-offs, [cta][unit < 48][8].
 __device__ unsigned long long* g_trace = nullptr;
-#define KAIO_STAMP(it, slot)                                                            \
-    do {                                                                                \
-        if (trace_ptr && (it) < 16)                                                     \
-            trace_ptr[((it)) * 8 + (slot)] = clock64();                                 \
+#define KAIO_STAMP(it, slot)                                        \
+    do {                                                            \
+        if (trace_ptr && (it) < 48)                                 \
+            trace_ptr[(it) * 8 + (slot)] = clock64();               \
     } while (0)
 #else
 #define KAIO_STAMP(it, slot) do { } while (0)
 #endif
 
 template <bool OUT_F16>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
-w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const Params p)
+__global__ void __launch_bounds__(NUM_THREADS, CTAS_PER_SM)
+w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
+                    const __grid_constant__ CUtensorMap tmap_x, const Params p)
 {
     extern __shared__ uint8_t smem_raw[];
-    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + STAGES * STAGE_BYTES);
-    const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+    // head (barriers, flags) at the start, rings at the next 1024-byte boundary behind it
+    const uint32_t raw_base = smem_u32(smem_raw);
+    const uint32_t smem_base = (raw_base + NUM_BARRIERS * 8 + 64 + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - raw_base);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw);
+    const uint32_t bar_base = raw_base;
+    // the allocation holds the rings only if the head ends within its first KiB
+    const bool layout_ok = (smem_base - raw_base) + RING_BYTES <= SMEM_BYTES;
+    // w_full[s]: the weight box has landed.  w_empty[s]: the eight dequantising warps have
+    // consumed it (released behind the instructions that used the words, never behind the mere
+    // issue of the loads).  x_full[s]: the activation slice has landed; x_empty[s]: both
+    // k-halves' MMAs that read it have retired.
     auto w_full = [&](uint32_t s) { return bar_base + 8u * s; };
-    auto w_empty = [&](uint32_t s) { return bar_base + 8u * (STAGES + s); };
-    // mma_done[s]: the MMAs of the unit that used ring slot s have retired (one commit per unit
-    // frees both the unit's activation slot and its tensor-memory block)
-    auto mma_done = [&](uint32_t s) { return bar_base + 8u * (2 * STAGES + s); };
-    auto a_full = [&](uint32_t t) { return bar_base + 8u * (3 * STAGES + t); };
-    auto d_full = [&](uint32_t b) { return bar_base + 8u * (3 * STAGES + A_SLOTS + b); };
-    auto d_empty = [&](uint32_t b) { return bar_base + 8u * (3 * STAGES + A_SLOTS + 2 + b); };
+    auto w_empty = [&](uint32_t s) { return bar_base + 8u * (W_STAGES + s); };
+    auto x_full = [&](uint32_t s) { return bar_base + 8u * (2 * W_STAGES + s); };
+    auto x_empty = [&](uint32_t s) { return bar_base + 8u * (2 * W_STAGES + X_STAGES + s); };
+    constexpr uint32_t BAR_A = 2 * W_STAGES + 2 * X_STAGES;
+    // Tensor-memory blocks are used in the order of the half-unit index h = 2 * unit + k-half:
+    // block h % 3.  Consecutive uses of a block belong to different k-halves, i.e. to different
+    // warps, and a parity wait is only sound for a waiter that observes EVERY phase of its
+    // barrier (one that looks at every other phase cannot tell "my phase completed" from "the
+    // phase before it is still open").  So the barriers are indexed by h % 6: each then has one
+    // producer and one consumer, always the same warps.
+    //   a_full[h % 6]:  the k-half's four dequantising warps have filled block h % 3 for h;
+    //   a_empty[h % 6]: the MMAs of half-unit h have retired (waited for by the writers of h + 3).
+    // d_full[b]: both k-halves' MMAs of a segment have retired; d_empty[b]: the epilogue has
+    // read D[b].
+    auto a_full = [&](uint32_t j) { return bar_base + 8u * (BAR_A + j); };
+    auto a_empty = [&](uint32_t j) { return bar_base + 8u * (BAR_A + 2 * A_SLOTS + j); };
+    auto d_full = [&](uint32_t b) { return bar_base + 8u * (BAR_A + 4 * A_SLOTS + b); };
+    auto d_empty = [&](uint32_t b) { return bar_base + 8u * (BAR_A + 4 * A_SLOTS + 2 + b); };
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + NUM_BARRIERS);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     volatile uint32_t* last_flag = tmem_slot + 2;
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
-#ifdef KAIO_TRACE
-    unsigned long long* const trace_ptr = g_trace ? g_trace + (size_t)blockIdx.x * 128 : nullptr;
-#endif
 
+#ifdef KAIO_TRACE
+    unsigned long long* const trace_ptr = g_trace ? g_trace + (size_t)blockIdx.x * 48 * 8 : nullptr;
+    auto gtime = [] {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        return t;
+    };
+    if (threadIdx.x == 0 && trace_ptr) {
+        trace_ptr[47 * 8 + 0] = gtime();
+        trace_ptr[47 * 8 + 4] = clock64();
+    }
+#endif
     const uint32_t units = p.num_tiles * p.num_kb;
     const uint32_t u_begin = range_begin(blockIdx.x, units, gridDim.x);
-    const uint32_t u_end = range_begin(blockIdx.x + 1, units, gridDim.x);
+    uint32_t u_end = range_begin(blockIdx.x + 1, units, gridDim.x);
+    if (!layout_ok) {
+        // never seen (the dynamic window starts 1024-aligned when a kernel has no static shared
+        // memory); reported instead of assumed
+        if (threadIdx.x == 0)
+            report_status(p.status, DEV_BAD_LAYOUT, 0, KERNEL_W4A16_DECODE);
+        u_end = u_begin;
+    }
 
+    // What this launch may do before the kernels in front of it in the stream have finished
+    // (programmatic dependent launch): everything that reads only the packed weights and their
+    // scales -- model state, which nothing in flight writes -- i.e. the first weight boxes and
+    // the dequantisation of the first blocks into tensor memory.  The activations, the split-K
+    // scratch and the outputs are touched only behind pdl_wait().
+    pdl_launch_dependents();
+    const uint32_t n_pre = (u_end - u_begin) < (uint32_t)W_STAGES ? (u_end - u_begin) : (uint32_t)W_STAGES;
     if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < STAGES; ++s) {
-            mbar_init(w_full(s), 2);  // TMA (expect_tx) + the stage's loader warp
+        for (uint32_t s = 0; s < W_STAGES; ++s) {
+            mbar_init(w_full(s), 1);
             mbar_init(w_empty(s), NUM_DEQUANT_WARPS);
-            mbar_init(mma_done(s), 1);
         }
-        for (uint32_t t = 0; t < A_SLOTS; ++t) {
-            mbar_init(a_full(t), NUM_DEQUANT_WARPS);
+        fence_barrier_init();
+        // the first weight boxes go out before the rest of the set-up: their HBM latency
+        // (~1.7 us on a cold launch) then overlaps barrier set-up and the tensor-memory allocation
+        {
+            const uint64_t pol_w = l2_policy_evict_first();
+            uint32_t tile = u_begin / p.num_kb, kb = u_begin % p.num_kb;
+            for (uint32_t i = 0; i < n_pre; ++i) {
+                mbar_expect_tx(w_full(i), W_BYTES);
+                tma_load_2d_hint(smem_base + i * W_BYTES, &tmap_w, w_full(i),
+                                 (int32_t)(kb * (BKK / 8)), (int32_t)(tile * BN), pol_w);
+                if (++kb == p.num_kb) {
+                    kb = 0;
+                    ++tile;
+                }
+            }
+        }
+        for (uint32_t s = 0; s < X_STAGES; ++s) {
+            mbar_init(x_full(s), 1);
+            mbar_init(x_empty(s), 2);  // one commit per k-half
+        }
+        for (uint32_t j = 0; j < 2 * A_SLOTS; ++j) {
+            mbar_init(a_full(j), NUM_DEQUANT_WARPS / 2);
+            mbar_init(a_empty(j), 1);
         }
         for (uint32_t b = 0; b < 2; ++b) {
-            mbar_init(d_full(b), 1);
+            mbar_init(d_full(b), 2);   // one commit per k-half
             mbar_init(d_empty(b), 4);
         }
         *abort_flag = 0;
         *last_flag = 0;
         fence_barrier_init();
-        tma_prefetch_desc(&tmap_w);
+        tma_prefetch_desc(&tmap_x);
     }
-    if (warp == 1) {
+    if (warp == 0) {
         tmem_alloc<TMEM_COLS>(smem_u32(const_cast<uint32_t*>(tmem_slot)));
         tmem_relinquish();
     }
@@ -249,85 +377,233 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const Params p)
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    if (threadIdx.x == 0)
-        KAIO_STAMP(15, 7);
+#ifdef KAIO_TRACE
+    if (threadIdx.x == 0 && trace_ptr)
+        trace_ptr[47 * 8 + 1] = gtime();
+#endif
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer (weights)
         // The whole warp runs the loop so that its control flow and address arithmetic stay
         // warp-uniform (uniform registers feed the TMA instruction directly); one elected lane
         // issues.
-        const uint64_t policy = l2_policy_evict_first();
-        uint32_t tile = u_begin / p.num_kb, kb = u_begin % p.num_kb;
-        uint32_t s = 0, ph = 0;
-        for (uint32_t u = u_begin; u < u_end; ++u) {
-            if (!mbar_wait_bounded(w_empty(s), ph ^ 1u, abort_flag, p.status, SITE_W_EMPTY,
+        const uint64_t pol_w = l2_policy_evict_first();
+        // the first n_pre boxes were issued during set-up
+        const uint32_t u0 = u_begin + n_pre;
+        uint32_t tile = u0 / p.num_kb, kb = u0 % p.num_kb;
+        uint32_t ws = n_pre % W_STAGES, wph = n_pre / W_STAGES;
+        for (uint32_t u = u0; u < u_end; ++u) {
+            if (!mbar_wait_bounded(w_empty(ws), wph ^ 1u, abort_flag, p.status, SITE_W_EMPTY,
                                    KERNEL_W4A16_DECODE))
                 break;
             if (elect_one()) {
-                mbar_expect_tx(w_full(s), W_BYTES);
-                tma_load_2d_hint(smem_base + s * STAGE_BYTES, &tmap_w, w_full(s),
-                                 (int32_t)(kb * (BKK / 8)), (int32_t)(tile * BN), policy);
                 KAIO_STAMP(u - u_begin, 0);
+                mbar_expect_tx(w_full(ws), W_BYTES);
+                tma_load_2d_hint(smem_base + ws * W_BYTES, &tmap_w, w_full(ws),
+                                 (int32_t)(kb * (BKK / 8)), (int32_t)(tile * BN), pol_w);
             }
             __syncwarp();
             if (++kb == p.num_kb) {
                 kb = 0;
                 ++tile;
             }
-            if (++s == STAGES) {
-                s = 0;
-                ph ^= 1u;
+            if (++ws == W_STAGES) {
+                ws = 0;
+                wph ^= 1u;
             }
         }
         if (*abort_flag)
             for (uint32_t spin = 0; spin < 2000; ++spin)
                 __nanosleep(100);
-    } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer
-        // Converged warp, one elected lane issues: descriptors and addresses are then computed
-        // in the uniform datapath instead of being moved there per instruction, which is what
-        // bounds the issue rate of these short (N = 16) MMAs.
-        uint32_t seg = 0, s = 0, ph = 0, t = 0, aph = 0;
+    } else if (warp < 1 + NUM_DEQUANT_WARPS) {
+        // ------------------------------------------------------------ dequantisers
+        const uint32_t q = warp & 3u;          // tensor-memory lane quarter of this warp
+        const uint32_t wg = (warp - 1) >> 2;   // which 128-k half (= scale group) of the stage
+        const uint32_t row = q * 32 + lane;    // weight column inside the tile = TMEM lane
+        // loop-invariant offsets: this thread's four 16-byte chunks of packed weights
+        uint32_t w_off[4];
+#pragma unroll
+        for (uint32_t c = 0; c < 4; ++c)
+            w_off[c] = sw128_offset(row, wg * 4 + c);
+        // ... and the two 16-byte chunks of this half's activations it reorders in place (one in
+        // each 64-k sub-tile; chunk c of a sub-tile lies in row c / 8).  The dequantiser emits
+        // each group of 8 k in the order [0,4,1,5,2,6,3,7]; the same order applied inside every
+        // 16-byte chunk of the activations commutes with the 128-byte swizzle (which moves whole
+        // chunks), so the slice stays a valid K-major operand.
+        const uint32_t tid_g = ((warp - 1) & 3u) * 32 + lane;
+        const uint32_t x_off = X_RING_OFF + wg * 2 * X_SUB_BYTES + tid_g * 16;
+        const bool x_live = (tid_g >> 3) < p.m;  // rows >= M are zero
+        const uint32_t a_lane = tmem_base + ((q * 32u) << 16) + TMEM_A_COL;
+        const uint32_t groups = p.k >> 7;
+        auto load_scale = [&](uint32_t t, uint32_t b) -> __half {
+            const uint32_t grp = b * 2 + wg, col = t * BN + row;
+            if (t < p.num_tiles && grp < groups && col < p.n)
+                return __ldg(p.scales + (size_t)grp * p.n + col);
+            return __float2half(0.0f);
+        };
+        auto advance = [&](uint32_t& t, uint32_t& b) {
+            if (++b == p.num_kb) {
+                b = 0;
+                ++t;
+            }
+        };
+        // group scales, two units ahead of their use
+        uint32_t pt = u_begin / p.num_kb, pb = u_begin % p.num_kb;
+        __half sc0 = load_scale(pt, pb);
+        advance(pt, pb);
+        __half sc1 = (u_begin + 1 < u_end) ? load_scale(pt, pb) : __float2half(0.0f);
+        advance(pt, pb);
+        uint32_t ws = 0, wph = 0, xs = 0, xph = 0;
+        uint32_t hu = wg;  // half-unit index 2 * (u - u_begin) + wg
+        for (uint32_t u = u_begin; u < u_end; ++u, hu += 2) {
+            const __half sc2 = (u + 2 < u_end) ? load_scale(pt, pb) : __float2half(0.0f);
+            advance(pt, pb);
+            if (!mbar_wait_bounded(w_full(ws), wph, abort_flag, p.status, SITE_W_FULL,
+                                   KERNEL_W4A16_DECODE))
+                break;
+#ifndef KAIO_TRACE2
+            if (warp == 1 && lane == 0)
+                KAIO_STAMP(u - u_begin, 1);
+#endif
+            const uint8_t* w_s = smem_gen + ws * W_BYTES;
+            uint4 wv[4];
+#pragma unroll
+            for (uint32_t c = 0; c < 4; ++c)
+                wv[c] = *reinterpret_cast<const uint4*>(w_s + w_off[c]);
+            if (!mbar_wait_bounded(x_full(xs), xph, abort_flag, p.status, SITE_X_FULL,
+                                   KERNEL_W4A16_DECODE))
+                break;
+#ifndef KAIO_ABL_NOPERM
+            if (x_live)
+#else
+            if (false)
+#endif
+            {
+#pragma unroll
+                for (uint32_t j = 0; j < 2; ++j) {
+                    uint4* xp = reinterpret_cast<uint4*>(smem_gen + xs * X_BYTES + x_off + j * X_SUB_BYTES);
+                    const uint4 v = *xp;
+                    uint4 o;  // memory order [0..7] -> dequantiser order [0,4,1,5,2,6,3,7]
+                    o.x = __byte_perm(v.x, v.z, 0x5410);  // (h0, h4)
+                    o.y = __byte_perm(v.x, v.z, 0x7632);  // (h1, h5)
+                    o.z = __byte_perm(v.y, v.w, 0x5410);  // (h2, h6)
+                    o.w = __byte_perm(v.y, v.w, 0x7632);  // (h3, h7)
+                    *xp = o;
+                }
+            }
+            const __half2 sc = __half2half2(sc0);
+            // the tensor-memory block is free once the MMAs of the half-unit three back retired
+            if (hu >= A_SLOTS &&
+                !mbar_wait_bounded(a_empty((hu - A_SLOTS) % (2 * A_SLOTS)),
+                                   ((hu - A_SLOTS) / (2 * A_SLOTS)) & 1u, abort_flag, p.status,
+                                   SITE_A_EMPTY, KERNEL_W4A16_DECODE))
+                break;
+            tc_fence_after_sync();
+#ifndef KAIO_TRACE2
+            if (warp == 1 && lane == 0)
+                KAIO_STAMP(u - u_begin, 2);
+#endif
+            const uint32_t a_tmem = a_lane + (hu % A_SLOTS) * (BKK / 4);
+#pragma unroll
+            for (uint32_t c = 0; c < 4; ++c) {
+                uint32_t r[16];
+#ifdef KAIO_ABL_NOALU
+                r[0] = wv[c].x; r[1] = wv[c].y; r[2] = wv[c].z; r[3] = wv[c].w;
+                r[4] = wv[c].x ^ h2_as_u32(sc); r[5] = r[1]; r[6] = r[2]; r[7] = r[3];
+                r[8] = r[0]; r[9] = r[1]; r[10] = r[2]; r[11] = r[3];
+                r[12] = r[0]; r[13] = r[1]; r[14] = r[2]; r[15] = r[3];
+#else
+                dequant8(wv[c].x, sc, r[0], r[1], r[2], r[3]);
+                dequant8(wv[c].y, sc, r[4], r[5], r[6], r[7]);
+                dequant8(wv[c].z, sc, r[8], r[9], r[10], r[11]);
+                dequant8(wv[c].w, sc, r[12], r[13], r[14], r[15]);
+#endif
+                tmem_st_32x32b_x16(a_tmem + c * 16, r);
+            }
+#ifndef KAIO_TRACE2
+            if (warp == 1 && lane == 0)
+                KAIO_STAMP(u - u_begin, 3);
+#endif
+            tmem_st_wait();
+            if (warp == 1 && lane == 0)
+                KAIO_STAMP(u - u_begin, 4);
+            if (warp == 5 && lane == 0)
+                KAIO_STAMP(u - u_begin, 5);
+            tc_fence_before_sync();
+            fence_proxy_async_smem();  // the reordered activations are read by the tensor core
+            __syncwarp();
+            if (lane == 0) {
+                // The weight stage is released here, behind the instructions that consumed its
+                // words: an arrive placed right after the loads were issued is not ordered
+                // behind them, and a refill can then land before a late load has read the stage.
+                mbar_arrive(w_empty(ws));
+                mbar_arrive(a_full(hu % (2 * A_SLOTS)));
+            }
+            sc0 = sc1;
+            sc1 = sc2;
+            if (++ws == W_STAGES) {
+                ws = 0;
+                wph ^= 1u;
+            }
+            if (++xs == X_STAGES) {
+                xs = 0;
+                xph ^= 1u;
+            }
+        }
+    } else if (warp == 13 || warp == 14) {
+        // ------------------------------------------------------------ MMA issuers
+        // One warp per k-half, each with its own accumulator, on two different schedulers: a
+        // single issuer shares its scheduler with dequantising warps that are always ready to
+        // issue, and its ~150 instructions per unit then take ~1800 cycles -- more than the HBM
+        // time of the unit.  Converged warp, one elected lane issues, so descriptors and
+        // addresses are computed in the uniform datapath.
+        const uint32_t wg = warp - 13;
+        uint32_t seg = 0, xs = 0;
+        uint32_t hu = wg;  // half-unit index 2 * (u - u_begin) + wg
         uint32_t kb = u_begin % p.num_kb;
         bool seg_first = true;
-        for (uint32_t u = u_begin; u < u_end; ++u) {
+        for (uint32_t u = u_begin; u < u_end; ++u, hu += 2) {
             const bool seg_last = (kb + 1 == p.num_kb) || (u + 1 == u_end);
             const uint32_t buf = seg & 1u;
-            if (lane == 0)
-                KAIO_STAMP(u - u_begin, 7);
             if (seg_first &&
                 !mbar_wait_bounded(d_empty(buf), ((seg >> 1) & 1u) ^ 1u, abort_flag, p.status,
                                    SITE_D_EMPTY, KERNEL_W4A16_DECODE))
                 break;
-            // a_full implies the stage's activations are in place: the dequantisers waited for
-            // the loader's arrival on w_full before they produced this block
-            if (!mbar_wait_bounded(a_full(t), aph, abort_flag, p.status, SITE_A_FULL,
-                                   KERNEL_W4A16_DECODE))
+            // a_full implies that the unit's activation slice has landed and that this half of
+            // it is in the dequantiser's k order
+            const uint32_t aj = hu % (2 * A_SLOTS);
+            if (!mbar_wait_bounded(a_full(aj), (hu / (2 * A_SLOTS)) & 1u, abort_flag, p.status,
+                                   SITE_A_FULL, KERNEL_W4A16_DECODE))
                 break;
             tc_fence_after_sync();
-            if (lane == 0)
-                KAIO_STAMP(u - u_begin, 5);
-            const uint32_t d_tmem = tmem_base + TMEM_D_COL + buf * NROWS;
-            const uint32_t a_tmem = tmem_base + TMEM_A_COL + t * (BKK / 2);
-            const uint64_t b_desc0 =
-                make_smem_desc_sw128(smem_base + s * STAGE_BYTES + W_BYTES, 16, 1024);
+#ifdef KAIO_TRACE2
+            if (lane == 0 && wg == 0)
+                KAIO_STAMP(u - u_begin, 3);
+#endif
+            const uint32_t d_tmem = tmem_base + TMEM_D_COL + buf * 2 * NROWS + wg * NROWS;
+            const uint32_t a_blk = tmem_base + TMEM_A_COL + (hu % A_SLOTS) * (BKK / 4);
+            // this half's two activation sub-tiles (64 k, 2 KiB each); 32 bytes per MMA inside
+            // the row; the descriptor's address field counts 16-byte units
+            const uint64_t b_desc0 = make_smem_desc_sw128(
+                smem_base + X_RING_OFF + xs * X_BYTES + wg * 2 * X_SUB_BYTES, 16, 1024);
             if (elect_one()) {
-                umma_f16_ts(d_tmem, a_tmem, b_desc0, IDESC, seg_first ? 0u : 1u);
+#ifndef KAIO_ABL_NOMMA
 #pragma unroll
-                for (uint32_t kk = 1; kk < BKK / 16; ++kk) {
-                    // activations: sub-tile kk/4 (64 k, 2 KiB apart), 32 bytes per MMA inside
-                    // the row; the descriptor's address field counts 16-byte units
-                    umma_f16_ts(d_tmem, a_tmem + kk * 8,
-                                b_desc0 + (uint64_t)((kk >> 2) * 128 + (kk & 3u) * 2), IDESC, 1u);
-                }
-                umma_commit(mma_done(s));
+                for (uint32_t kk = 0; kk < 8; ++kk)
+#else
+                for (uint32_t kk = 0; kk < 1; ++kk)
+#endif
+                    umma_f16_ts(d_tmem, a_blk + kk * 8,
+                                b_desc0 + (uint64_t)((kk >> 2) * (X_SUB_BYTES / 16) + (kk & 3u) * 2),
+                                IDESC, (seg_first && kk == 0) ? 0u : 1u);
+                umma_commit(a_empty(aj));
+                umma_commit(x_empty(xs));
                 if (seg_last)
                     umma_commit(d_full(buf));
             }
             __syncwarp();
             if (lane == 0)
-                KAIO_STAMP(u - u_begin, 6);
+                KAIO_STAMP(u - u_begin, 6 + wg);
             seg_first = false;
             if (seg_last) {
                 ++seg;
@@ -335,156 +611,44 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const Params p)
             }
             if (++kb == p.num_kb)
                 kb = 0;
-            if (++s == STAGES) {
-                s = 0;
-                ph ^= 1u;
-            }
-            if (++t == A_SLOTS) {
-                t = 0;
-                aph ^= 1u;
-            }
+            if (++xs == X_STAGES)
+                xs = 0;
         }
-        (void)ph;
-    } else if (warp == 2 || warp == 3 || warp == 16 || warp == 17) {
-        // ------------------------------------------------------------ activation / scale loaders
-        const uint32_t lw = warp < 4 ? warp - 2 : warp - 14;
-        const uint32_t groups = p.k >> 7;
-        for (uint32_t it = lw; u_begin + it < u_end; it += NUM_LOADER_WARPS) {
-            const uint32_t u = u_begin + it;
-            const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-            // the slot is free when the MMAs that read the activations and the dequantisers
-            // that read the scales have both finished with it
-            if (!mbar_wait_bounded(mma_done(s), ph ^ 1u, abort_flag, p.status, SITE_X_EMPTY,
-                                   KERNEL_W4A16_DECODE) ||
-                !mbar_wait_bounded(w_empty(s), ph ^ 1u, abort_flag, p.status, SITE_W_EMPTY,
+    } else if (warp == 15) {
+        // ------------------------------------------------------------ TMA producer (activations)
+        // Its own warp, so that neither ring waits for the other: a slot of this ring is freed
+        // by the commits of the MMAs that read it, much later than a weight stage.
+        const uint64_t pol_x = l2_policy_evict_last();
+        uint32_t kb = u_begin % p.num_kb;
+        uint32_t xs = 0, xph = 0;
+        pdl_wait();  // the activations may be the output of the kernel in front of this one
+        for (uint32_t u = u_begin; u < u_end; ++u) {
+            if (!mbar_wait_bounded(x_empty(xs), xph ^ 1u, abort_flag, p.status, SITE_X_EMPTY,
                                    KERNEL_W4A16_DECODE))
                 break;
-            const uint32_t tile = u / p.num_kb, kb = u % p.num_kb;
-            uint8_t* stage = smem_gen + s * STAGE_BYTES;
-            uint8_t* x_s = stage + W_BYTES;
-            __half* s_s = reinterpret_cast<__half*>(stage + W_BYTES + X_BYTES);
-            const uint32_t k0 = kb * BKK;
-            // lane = 8-k group cj of the stage (32 groups); one activation row per step
-            const uint32_t cj = lane;
-            const uint32_t kk = k0 + cj * 8;
-            __half sv[8];
+            if (elect_one()) {
+                const uint32_t x_s = smem_base + X_RING_OFF + xs * X_BYTES;
+                mbar_expect_tx(x_full(xs), X_BYTES);
 #pragma unroll
-            for (uint32_t x = 0; x < 8; ++x) {
-                const uint32_t i = lane + 32 * x;
-                const uint32_t grp = kb * 2 + (i >> 7), col = tile * BN + (i & 127u);
-                sv[x] = __float2half(0.0f);
-                if (grp < groups && col < p.n)
-                    sv[x] = __ldg(p.scales + (size_t)grp * p.n + col);
+                for (uint32_t j = 0; j < 4; ++j)
+                    tma_load_2d_hint(x_s + j * X_SUB_BYTES, &tmap_x, x_full(xs),
+                                     (int32_t)(kb * BKK + j * 64), 0, pol_x);
             }
-#pragma unroll
-            for (uint32_t r0 = 0; r0 < NROWS; r0 += 8) {
-                if (r0 >= p.m)
-                    break;  // rows >= M feed output rows that are never stored
-                uint4 v[8];
-#pragma unroll
-                for (uint32_t r = 0; r < 8; ++r) {
-                    v[r] = make_uint4(0, 0, 0, 0);
-                    if (r0 + r < p.m && kk < p.k)
-                        v[r] = __ldg(
-                            reinterpret_cast<const uint4*>(p.a + (size_t)(r0 + r) * p.k + kk));
-                }
-#pragma unroll
-                for (uint32_t r = 0; r < 8; ++r) {
-                    if (r0 + r < p.m) {
-                        uint4 o;  // memory order [0..7] -> dequantiser order [0,4,1,5,2,6,3,7]
-                        o.x = __byte_perm(v[r].x, v[r].z, 0x5410);  // (h0, h4)
-                        o.y = __byte_perm(v[r].x, v[r].z, 0x7632);  // (h1, h5)
-                        o.z = __byte_perm(v[r].y, v[r].w, 0x5410);  // (h2, h6)
-                        o.w = __byte_perm(v[r].y, v[r].w, 0x7632);  // (h3, h7)
-                        // K-major 128-byte-swizzle tile: sub-tile cj/8, row, 16-byte chunk cj%8
-                        *reinterpret_cast<uint4*>(x_s + (cj >> 3) * 2048 +
-                                                  sw128_offset(r0 + r, cj & 7u)) = o;
-                    }
-                }
-            }
-#pragma unroll
-            for (uint32_t x = 0; x < 8; ++x)
-                s_s[lane + 32 * x] = sv[x];
-            fence_proxy_async_smem();  // the activations are read by the tensor core (async proxy)
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(w_full(s));
-                KAIO_STAMP(it, 1);
+            if (++kb == p.num_kb)
+                kb = 0;
+            if (++xs == X_STAGES) {
+                xs = 0;
+                xph ^= 1u;
             }
         }
-    } else if (warp >= 4 && warp < 12) {
-        // ------------------------------------------------------------ dequantisers
-        const uint32_t q = warp & 3u;          // tensor-memory lane quarter of this warp
-        const uint32_t wg = (warp - 4) >> 2;   // which 128-k half (= scale group) of the stage
-        const uint32_t row = q * 32 + lane;    // weight column inside the tile = TMEM lane
-        // loop-invariant offsets: this thread's four 16-byte chunks and its group scale
-        uint32_t w_off[4];
-#pragma unroll
-        for (uint32_t c = 0; c < 4; ++c)
-            w_off[c] = sw128_offset(row, wg * 4 + c);
-        const uint32_t sc_off = (wg * BN + row) * 2;
-        const uint32_t a_lane = tmem_base + ((q * 32u) << 16) + TMEM_A_COL + wg * 64;
-        uint32_t it = 0;
-        for (uint32_t u = u_begin; u < u_end; ++u, ++it) {
-            const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-            const uint32_t t = it % A_SLOTS;
-            // w_full completes when both the TMA box and the loader's activations/scales landed
-            if (!mbar_wait_bounded(w_full(s), ph, abort_flag, p.status, SITE_W_FULL,
-                                   KERNEL_W4A16_DECODE))
-                break;
-            if (warp == 4 && lane == 0)
-                KAIO_STAMP(it, 2);
-            const uint8_t* stage = smem_gen + s * STAGE_BYTES;
-            uint4 wv[4];
-#pragma unroll
-            for (uint32_t c = 0; c < 4; ++c)
-                wv[c] = *reinterpret_cast<const uint4*>(stage + w_off[c]);
-            const __half2 sc =
-                __half2half2(*reinterpret_cast<const __half*>(stage + W_BYTES + X_BYTES + sc_off));
-            // the tensor-memory block is free once the MMAs of unit it - A_SLOTS have retired
-            if (it >= A_SLOTS) {
-                const uint32_t pit = it - A_SLOTS;
-                if (!mbar_wait_bounded(mma_done(pit % STAGES), (pit / STAGES) & 1u, abort_flag,
-                                       p.status, SITE_A_EMPTY, KERNEL_W4A16_DECODE))
-                    break;
-            }
-            tc_fence_after_sync();
-            if (warp == 4 && lane == 0)
-                KAIO_STAMP(it, 3);
-            const uint32_t a_tmem = a_lane + t * (BKK / 2);
-#pragma unroll
-            for (uint32_t c = 0; c < 4; ++c) {
-                uint32_t r[16];
-                dequant8(wv[c].x, sc, r[0], r[1], r[2], r[3]);
-                dequant8(wv[c].y, sc, r[4], r[5], r[6], r[7]);
-                dequant8(wv[c].z, sc, r[8], r[9], r[10], r[11]);
-                dequant8(wv[c].w, sc, r[12], r[13], r[14], r[15]);
-                tmem_st_32x32b_x16(a_tmem + c * 16, r);
-            }
-            tmem_st_wait();
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) {
-                // The stage is released only here, behind the instructions that consumed the
-                // loaded words.  Releasing it right after the loads is not safe: nothing in the
-                // instruction stream then ties a load to the arrive, a load scheduled close to
-                // its use ran about a microsecond after the arrive, and the refill of the stage
-                // (six units ahead) occasionally landed first -- seen as a few columns computed
-                // from the wrong k block once in several hundred launches.
-                mbar_arrive(w_empty(s));
-                mbar_arrive(a_full(t));
-            }
-#ifdef KAIO_TRACE
-            if (lane == 0 && trace_ptr && it < 16)
-                atomicMax(&trace_ptr[it * 8 + 4], (unsigned long long)clock64());
-#endif
-        }
-    } else {
-        // ------------------------------------------------------------ epilogue (warps 12..15)
+    } else if (warp >= 9 && warp <= 12) {
+        // ------------------------------------------------------------ epilogue (warps 9..12)
         const uint32_t q = warp & 3u;
         const uint32_t tid = q * 32 + lane;  // weight column inside the tile = TMEM lane
         uint32_t seg = 0;
         uint32_t seg_kb_lo = u_begin % p.num_kb;
+        pdl_wait();  // the split-K scratch and the outputs belong to the launch in front until it is done
         for (uint32_t u = u_begin; u < u_end; ++u) {
             const uint32_t tile = u / p.num_kb, kb = u % p.num_kb;
             if (!((kb + 1 == p.num_kb) || (u + 1 == u_end)))
@@ -494,8 +658,11 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const Params p)
                                    KERNEL_W4A16_DECODE))
                 break;
             tc_fence_after_sync();
-            uint32_t raw[16];
-            tmem_ld_32x32b_x16(tmem_base + ((q * 32u) << 16) + TMEM_D_COL + buf * NROWS, raw);
+            // the two k-halves of every stage accumulate separately; their sum is the segment
+            uint32_t raw0[16], raw1[16];
+            const uint32_t d_lane = tmem_base + ((q * 32u) << 16) + TMEM_D_COL + buf * 2 * NROWS;
+            tmem_ld_32x32b_x16(d_lane, raw0);
+            tmem_ld_32x32b_x16(d_lane + NROWS, raw1);
             tmem_ld_wait();
             tc_fence_before_sync();
             __syncwarp();
@@ -504,34 +671,37 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const Params p)
             float acc[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i)
-                acc[i] = __uint_as_float(raw[i]);
+                acc[i] = __uint_as_float(raw0[i]) + __uint_as_float(raw1[i]);
 
             const bool complete = (seg_kb_lo == 0) && (kb + 1 == p.num_kb);
             bool write_out = complete;
             if (!complete) {
                 // slot 0: the segment that opens this CTA's range; slot 1: the one that closes it
                 const uint32_t first_tile = u_begin / p.num_kb;
-                const uint32_t slot = (tile == first_tile) ? 0u : 1u;
+                const uint32_t pslot = (tile == first_tile) ? 0u : 1u;
                 float* mine =
-                    p.partials + ((size_t)(blockIdx.x * 2 + slot) * PARTIAL_FLOATS) + tid * 16;
+                    p.partials + ((size_t)(blockIdx.x * 2 + pslot) * PARTIAL_FLOATS) + tid * 16;
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
                     __stcg(reinterpret_cast<float4*>(mine + i * 4),
                            make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]));
-                // One thread fences for the four warps: the barrier in front orders their parked
-                // stores before its release fence, the barrier behind orders its acquire fence
-                // before their loads (both fences are cumulative).  A fence in every thread costs
-                // about a microsecond per launch here.
+                // One thread synchronises for the four warps with a single acquire-release
+                // atomic: the barrier in front orders their parked stores before its release, the
+                // barrier behind orders its acquire before their loads (release and acquire are
+                // cumulative).  Separate fences around a relaxed atomic are three dependent
+                // round trips to L2 instead of one, in the tail of every CTA.
                 named_barrier(2, 128);
                 const uint32_t c_first = owner_of(tile * p.num_kb, units, gridDim.x);
                 const uint32_t c_last = owner_of(tile * p.num_kb + p.num_kb - 1, units, gridDim.x);
                 if (tid == 0) {
-                    asm volatile("fence.acq_rel.gpu;" ::: "memory");
-                    const uint32_t prev = atomicAdd(p.counters + tile, 1u);
+                    uint32_t prev;
+                    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;"
+                                 : "=r"(prev)
+                                 : "l"(p.counters + tile)
+                                 : "memory");
                     const bool last = (prev == c_last - c_first);
                     if (last)
                         p.counters[tile] = 0;  // self-resetting for the next launch
-                    asm volatile("fence.acq_rel.gpu;" ::: "memory");
                     *last_flag = last ? 1u : 0u;
                 }
                 named_barrier(2, 128);
@@ -582,15 +752,23 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const Params p)
             ++seg;
             seg_kb_lo = 0;  // the next segment starts a new tile
         }
+#ifdef KAIO_TRACE
+        if (warp == 9 && lane == 0 && trace_ptr)
+            trace_ptr[47 * 8 + 2] = gtime();
+#endif
     }
 
     // ---------------------------------------------------------------- teardown
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 1) {
+    if (warp == 0) {
         tc_fence_after_sync();
         tmem_dealloc<TMEM_COLS>(tmem_base);
     }
+#ifdef KAIO_TRACE
+    if (threadIdx.x == 0 && trace_ptr)
+        trace_ptr[47 * 8 + 3] = gtime();
+#endif
 }
 
 }  // namespace w4dec
@@ -614,7 +792,8 @@ bool w4a16_decode_ok(const void* x, const DqProblem* probs, int num_probs, uint3
 static uint32_t decode_grid(const DeviceCtx& ctx, uint32_t n, uint32_t k)
 {
     const uint32_t units = ((n + w4dec::BN - 1) / w4dec::BN) * ((k + w4dec::BKK - 1) / w4dec::BKK);
-    return units < (uint32_t)ctx.num_sms ? units : (uint32_t)ctx.num_sms;
+    const uint32_t ctas = (uint32_t)ctx.num_sms * w4dec::CTAS_PER_SM;
+    return units < ctas ? units : ctas;
 }
 
 size_t w4a16_decode_workspace_bytes(const DeviceCtx& ctx, uint32_t n, uint32_t k)
@@ -639,8 +818,13 @@ cudaError_t launch_w4a16_decode(const DeviceCtx& ctx, const __half* x, const DqP
                              (uint64_t)(k / 8) * 4, BKK / 8, BN, CU_TENSOR_MAP_SWIZZLE_128B);
     if (err != cudaSuccess)
         return err;
+    // activations [m, k] f16: boxes of [16 rows][64 k]; rows >= m are filled with zeros
+    CUtensorMap tmap_x;
+    err = encode_tensor_map_2d(&tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x, k, m, (uint64_t)k * 2,
+                               64, NROWS, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (err != cudaSuccess)
+        return err;
     Params p;
-    p.a = x;
     p.scales = prob.scales;
     for (int i = 0; i < 8; ++i)
         p.out[i] = copies ? copies->ptrs[(uint32_t)i < copies->count ? i : 0] : prob.out;
@@ -657,6 +841,25 @@ cudaError_t launch_w4a16_decode(const DeviceCtx& ctx, const __half* x, const DqP
     p.status = ctx.status;
     const uint32_t grid = decode_grid(ctx, n, k);
 
+    // Programmatic dependent launch: this launch may begin (weight prefetch, first
+    // dequantisation) while the kernel in front of it in the stream drains; it reads the
+    // activations and writes scratch and outputs only after that kernel has completed.
+    // KAIO_B200_PDL=0 restores plain stream serialisation.
+    static const bool use_pdl = [] {
+        const char* e = getenv("KAIO_B200_PDL");
+        return !(e != nullptr && e[0] == '0');
+    }();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = use_pdl ? 1 : 0;
+
     static bool attr_set[2][64] = {};
 #define KAIO_LAUNCH_W4DEC(F16)                                                                    \
     do {                                                                                          \
@@ -667,7 +870,9 @@ cudaError_t launch_w4a16_decode(const DeviceCtx& ctx, const __half* x, const DqP
                 return err;                                                                       \
             attr_set[F16 ? 1 : 0][ctx.device] = true;                                             \
         }                                                                                         \
-        w4a16_decode_kernel<F16><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmap_w, p);           \
+        err = cudaLaunchKernelEx(&cfg, w4a16_decode_kernel<F16>, tmap_w, tmap_x, p);              \
+        if (err != cudaSuccess)                                                                   \
+            return err;                                                                           \
     } while (0)
 
     if (out_f16)

@@ -85,6 +85,17 @@ def selftest_bounded_wait(device: KaioDevice, budget_us: int = 5):
     _call(device, "kaio_b200_selftest_bounded_wait", C.c_uint32(budget_us))
 
 
+def probe_int8_mma_rate(device: KaioDevice, iters: int) -> int:
+    """Enqueue the INT8 tensor-pipe rate probe (one CTA per SM, ``iters`` back-to-back
+    ``tcgen05.mma kind::i8`` M128 N256 K32 each); returns the integer operations it stands for."""
+    ops_count = C.c_uint64(0)
+    lib = _lib.load()
+    with torch.cuda.device(device.ordinal):
+        _check(lib.kaio_b200_probe_int8_mma_rate(C.c_uint32(iters), C.byref(ops_count),
+                                                 C.c_void_p(device.stream_handle())))
+    return int(ops_count.value)
+
+
 # ------------------------------------------------------------------ W8A8
 
 def matmul_int8(device, a, b, c, scale, m, n, k):

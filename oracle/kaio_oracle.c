@@ -494,6 +494,18 @@ KAIO_EXPORT void kaio_oracle_quantize_gptq_lite(const float *w, uint32_t k, uint
 
 /* ---------------------------------------------------------------- misc */
 
+/* Sets the number of OpenMP threads of the following calls (a launcher such as torchrun exports
+ * OMP_NUM_THREADS=1 to its workers; a timed CPU baseline wants all the host's cores). */
+KAIO_EXPORT void kaio_oracle_set_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0)
+        omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 KAIO_EXPORT int kaio_oracle_num_threads(void)
 {
 #ifdef _OPENMP

@@ -49,6 +49,12 @@ def lib() -> C.CDLL:
     return _lib
 
 
+def set_threads(n: int) -> int:
+    """Use ``n`` OpenMP threads from now on; returns the count now in effect."""
+    lib().kaio_oracle_set_threads(C.c_int(int(n)))
+    return num_threads()
+
+
 def _p(a: np.ndarray | None):
     if a is None:
         return None
