@@ -88,6 +88,11 @@ int32_t kaio_b200_matmul_tc_async(const kaio_f16* a, size_t a_len, const kaio_f1
                                   float* c, size_t c_len, uint32_t m, uint32_t n, uint32_t k,
                                   void* stream);
 
+/* Extension: the same product narrowed to f16 (round to nearest even): c f16 [m,n]. */
+int32_t kaio_b200_matmul_tc_f16out(const kaio_f16* a, size_t a_len, const kaio_f16* b, size_t b_len,
+                                   kaio_f16* c, size_t c_len, uint32_t m, uint32_t n, uint32_t k,
+                                   void* stream);
+
 /* ---- W4A16 ----------------------------------------------------------------------- */
 
 /* Replaces kaio_ops::matmul_int4 (kaio-ops/src/matmul_int4_kernel.rs:2126-2171).
@@ -98,6 +103,17 @@ int32_t kaio_b200_matmul_int4(const kaio_f16* a, size_t a_len, const uint32_t* b
                               size_t b_len, const kaio_f16* scales, size_t scales_len, float* c,
                               size_t c_len, uint32_t m, uint32_t n, uint32_t k,
                               uint32_t group_size, void* stream);
+
+/* Extension (no reference counterpart): the dequantisation step of kaio_b200_matmul_int4 on its
+ * own -- w[kk, j] = f16(q[kk, j]) * scales[kk / 128, j] rounded to f16, the reference's mul.f16
+ * (kaio-ops/src/matmul_int4_kernel.rs:655-713) -- written as f16 [k, n] row-major.  A caller that
+ * runs several products against the same weights in one step (row chunks of a large M whose
+ * partial results are exchanged while the next chunk is computed) dequantises once and then calls
+ * kaio_b200_matmul_tc / kaio_b200_matmul_tc_f16out: the results equal kaio_b200_matmul_int4's for
+ * m > 512 bit for bit, since that op runs these two steps internally.  n even. */
+int32_t kaio_b200_dequantize_int4(const uint32_t* b_packed, size_t b_len, const kaio_f16* scales,
+                                  size_t scales_len, kaio_f16* w, size_t w_len, uint32_t k,
+                                  uint32_t n, uint32_t group_size, void* stream);
 
 /* Extension: same product with the f32 accumulator narrowed to f16 (round to nearest even). */
 int32_t kaio_b200_matmul_int4_f16out(const kaio_f16* a, size_t a_len, const uint32_t* b_packed,

@@ -24,6 +24,8 @@ SIGNATURES = {
     "kaio_b200_matmul_int8_acc": [_VP, _SZ, _VP, _SZ, _VP, _SZ, _U32, _U32, _U32, _VP],
     "kaio_b200_matmul_tc": [_VP, _SZ, _VP, _SZ, _VP, _SZ, _U32, _U32, _U32, _VP],
     "kaio_b200_matmul_tc_async": [_VP, _SZ, _VP, _SZ, _VP, _SZ, _U32, _U32, _U32, _VP],
+    "kaio_b200_matmul_tc_f16out": [_VP, _SZ, _VP, _SZ, _VP, _SZ, _U32, _U32, _U32, _VP],
+    "kaio_b200_dequantize_int4": [_VP, _SZ, _VP, _SZ, _VP, _SZ, _U32, _U32, _U32, _VP],
     "kaio_b200_matmul_int4": [_VP, _SZ, _VP, _SZ, _VP, _SZ, _VP, _SZ, _U32, _U32, _U32, _U32, _VP],
     "kaio_b200_matmul_int4_noalloc": [_VP, _SZ, _VP, _SZ, _VP, _SZ, _VP, _SZ, _U32, _U32, _U32, _U32, _VP],
     "kaio_b200_matmul_int4_allgather": [_VP, _SZ, _VP, _SZ, _VP, _SZ, _VP, _SZ, _U32, _U32, _U32, _U32, _U32,

@@ -646,7 +646,7 @@ KAIO_API int32_t kaio_b200_matmul_int8_acc(const int8_t* a, size_t a_len, const 
 // ---------------------------------------------------------------- matmul_tc (f16 x f16 -> f32)
 // Messages restate validate_dims_tc (kaio-ops/src/matmul_tc_kernel.rs:123-164).
 static int32_t run_matmul_tc(const kaio_f16* a, size_t a_len, const kaio_f16* b, size_t b_len,
-                             float* c, size_t c_len, uint32_t m, uint32_t n, uint32_t k,
+                             void* c, size_t c_len, bool out_f16, uint32_t m, uint32_t n, uint32_t k,
                              void* stream)
 {
     if (m == 0 || n == 0 || k == 0)
@@ -661,7 +661,8 @@ static int32_t run_matmul_tc(const kaio_f16* a, size_t a_len, const kaio_f16* b,
     if (b_len < kn)
         INVALID("matmul_tc: B buffer too small: need %zu f16 (%u\xC3\x97%u), got %zu", kn, k, n, b_len);
     if (c_len < mn)
-        INVALID("matmul_tc: C buffer too small: need %zu f32 (%u\xC3\x97%u), got %zu", mn, m, n, c_len);
+        INVALID("matmul_tc: C buffer too small: need %zu %s (%u\xC3\x97%u), got %zu", mn,
+                out_f16 ? "f16" : "f32", m, n, c_len);
     REQUIRE_PTR(a, "matmul_tc", "A");
     REQUIRE_PTR(b, "matmul_tc", "B");
     REQUIRE_PTR(c, "matmul_tc", "C");
@@ -677,10 +678,10 @@ static int32_t run_matmul_tc(const kaio_f16* a, size_t a_len, const kaio_f16* b,
     pr.scale = 1.0f;
     pr.out = c;
     const __half* x = reinterpret_cast<const __half*>(a);
-    if (dq_gemm_fast_path_ok(WFMT_F16, x, &pr, 1, false, m, n, k))
-        return finish(launch_dq_gemm(*ctx, WFMT_F16, x, &pr, 1, false, false, m, n, k, nullptr, s),
+    if (dq_gemm_fast_path_ok(WFMT_F16, x, &pr, 1, out_f16, m, n, k))
+        return finish(launch_dq_gemm(*ctx, WFMT_F16, x, &pr, 1, out_f16, false, m, n, k, nullptr, s),
                       "matmul_tc", "f16_tcgen05");
-    return finish(launch_dq_generic(WFMT_F16, x, &pr, 1, false, false, m, n, k, s), "matmul_tc",
+    return finish(launch_dq_generic(WFMT_F16, x, &pr, 1, out_f16, false, m, n, k, s), "matmul_tc",
                   "f16_generic");
 }
 
@@ -688,14 +689,61 @@ KAIO_API int32_t kaio_b200_matmul_tc(const kaio_f16* a, size_t a_len, const kaio
                                      float* c, size_t c_len, uint32_t m, uint32_t n, uint32_t k,
                                      void* stream)
 {
-    return run_matmul_tc(a, a_len, b, b_len, c, c_len, m, n, k, stream);
+    return run_matmul_tc(a, a_len, b, b_len, c, c_len, false, m, n, k, stream);
+}
+
+KAIO_API int32_t kaio_b200_matmul_tc_f16out(const kaio_f16* a, size_t a_len, const kaio_f16* b,
+                                            size_t b_len, kaio_f16* c, size_t c_len, uint32_t m,
+                                            uint32_t n, uint32_t k, void* stream)
+{
+    return run_matmul_tc(a, a_len, b, b_len, c, c_len, true, m, n, k, stream);
+}
+
+KAIO_API int32_t kaio_b200_dequantize_int4(const uint32_t* b_packed, size_t b_len,
+                                           const kaio_f16* scales, size_t scales_len, kaio_f16* w,
+                                           size_t w_len, uint32_t k, uint32_t n,
+                                           uint32_t group_size, void* stream)
+{
+    const char* op = "dequantize_int4";
+    if (k == 0 || n == 0)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG, "%s dimensions must be non-zero", op);
+    if (group_size != 128)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG, "%s: group_size must be 128 (got %u)", op, group_size);
+    if (k % 128 != 0)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: K must be a multiple of group_size=128 (got %u)", op, k);
+    if (n % 2 != 0)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG, "%s: N must be even (got %u)", op, n);
+    const size_t words = (size_t)(k / 8) * n, cells = (size_t)(k / 128) * n, kn = (size_t)k * n;
+    if (b_len < words)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG, "%s: packed buffer too small: need %zu u32, got %zu",
+                    op, words, b_len);
+    if (scales_len < cells)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG, "%s: scales buffer too small: need %zu f16, got %zu",
+                    op, cells, scales_len);
+    if (w_len < kn)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: W buffer too small: need %zu f16 (%u\xC3\x97%u), got %zu", op, kn, k, n, w_len);
+    REQUIRE_PTR(b_packed, op, "packed");
+    REQUIRE_PTR(scales, op, "scales");
+    REQUIRE_PTR(w, op, "W");
+    if ((uintptr_t)w % 4 != 0)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG, "%s: W must be 4-byte aligned", op);
+    DeviceCtx* ctx;
+    int32_t rc;
+    if ((rc = get_ctx(&ctx, w)))
+        return rc;
+    return finish(launch_dequant_s4(b_packed, reinterpret_cast<const __half*>(scales),
+                                    reinterpret_cast<__half*>(w), n, k,
+                                    static_cast<cudaStream_t>(stream)),
+                  op, "dequant_s4");
 }
 
 KAIO_API int32_t kaio_b200_matmul_tc_async(const kaio_f16* a, size_t a_len, const kaio_f16* b,
                                            size_t b_len, float* c, size_t c_len, uint32_t m,
                                            uint32_t n, uint32_t k, void* stream)
 {
-    return run_matmul_tc(a, a_len, b, b_len, c, c_len, m, n, k, stream);
+    return run_matmul_tc(a, a_len, b, b_len, c, c_len, false, m, n, k, stream);
 }
 
 KAIO_API int32_t kaio_b200_matmul_int4(const kaio_f16* a, size_t a_len, const uint32_t* b_packed,

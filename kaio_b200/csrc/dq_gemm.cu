@@ -510,6 +510,18 @@ static cudaError_t launch_f16_gemm(const DeviceCtx& ctx, const f16g::TensorMaps&
     return cudaLaunchKernelEx(&cfg, f16_gemm_kernel<PAIR, OUT_F16>, maps, p);
 }
 
+cudaError_t launch_dequant_s4(const uint32_t* w_packed, const __half* scales, __half* out,
+                              uint32_t n, uint32_t k, cudaStream_t stream)
+{
+    DequantArgs da = {};
+    da.w[0] = w_packed;
+    da.scales[0] = scales;
+    da.out[0] = out;
+    dim3 grid((n + 63) / 64, (k + 63) / 64, 1);
+    dequant_s4_kernel<<<grid, 256, 0, stream>>>(da, n, k);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_dq_gemm(const DeviceCtx& ctx, int wfmt, const __half* x, const DqProblem* probs,
                            int num_probs, bool out_f16, bool post_scale, uint32_t m, uint32_t n,
                            uint32_t k, void* dq_workspace, cudaStream_t stream,

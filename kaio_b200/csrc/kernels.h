@@ -114,6 +114,10 @@ struct OutputCopies {
 };
 
 size_t dq_gemm_workspace_bytes(int num_probs, uint32_t n, uint32_t k);
+// The pre-pass of the M > 512 W4A16 path on its own: packed s4 + group scales -> f16 [K,N]
+// row-major with the reference's rounding (f16(q) * f16(scale) in f16).  n even.
+cudaError_t launch_dequant_s4(const uint32_t* w_packed, const __half* scales, __half* out,
+                              uint32_t n, uint32_t k, cudaStream_t stream);
 cudaError_t launch_dq_gemm(const DeviceCtx& ctx, int wfmt, const __half* x, const DqProblem* probs,
                            int num_probs, bool out_f16, bool post_scale, uint32_t m, uint32_t n,
                            uint32_t k, void* dq_workspace, cudaStream_t stream,

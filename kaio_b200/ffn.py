@@ -17,6 +17,10 @@ symmetric allocation), the ranks meet at a barrier, and a small kernel adds the 
 barrier); large ones are scattered by column block and the summed blocks are stored back to every
 rank (two steps, the traffic of a ring all-reduce).
 
+For large M (``reduce="overlap"``, :meth:`FfnInt4.run_overlapped`) the NCCL all-reduce is hidden
+behind the GEMMs: the weights are dequantised once per call, the rows are cut into a few chunks, and
+chunk ``i``'s partial rows are summed on a second stream while chunk ``i+1`` is computed.
+
 The helpers at the top are layout logic and run on CPU tensors too.
 """
 from __future__ import annotations
@@ -79,8 +83,8 @@ class FfnInt4:
 
     def __init__(self, ops, device, hidden: int, inter: int, w_gate, s_gate, w_up, s_up, w_down, s_down,
                  world: int = 1, rank: int = 0, group=None, max_m: int = 4096, reduce: str = "all"):
-        if reduce not in ("all", "scatter", "none", "fused"):
-            raise ValueError(f"reduce must be 'all', 'scatter', 'none' or 'fused', got {reduce!r}")
+        if reduce not in ("all", "scatter", "none", "fused", "overlap"):
+            raise ValueError(f"reduce must be 'all', 'scatter', 'none', 'fused' or 'overlap', got {reduce!r}")
         self.ops, self.device, self.group = ops, device, group
         self.hidden, self.inter, self.world, self.rank, self.reduce = hidden, inter, world, rank, reduce
         lo, hi = shard_bounds(inter, world, rank, multiple=GROUP)
@@ -153,6 +157,69 @@ class FfnInt4:
         self.out_h.barrier()  # every rank's summed block has landed in every rank's output
         return self.out_sym[: m * h].view(m, h)
 
+    # ---- all-reduce overlapped with the GEMMs (large M)
+
+    @staticmethod
+    def default_chunks(m: int) -> list[int]:
+        """Row chunks for :meth:`run_overlapped`: about a half, then a third, then the rest, each
+        a multiple of 256 rows (the tile height of the paired GEMM) -- the exchange of a chunk
+        hides behind the next chunk's GEMMs, and only the last, smallest chunk's is exposed."""
+        if m <= 1024 or m % 256 != 0:
+            return [m]
+        t = m // 256
+        first = max(1, t // 2)
+        second = max(1, (t - first) * 5 // 8)
+        rest = t - first - second
+        rows = [first * 256, second * 256] + ([rest * 256] if rest > 0 else [])
+        return sorted(rows, reverse=True)
+
+    def _init_overlap(self):
+        dev = self.out.device
+        self.w_gu_f16 = torch.empty(self.hidden * 2 * self.i_loc, dtype=torch.float16, device=dev)
+        self.w_down_f16 = torch.empty(self.i_loc * self.hidden, dtype=torch.float16, device=dev)
+        self.comm_stream = torch.cuda.Stream(device=dev)
+
+    def run_overlapped(self, x: torch.Tensor, m: int, chunks: "list[int] | None" = None) -> torch.Tensor:
+        """The chain for large ``m`` with its all-reduce hidden behind the GEMMs.
+
+        The weights are dequantised ONCE per call (``dequantize_int4``, the pre-pass that
+        ``matmul_int4`` runs internally for m > 512), the rows are cut into ``chunks``, and while
+        chunk ``i+1`` runs its three launches (f16 GEMM, SiLU-gate, f16 GEMM) on the calling
+        stream, chunk ``i``'s f32 partial rows are summed across the ranks by NCCL on a second
+        stream.  Per element this is the arithmetic of :meth:`local` (same kernels, same
+        operands), so the un-reduced partial is bit-identical to it.  Returns the complete f32
+        ``[m, hidden]`` on every rank."""
+        if m > self.max_m:
+            raise ValueError(f"m={m} exceeds max_m={self.max_m}")
+        if not hasattr(self, "w_gu_f16"):
+            self._init_overlap()
+        chunks = list(chunks) if chunks is not None else self.default_chunks(m)
+        if sum(chunks) != m or min(chunks) < 1:
+            raise ValueError(f"chunks {chunks} do not add up to m={m}")
+        ops, d, il, h = self.ops, self.device, self.i_loc, self.hidden
+        ops.dequantize_int4(d, self.w_gu, self.s_gu, self.w_gu_f16, h, 2 * il, GROUP)
+        ops.dequantize_int4(d, self.w_down, self.s_down, self.w_down_f16, il, h, GROUP)
+        main = torch.cuda.current_stream()
+        r0 = 0
+        for rows in chunks:
+            xs = x.view(-1)[r0 * h:(r0 + rows) * h]
+            gu = self.gu[r0 * 2 * il:(r0 + rows) * 2 * il]
+            act = self.act[r0 * il:(r0 + rows) * il]
+            out = self.out[r0 * h:(r0 + rows) * h]
+            ops.matmul_tc_f16out(d, xs, self.w_gu_f16, gu, rows, 2 * il, h)
+            ops.silu_gate_f16(d, gu, gu[il:], act, rows, il, x_ld=2 * il, gate_ld=2 * il)
+            ops.matmul_tc(d, act, self.w_down_f16, out, rows, h, il)
+            if self.world > 1:
+                ev = torch.cuda.Event()
+                ev.record(main)
+                with torch.cuda.stream(self.comm_stream):
+                    self.comm_stream.wait_event(ev)
+                    dist.all_reduce(out, op=dist.ReduceOp.SUM, group=self.group)
+            r0 += rows
+        if self.world > 1:
+            main.wait_stream(self.comm_stream)
+        return self.out[: m * h].view(m, h)
+
     def local(self, x: torch.Tensor, m: int) -> torch.Tensor:
         """The three launches of this rank; returns the f32 ``[m, hidden]`` partial sum."""
         if m > self.max_m:
@@ -167,10 +234,12 @@ class FfnInt4:
     def run(self, x: torch.Tensor, m: int) -> torch.Tensor:
         if self.world > 1 and self.reduce == "fused":
             return self.run_fused(x, m)
+        if self.reduce == "overlap" and m > 512:
+            return self.run_overlapped(x, m)
         part = self.local(x, m)
         if self.world == 1 or self.reduce == "none":
             return part
-        if self.reduce == "all":
+        if self.reduce in ("all", "overlap"):
             dist.all_reduce(part, op=dist.ReduceOp.SUM, group=self.group)
             return part
         if m % self.world != 0:

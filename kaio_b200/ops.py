@@ -125,6 +125,20 @@ def matmul_tc(device, a, b, c, m, n, k):
           *_buf(c, torch.float32, "c"), m, n, k)
 
 
+def matmul_tc_f16out(device, a, b, c, m, n, k):
+    """Extension: ``matmul_tc`` with the accumulator narrowed to f16 (``c`` float16)."""
+    _call(device, "kaio_b200_matmul_tc_f16out", *_buf(a, torch.float16, "a"), *_buf(b, torch.float16, "b"),
+          *_buf(c, torch.float16, "c"), m, n, k)
+
+
+def dequantize_int4(device, b_packed, scales, w, k, n, group_size=GROUP_SIZE):
+    """Extension: packed s4 weights + f16 group scales -> f16 ``[k, n]`` row-major with the
+    reference's rounding (``f16(q) * f16(scale)`` in f16): the first step of ``matmul_int4`` for
+    large ``m``, on its own, for callers that reuse the dequantised weights within a step."""
+    _call(device, "kaio_b200_dequantize_int4", *_buf(b_packed, torch.int32, "b_packed"),
+          *_buf(scales, torch.float16, "scales"), *_buf(w, torch.float16, "w"), k, n, group_size)
+
+
 def matmul_tc_async(device, a, b, c, m, n, k):
     """``kaio_ops::matmul_tc_async`` (kaio-ops/src/matmul_tc_async_kernel.rs): same contract."""
     _call(device, "kaio_b200_matmul_tc_async", *_buf(a, torch.float16, "a"), *_buf(b, torch.float16, "b"),

@@ -84,49 +84,6 @@ class ColumnGather:
         return self.full
 
 
-class PanelPipeline:
-    """Sharded W4A16 GEMM whose all-gather overlaps the GEMM: the rank's ``N/P`` columns are cut
-    into ``panels`` column panels; panel ``i`` is gathered (NCCL, on ``comm_stream``) while panel
-    ``i+1`` is computed.  Packed INT4 weights are column-major, so a column panel of the shard is
-    a contiguous slice; the group scales of each panel are copied once at construction.
-
-    After ``run()`` every rank holds the row-major ``[M, N]`` product in ``self.full``.
-    """
-
-    def __init__(self, ops, device, a, w_packed_shard, scales_shard, m, n, k, world, rank, comm_stream,
-                 panels: int = 4, group=None):
-        self.ops, self.device, self.a = ops, device, a
-        self.m, self.n, self.k, self.world, self.group = m, n, k, world, group
-        self.n_loc = n // world
-        while panels > 1 and self.n_loc % (panels * 16) != 0:
-            panels -= 1
-        self.panels, self.pw = panels, self.n_loc // panels
-        kw, groups = k // 8, k // 128
-        self.w = [w_packed_shard.view(-1)[i * self.pw * kw:(i + 1) * self.pw * kw] for i in range(panels)]
-        sc2d = scales_shard.view(groups, self.n_loc)
-        self.sc = [sc2d[:, i * self.pw:(i + 1) * self.pw].contiguous().view(-1) for i in range(panels)]
-        dev_t = a.device
-        self.c = [torch.empty(m * self.pw, dtype=torch.float16, device=dev_t) for _ in range(panels)]
-        self.gathered = [torch.empty(world * m * self.pw, dtype=torch.float16, device=dev_t) for _ in range(panels)]
-        self.full = torch.empty(m, n, dtype=torch.float16, device=dev_t)
-        self.comm_stream = comm_stream
-        self.events = [torch.cuda.Event() for _ in range(panels)]
-
-    def run(self):
-        main = torch.cuda.current_stream()
-        # full[i, p*n_loc + q*pw + j] <- gathered[q][p, i, j]
-        full5 = self.full.view(self.m, self.world, self.panels, self.pw)
-        for q in range(self.panels):
-            self.ops.matmul_int4(self.device, self.a, self.w[q], self.sc[q], self.c[q], self.m, self.pw, self.k, 128)
-            self.events[q].record(main)
-            with torch.cuda.stream(self.comm_stream):
-                self.comm_stream.wait_event(self.events[q])
-                dist.all_gather_into_tensor(self.gathered[q], self.c[q], group=self.group)
-                full5[:, :, q, :].copy_(self.gathered[q].view(self.world, self.m, self.pw).transpose(0, 1))
-        main.wait_stream(self.comm_stream)
-        return self.full
-
-
 class FusedGatherGemm:
     """Sharded W4A16 GEMM whose epilogue writes into every rank's output buffer (peer memory):
     one kernel per rank does the GEMM and the all-gather, tile by tile over NVLink.

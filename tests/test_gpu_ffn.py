@@ -173,3 +173,50 @@ def test_sum_partials_argument_errors():
         ops.sum_partials_f32(d, s[:100], 2, 4, 16, [o.data_ptr()], o.numel(), 16, 0)
     with pytest.raises(InvalidConfig, match="out buffers too small"):
         ops.sum_partials_f32(d, s, 2, 4, 16, [o.data_ptr()], 60, 16, 0)
+
+
+def test_dequantize_then_f16_gemm_equals_matmul_int4(oracle):
+    """kaio_b200_dequantize_int4 writes exactly f16(q) * f16(scale) (checked against numpy), and
+    the f16 GEMM on those weights returns the bits matmul_int4 returns for m > 512 (it runs the
+    same two steps internally)."""
+    m, k, n = 768, 512, 640
+    rng = np.random.default_rng(3)
+    q = rng.integers(-8, 8, (k, n), dtype=np.int8)
+    s = rng.uniform(0.005, 0.02, (k // 128, n)).astype(np.float16)
+    a = rng.standard_normal(m * k).astype(np.float16)
+    packed = oracle.pack_s4(q, k, n)
+    d = device()
+    w16 = torch.full((k * n,), float("nan"), device="cuda", dtype=torch.float16)
+    ops.dequantize_int4(d, dev(packed), dev(s), w16, k, n)
+    want_w = (q.astype(np.float16) * np.repeat(s, 128, axis=0)).astype(np.float16)  # one f16 rounding
+    assert np.array_equal(host(w16, (k, n)).view(np.uint16), want_w.view(np.uint16))
+    for f16_out in (False, True):
+        dt = torch.float16 if f16_out else torch.float32
+        ref = torch.zeros(m * n, device="cuda", dtype=dt)
+        ops.matmul_int4(d, dev(a), dev(packed), dev(s), ref, m, n, k, 128)
+        assert ops.last_variant() == "w4a16_tcgen05"
+        got = torch.zeros(m * n, device="cuda", dtype=dt)
+        (ops.matmul_tc_f16out if f16_out else ops.matmul_tc)(d, dev(a), w16, got, m, n, k)
+        assert ops.device_status(d)[0] == 0
+        assert torch.equal(got.view(torch.int16 if f16_out else torch.int32),
+                           ref.view(torch.int16 if f16_out else torch.int32))
+        want = oracle.matmul_int4(a, packed, s.reshape(-1), m, n, k, f16_out=f16_out)
+        assert max_rel(host(got, (m, n)), want) < (2e-2 if f16_out else 1e-3)
+
+
+def test_chunked_chain_equals_the_whole_chain(oracle):
+    """FfnInt4.run_overlapped on one rank (weights dequantised once, rows in chunks): the same
+    bits as the three whole launches, and the oracle's chain within the GEMMs' bar."""
+    hidden, inter, m = 512, 1024, 1024
+    case = make_ffn_case(oracle, hidden, inter, m, seed=9)
+    weights = [case[n] for n in ("w_gate", "s_gate", "w_up", "s_up", "w_down", "s_down")]
+    chain = ffn.FfnInt4(ops, device(), hidden, inter, *weights, world=1, rank=0, max_m=m, reduce="none")
+    x = case["x"].cuda()
+    whole = chain.local(x, m).clone()
+    parts = chain.run_overlapped(x, m, chunks=[512, 256, 256]).clone()
+    torch.cuda.synchronize()
+    assert ops.device_status(device())[0] == 0
+    assert torch.equal(whole.view(torch.int32), parts.view(torch.int32))
+    want = ffn_oracle(oracle, case, hidden, inter, m)
+    assert max_rel(parts.cpu().numpy(), want) < 1e-2
+    assert ffn.FfnInt4.default_chunks(4096) == [2048, 1280, 768] and ffn.FfnInt4.default_chunks(512) == [512]

@@ -39,13 +39,16 @@ def _worker(rank, world, port, shapes, ret):
             want = ffn_oracle(orc, case, hidden, inter, m)
             weights = [case[n] for n in ("w_gate", "s_gate", "w_up", "s_up", "w_down", "s_down")]
             x = case["x"].cuda()
-            for reduce in ("all", "scatter"):
+            for reduce in ("all", "scatter", "overlap"):
                 chain = ffn.FfnInt4(ops, dev, hidden, inter, *weights, world=world, rank=rank, max_m=max(m, 16),
                                     reduce=reduce)
-                got = chain.run(x, m)
+                # "overlap": the all-reduce of each row chunk on a second stream behind the next
+                # chunk's GEMMs (forced here on shapes below its usual m > 512 threshold)
+                got = chain.run_overlapped(x, m, chunks=[m - m // 2, m // 2]) if reduce == "overlap" \
+                    else chain.run(x, m)
                 torch.cuda.synchronize()
                 got = got.cpu().numpy()
-                ref = want if reduce == "all" else want[rank * (m // world):(rank + 1) * (m // world)]
+                ref = want[rank * (m // world):(rank + 1) * (m // world)] if reduce == "scatter" else want
                 rel = np.max(np.abs(got - ref) / np.maximum(np.abs(ref), 1.0))
                 ok = ok and got.shape == ref.shape and bool(np.all(np.isfinite(got))) and rel < 1e-2
             # the reduction fused into the down projection: one step (whole partials to every rank),

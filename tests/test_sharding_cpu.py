@@ -79,26 +79,3 @@ def test_two_rank_gloo_all_gather_rebuilds_full_output(oracle):
     port = _free_port()
     mp.spawn(_worker, args=(world, port, m, n, k, ret), nprocs=world, join=True)
     assert dict(ret) == {0: True, 1: True}
-
-
-def test_panel_layout_matches_full_product(oracle):
-    """PanelPipeline's index algebra (rank p, panel q, column j -> p*N/P + q*pw + j) on CPU: the
-    panels of every rank's shard, gathered rank-major and un-sharded, give the full product."""
-    m, n, k, world, panels = 5, 128, 128, 2, 2
-    rng = np.random.default_rng(0)
-    w = rng.integers(-8, 8, (k, n), dtype=np.int8)
-    a = rng.standard_normal(m * k).astype(np.float16)
-    sc = rng.uniform(0.005, 0.02, (k // 128) * n).astype(np.float16)
-    want = oracle.matmul_int4(a, oracle.pack_s4(w, k, n), sc, m, n, k, f16_out=True)
-    n_loc, pw = n // world, n // world // panels
-    full = torch.zeros(m, n, dtype=torch.float16)
-    full5 = full.view(m, world, panels, pw)
-    for q in range(panels):
-        gathered = torch.zeros(world, m, pw, dtype=torch.float16)
-        for p in range(world):
-            lo = p * n_loc + q * pw
-            cols = np.ascontiguousarray(w[:, lo:lo + pw])
-            scs = np.ascontiguousarray(sc.reshape(-1, n)[:, lo:lo + pw]).reshape(-1)
-            gathered[p] = torch.from_numpy(oracle.matmul_int4(a, oracle.pack_s4(cols, k, pw), scs, m, pw, k, f16_out=True))
-        full5[:, :, q, :].copy_(gathered.transpose(0, 1))
-    assert np.array_equal(full.numpy(), want)
