@@ -158,6 +158,18 @@ int32_t kaio_b200_matmul_int4_allgather(const kaio_f16* a, size_t a_len,
                                         uint32_t rank, uint32_t m, uint32_t n_total, uint32_t k,
                                         uint32_t group_size, void* stream);
 
+/* Extension (no reference counterpart; KAIO is single-device): the all-gather of a column-parallel
+ * GEMM's output through NCCL.  Every rank passes its [m, n_total / world] shard (row-major,
+ * elem_bytes = 2 for f16 or 4 for f32) and receives the row-major [m, n_total] matrix in `out`.
+ * `nccl_comm` is the caller's ncclComm_t for the `world` ranks; the op enqueues one ncclAllGather
+ * and one copy kernel on `stream`.  NCCL is looked up at the first call (dlopen of libnccl.so.2,
+ * i.e. the NCCL already loaded into the process when there is one), so the library itself has no
+ * link-time dependency on it; without NCCL the call returns KAIO_B200_ERR_CUDA.  The staging
+ * buffer ([world][m][n_total / world]) is library-owned per-stream scratch. */
+int32_t kaio_b200_allgather_cols(const void* shard, size_t shard_len, void* out, size_t out_len,
+                                 uint32_t m, uint32_t n_total, uint32_t elem_bytes, uint32_t world,
+                                 void* nccl_comm, void* stream);
+
 /* ---- fused QKV projection ---------------------------------------------------------- */
 
 /* Replaces kaio_ops::qkv_project_int8 (kaio-ops/src/qkv_project_int8_kernel.rs:2008-2064),

@@ -74,7 +74,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
                     print(log)
     objs = [j[1] for j in jobs]
     if force or any(j[2] for j in jobs) or not os.path.exists(LIB):
-        r = subprocess.run([nvcc, "-shared", "-o", LIB, *objs, "-cudart", "static",
+        r = subprocess.run([nvcc, "-shared", "-o", LIB, *objs, "-cudart", "static", "-ldl",
                             "-gencode", "arch=compute_100a,code=sm_100a"], capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")

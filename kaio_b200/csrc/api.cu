@@ -1241,6 +1241,60 @@ KAIO_API int32_t kaio_b200_matmul_int4_allgather(const kaio_f16* a, size_t a_len
                   op, "w4a16_tcgen05_allgather");
 }
 
+// ---------------------------------------------------------------- NCCL all-gather of column shards
+KAIO_API int32_t kaio_b200_allgather_cols(const void* shard, size_t shard_len, void* out,
+                                          size_t out_len, uint32_t m, uint32_t n_total,
+                                          uint32_t elem_bytes, uint32_t world, void* nccl_comm,
+                                          void* stream)
+{
+    const char* op = "allgather_cols";
+    if (m == 0 || n_total == 0 || world == 0)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG, "%s dimensions must be non-zero", op);
+    if (elem_bytes != 2 && elem_bytes != 4)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG, "%s: elem_bytes must be 2 (f16) or 4 (f32), got %u",
+                    op, elem_bytes);
+    if (n_total % world != 0 || ((n_total / world) * elem_bytes) % 16 != 0)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: N (%u) must split into %u shards whose rows are a multiple of 16 bytes", op,
+                    n_total, world);
+    const uint32_t n_loc = n_total / world;
+    if (shard_len < (size_t)m * n_loc)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: shard buffer too small: need %zu elements (%u\xC3\x97%u), got %zu", op,
+                    (size_t)m * n_loc, m, n_loc, shard_len);
+    if (out_len < (size_t)m * n_total)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: out buffer too small: need %zu elements (%u\xC3\x97%u), got %zu", op,
+                    (size_t)m * n_total, m, n_total, out_len);
+    REQUIRE_PTR(shard, op, "shard");
+    REQUIRE_PTR(out, op, "out");
+    REQUIRE_PTR(nccl_comm, op, "nccl_comm");
+    if ((uintptr_t)shard % 16 != 0 || (uintptr_t)out % 16 != 0)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG, "%s: shard and out must be 16-byte aligned", op);
+    if (!nccl_available())
+        return fail(KAIO_B200_ERR_CUDA, "%s: libnccl.so.2 could not be loaded", op);
+    DeviceCtx* ctx;
+    int32_t rc;
+    if ((rc = get_ctx(&ctx, out)))
+        return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (world == 1) {
+        cudaError_t err = cudaMemcpyAsync(out, shard, (size_t)m * n_total * elem_bytes,
+                                          cudaMemcpyDeviceToDevice, s);
+        return finish(err, op, "allgather_cols_copy");
+    }
+    StreamScratch* sc = nullptr;
+    if ((rc = ensure_dq_workspace(ctx, s, (size_t)m * n_total * elem_bytes, &sc)))
+        return rc;
+    const char* msg = "";
+    cudaError_t cuda_err = cudaSuccess;
+    const int nrc = launch_allgather_cols(shard, sc->dq_workspace, out, m, n_loc, elem_bytes, world,
+                                          nccl_comm, s, &msg, &cuda_err);
+    if (nrc != 0)
+        return fail(KAIO_B200_ERR_CUDA, "%s: NCCL error %d (%s)", op, nrc, msg);
+    return finish(cuda_err, op, "allgather_cols_nccl");
+}
+
 // ---------------------------------------------------------------- row-parallel W4A16 + reduction
 KAIO_API int32_t kaio_b200_matmul_int4_peer_partials(const kaio_f16* a, size_t a_len,
                                                      const uint32_t* b_packed, size_t b_len,

@@ -148,6 +148,15 @@ cudaError_t launch_silu_gate_f16(const __half* x, const __half* gate, __half* ou
 cudaError_t launch_selftest_bounded_wait(const DeviceCtx& ctx, uint32_t budget_us,
                                          cudaStream_t stream);
 
+// ---------------------------------------------------------------- NCCL all-gather of column shards
+// NCCL is looked up with dlopen at first use; false when no libnccl.so.2 can be loaded.
+bool nccl_available();
+// ncclAllGather into staging ([P][m][n_loc]) + un-shard copy into out ([m][P * n_loc]).  Returns
+// the NCCL result (0 = ok) with its text in *msg; a CUDA launch error in *cuda_err.
+int launch_allgather_cols(const void* shard, void* staging, void* out, uint32_t m, uint32_t n_loc,
+                          uint32_t elem_bytes, uint32_t world, void* nccl_comm, cudaStream_t stream,
+                          const char** msg, cudaError_t* cuda_err);
+
 // ---------------------------------------------------------------- tensor-pipe rate probe
 // One CTA per SM issues `iters` back-to-back tcgen05.mma kind::i8 M128 N256 K32.
 cudaError_t launch_int8_mma_rate(const DeviceCtx& ctx, uint32_t iters, cudaStream_t stream);

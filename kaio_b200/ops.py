@@ -169,6 +169,16 @@ def matmul_int4_allgather(device, a, b_packed_shard, scales_shard, out_ptrs, out
           C.cast(arr, C.c_void_p), C.c_size_t(out_numel), world, rank, m, n_total, k, group_size)
 
 
+def allgather_cols(device, shard, out, m, n_total, world, nccl_comm):
+    """Extension: NCCL all-gather of ``[m, n_total/world]`` column shards into the row-major
+    ``[m, n_total]`` ``out`` on every rank, through the C ABI.  ``nccl_comm`` is the raw
+    ``ncclComm_t`` address of the ranks' communicator."""
+    if shard.dtype != out.dtype or shard.dtype not in (torch.float16, torch.float32):
+        raise TypeError("allgather_cols: shard and out must both be float16 or float32")
+    _call(device, "kaio_b200_allgather_cols", *_buf(shard, shard.dtype, "shard"), *_buf(out, out.dtype, "out"),
+          m, n_total, shard.element_size(), world, C.c_void_p(int(nccl_comm)))
+
+
 def matmul_int4_peer_partials(device, a, b_packed, scales, slot_ptrs, slot_numel, world, rank, scatter,
                               m, n, k, group_size=GROUP_SIZE):
     """Extension: this rank's K shard of a W4A16 GEMM; the f32 partial ``[m, n]`` is stored by the

@@ -81,3 +81,19 @@ def test_rejects_bad_arguments():
         ops.matmul_tc(d, a, a[:10], c, 16, 8, 16)
     with pytest.raises(InvalidConfig, match="C buffer too small"):
         ops.matmul_tc(d, a, a, c[:10], 16, 8, 16)
+
+
+def test_allgather_cols_single_rank_is_a_copy():
+    """kaio_b200_allgather_cols with one rank: the shard is the whole matrix (no NCCL call);
+    argument checks as for the other entry points."""
+    from kaio_b200 import InvalidConfig
+    m, n = 37, 256
+    shard = torch.randn(m * n, device="cuda").half()
+    out = torch.zeros(m * n, device="cuda", dtype=torch.float16)
+    ops.allgather_cols(device(), shard, out, m, n, 1, nccl_comm=1)  # the communicator is not used
+    assert ops.last_variant() == "allgather_cols_copy"
+    assert torch.equal(out, shard)
+    with pytest.raises(InvalidConfig, match="must split into"):
+        ops.allgather_cols(device(), shard, out, m, n, 3, nccl_comm=1)
+    with pytest.raises(InvalidConfig, match="out buffer too small"):
+        ops.allgather_cols(device(), shard, out[:100], m, n, 1, nccl_comm=1)

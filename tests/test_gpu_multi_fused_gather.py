@@ -53,6 +53,17 @@ def _worker(rank, world, port, shapes, ret):
                 got = out.float().cpu().numpy()
                 rel = np.max(np.abs(got - want) / np.maximum(np.abs(want), 1.0))
                 ok = ok and bool(np.all(np.isfinite(got))) and rel < 2e-2
+            # the NCCL form behind the C ABI (kaio_b200_allgather_cols) on the same shard: the
+            # gathered matrix must equal the fused one bit for bit
+            n_loc = n // world
+            shard = torch.empty(m * n_loc, device="cuda", dtype=torch.float16)
+            ops.matmul_int4(dev, torch.from_numpy(a).cuda(), w_loc, sc_loc, shard, m, n_loc, k, G)
+            full = torch.full((m * n,), float("nan"), device="cuda", dtype=torch.float16)
+            comm = dist.distributed_c10d._get_default_group()._get_backend(torch.device("cuda"))._comm_ptr()
+            ops.allgather_cols(dev, shard, full, m, n, world, comm)
+            torch.cuda.synchronize()
+            ok = ok and ops.last_variant() == "allgather_cols_nccl"
+            ok = ok and bool(torch.equal(full.view(torch.int16), out.reshape(-1).view(torch.int16)))
             assert ops.device_status(dev)[0] == 0
         ret[rank] = ok
     finally:
