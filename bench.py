@@ -428,6 +428,7 @@ def sharded_summary(world, ffn, chain):
     out["chain_m4096_ms"] = {k: r3(c4.get(v)) for k, v in (
         ("three_launches", "ms_three_launches"), ("nccl_all_reduce", "ms_with_all_reduce"),
         ("overlapped_all_reduce", "ms_overlapped_all_reduce"), ("fused_all_reduce", "ms_fused_all_reduce"),
+        ("fused_pipelined_all_reduce", "ms_fused_pipelined_all_reduce"),
         ("reduce_scatter", "ms_with_reduce_scatter"))}
     out["chain_m4096_best_all_reduce_ms"] = r3(c4.get("ms_best_all_reduce"))
     for mm in (16, 256):
@@ -990,21 +991,29 @@ def bench_ffn_chain(torch, dist, ops, dev, rank, world, peaks):
                 forms = [with_all_reduce, with_reduce_scatter if mm % world == 0 else with_all_reduce,
                          fused if fused_ok else with_all_reduce]
                 forms += [(lambda ch=ch: chain.run_overlapped(x, mm, chunks=ch)) for ch in chunk_sets]
+                fp_chunks = [[mm // 2, mm // 2], [mm // 4] * 4]
+                forms += [(lambda ch=ch: chain.run_fused_pipelined(x, mm, chunks=ch)) if fused_ok else with_all_reduce
+                          for ch in fp_chunks]
                 first = [_time_ms(torch, f, iters) for f in forms]
                 second = [_time_ms(torch, f, iters) for f in reversed(forms)][::-1]
                 ts += [min(a, b) for a, b in zip(first, second)]
             else:
                 ts += [ts[3]] * 3 + [_time_ms(torch, lambda ch=ch: chain.run_overlapped(x, mm, chunks=ch), iters)
-                                     for ch in chunk_sets]
-            t_gu, t_act, t_down, t_local, t_ar, t_rs, t_fused, t_ov0, t_ov1 = _max_over_ranks(torch, dist, world, ts)
+                                     for ch in chunk_sets] + [ts[3]] * 2
+                fp_chunks = [[mm], [mm]]
+            t_gu, t_act, t_down, t_local, t_ar, t_rs, t_fused, t_ov0, t_ov1, t_fp0, t_fp1 = \
+                _max_over_ranks(torch, dist, world, ts)
+            t_fp, fp_best = (t_fp0, fp_chunks[0]) if t_fp0 <= t_fp1 else (t_fp1, fp_chunks[1])
             t_ov, ov_chunks = (t_ov0, chunk_sets[0]) if t_ov0 <= t_ov1 else (t_ov1, chunk_sets[1])
-            best = min(t_ar, t_fused, t_ov) if world > 1 else t_local
+            best = min(t_ar, t_fused, t_ov, t_fp) if world > 1 else t_local
             act_bytes = 3 * mm * il * 2  # one rank's SiLU-gate pass: two f16 reads and one f16 write per element
             entry.update({
                 "ms_gate_up_gemm": t_gu, "ms_silu_gate": t_act, "ms_down_gemm": t_down, "ms_three_launches": t_local,
                 "ms_with_all_reduce": t_ar, "ms_with_reduce_scatter": t_rs,
                 "ms_fused_all_reduce": t_fused if fused_ok else None,
                 "ms_overlapped_all_reduce": t_ov, "overlap_chunks": ov_chunks,
+                "ms_fused_pipelined_all_reduce": t_fp if (fused_ok and world > 1) else None,
+                "fused_pipelined_chunks": fp_best,
                 "ms_best_all_reduce": best,
                 "fused_form": "-" if not fused_ok else ("one step" if mm <= chain.m_one else "two steps"),
                 "tflops": flops / best / 1e9, "weight_stream_gbs": wbytes / best / 1e6,
@@ -1023,7 +1032,10 @@ def bench_ffn_chain(torch, dist, ops, dev, rank, world, peaks):
                    "weight_stream_gbs = packed weights + scales of the three projections / that time; graph_ms_*: "
                    "the chain replayed from a CUDA graph over weight_sets_cycled distinct weight sets (> 2 x L2); "
                    "ms_fused_all_reduce: the down projection stores its partial tiles into the ranks' staging "
-                   "slots (peer memory), then a barrier and the slot sum; ms_overlapped_all_reduce: weights "
+                   "slots (peer memory), then a barrier and the slot sum; ms_fused_pipelined_all_reduce: the same "
+                   "with the whole chain in row chunks (gate|up weights dequantised once), each chunk's barrier + "
+                   "sum + store-back on a second stream behind the next chunk's launches; "
+                   "ms_overlapped_all_reduce: weights "
                    "dequantised once, rows in overlap_chunks, each chunk's NCCL all-reduce on a second stream "
                    "behind the next chunk's GEMMs")
     return res, {"checked": checked, "failed": failed}
@@ -1033,7 +1045,7 @@ def _check_chain(torch, dist, ops, np, chain, x, mm, hidden, inter, rank, world,
     """Every reduction form of the chain against the stage-wise CPU oracle on two rows (rank 0,
     unsharded weights; bar: 1e-2 of max(|want|, the row's rms)), and the fused form's bits across
     the ranks."""
-    outs = {"nccl": None, "fused": None, "overlap": None}
+    outs = {"nccl": None, "fused": None, "overlap": None, "fused_pipelined": None}
     part = chain.local(x, mm)
     dist.all_reduce(part, op=dist.ReduceOp.SUM)
     outs["nccl"] = part.clone()
@@ -1041,6 +1053,8 @@ def _check_chain(torch, dist, ops, np, chain, x, mm, hidden, inter, rank, world,
         outs["fused"] = chain.run_fused(x, mm).clone()
     if mm > 512:
         outs["overlap"] = chain.run_overlapped(x, mm).clone()
+        if fused_ok and mm > chain.m_one:
+            outs["fused_pipelined"] = chain.run_fused_pipelined(x, mm).clone()
     torch.cuda.synchronize()
     why = []
     ok = ops.device_status(chain.device)[0] == 0

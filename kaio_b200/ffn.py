@@ -157,6 +157,53 @@ class FfnInt4:
         self.out_h.barrier()  # every rank's summed block has landed in every rank's output
         return self.out_sym[: m * h].view(m, h)
 
+    def run_fused_pipelined(self, x: torch.Tensor, m: int, chunks: "list[int] | None" = None) -> torch.Tensor:
+        """The two-step fused all-reduce hidden behind the chain itself.  The rows are cut into
+        chunks; every chunk runs gate|up (f16 GEMM on weights dequantised once per call), SiLU-gate
+        and the down projection whose epilogue scatters the f32 partial tiles to the ranks that own
+        the column blocks (peer stores, as in :meth:`run_fused`); while chunk ``i+1`` computes on
+        the calling stream, chunk ``i``'s barrier, slot sum (fixed rank order: the same bits on
+        every rank and run), store-back to every rank and closing barrier run on a second stream.
+        The NVLink traffic of a chunk (2 x (P-1)/P of its f32 partial rows per rank) thus has a
+        whole chunk of compute to hide behind; only the last chunk's store-back is exposed.
+        Returns the complete f32 ``[m, hidden]`` (symmetric memory) on every rank."""
+        if m > self.max_m:
+            raise ValueError(f"m={m} exceeds max_m={self.max_m}")
+        ops, d, il, h, p = self.ops, self.device, self.i_loc, self.hidden, self.world
+        if chunks is None:
+            chunks = [m - m // 2, m // 2] if m >= 512 else [m]
+        if sum(chunks) != m or min(chunks) < 1:
+            raise ValueError(f"chunks {chunks} do not add up to m={m}")
+        if not hasattr(self, "side_stream"):
+            self.side_stream = torch.cuda.Stream(device=self.out.device)
+        if not hasattr(self, "w_gu_f16"):
+            self._init_overlap()
+        ops.dequantize_int4(d, self.w_gu, self.s_gu, self.w_gu_f16, h, 2 * il, GROUP)
+        main = torch.cuda.current_stream()
+        base, blk = 2 * self.one_elems, h // p
+        side_dev = type(d)(d.ordinal, self.side_stream)
+        r0 = 0
+        for rows in chunks:
+            xs = x.view(-1)[r0 * h:(r0 + rows) * h]
+            gu = self.gu[r0 * 2 * il:(r0 + rows) * 2 * il]
+            act = self.act[r0 * il:(r0 + rows) * il]
+            ops.matmul_tc_f16out(d, xs, self.w_gu_f16, gu, rows, 2 * il, h)
+            ops.silu_gate_f16(d, gu, gu[il:], act, rows, il, x_ld=2 * il, gate_ld=2 * il)
+            off = base + r0 * h  # this chunk's [P][rows][h/P] staging region (rows * h floats)
+            ops.matmul_int4_peer_partials(d, act, self.w_down, self.s_down, [q + off * 4 for q in self.stage_ptrs],
+                                          rows * h, p, self.rank, True, rows, h, il, GROUP)
+            ev = torch.cuda.Event()
+            ev.record(main)
+            with torch.cuda.stream(self.side_stream):
+                self.side_stream.wait_event(ev)
+                self.stage_h.barrier()  # column block r of every rank's partial rows has landed on rank r
+                ops.sum_partials_f32(side_dev, self.stage[off:off + rows * h], p, rows, blk,
+                                     [q + r0 * h * 4 for q in self.out_ptrs], rows * h, h, self.rank * blk)
+                self.out_h.barrier()  # every rank's summed block of these rows has landed everywhere
+            r0 += rows
+        main.wait_stream(self.side_stream)
+        return self.out_sym[: m * h].view(m, h)
+
     # ---- all-reduce overlapped with the GEMMs (large M)
 
     @staticmethod

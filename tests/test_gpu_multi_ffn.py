@@ -68,6 +68,19 @@ def _worker(rank, world, port, shapes, ret):
                 same = all(np.array_equal(runs[0], r) for r in runs[1:])
                 ok = ok and runs[0].shape == want.shape and bool(np.all(np.isfinite(runs[0]))) and rel < 1e-2 and same
                 dist.barrier()
+            # the pipelined two-step form: the chain in two row chunks (gate|up as an f16 GEMM on
+            # weights dequantised once), each chunk's barrier + slot sum + store-back on a second
+            # stream behind the next chunk's launches.  The same fixed summation order: two runs
+            # give the same bits, and the oracle's chain within the bar.
+            chain = ffn.FfnInt4(ops, dev, hidden, inter, *weights, world=world, rank=rank, max_m=max(m, 16),
+                                reduce="fused")
+            piped = [chain.run_fused_pipelined(x, m, chunks=[m - m // 2, m // 2]).clone() for _ in range(2)]
+            torch.cuda.synchronize()
+            got = piped[0].cpu().numpy()
+            rel = np.max(np.abs(got - want) / np.maximum(np.abs(want), 1.0))
+            ok = ok and bool(np.all(np.isfinite(got))) and rel < 1e-2
+            ok = ok and bool(torch.equal(piped[0].view(torch.int32), piped[1].view(torch.int32)))
+            dist.barrier()
             assert ops.device_status(dev)[0] == 0
         ret[rank] = ok
     finally:
