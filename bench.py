@@ -1003,6 +1003,28 @@ def bench_ffn_chain(torch, dist, ops, dev, rank, world, peaks):
                 fp_chunks = [[mm], [mm]]
             t_gu, t_act, t_down, t_local, t_ar, t_rs, t_fused, t_ov0, t_ov1, t_fp0, t_fp1 = \
                 _max_over_ranks(torch, dist, world, ts)
+            stage_ms = None
+            if world > 1 and fused_ok:
+                # where the fused form's time goes: events between its launches, 5 runs, the mean per
+                # stage, max over ranks (a stage that waits for the slowest rank shows as a long barrier)
+                labels, sums = [], {}
+                for it in range(2 + iters):
+                    evs = []
+
+                    def mark(label):
+                        ev = torch.cuda.Event(enable_timing=True)
+                        ev.record()
+                        evs.append((label, ev))
+                    mark("start")
+                    chain.run_fused(x, mm, mark=mark)
+                    torch.cuda.synchronize()
+                    if it >= 2:
+                        labels = [l for l, _ in evs[1:]]
+                        for (_, a), (l, b) in zip(evs[:-1], evs[1:]):
+                            sums[l] = sums.get(l, 0.0) + a.elapsed_time(b) / iters
+                vals = _max_over_ranks(torch, dist, world, [sums[l] for l in labels])
+                stage_ms = {l: round(v, 4) for l, v in zip(labels, vals)}
+                stage_ms["store_back"] = "multicast" if chain.out_mc else "peer stores"
             t_fp, fp_best = (t_fp0, fp_chunks[0]) if t_fp0 <= t_fp1 else (t_fp1, fp_chunks[1])
             t_ov, ov_chunks = (t_ov0, chunk_sets[0]) if t_ov0 <= t_ov1 else (t_ov1, chunk_sets[1])
             best = min(t_ar, t_fused, t_ov, t_fp) if world > 1 else t_local
@@ -1010,7 +1032,7 @@ def bench_ffn_chain(torch, dist, ops, dev, rank, world, peaks):
             entry.update({
                 "ms_gate_up_gemm": t_gu, "ms_silu_gate": t_act, "ms_down_gemm": t_down, "ms_three_launches": t_local,
                 "ms_with_all_reduce": t_ar, "ms_with_reduce_scatter": t_rs,
-                "ms_fused_all_reduce": t_fused if fused_ok else None,
+                "ms_fused_all_reduce": t_fused if fused_ok else None, "fused_stage_ms": stage_ms,
                 "ms_overlapped_all_reduce": t_ov, "overlap_chunks": ov_chunks,
                 "ms_fused_pipelined_all_reduce": t_fp if (fused_ok and world > 1) else None,
                 "fused_pipelined_chunks": fp_best,

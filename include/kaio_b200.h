@@ -285,6 +285,16 @@ int32_t kaio_b200_sum_partials_f32(const float* slots, size_t slots_len, uint32_
                                    uint32_t num_out, size_t out_len, uint32_t out_ld,
                                    uint32_t out_col0, void* stream);
 
+/* The same sum with ONE destination that is an address of an NVLink multicast object (every
+ * rank's output buffer bound to it, e.g. the multicast pointer of a torch symmetric-memory
+ * allocation): each vector leaves the GPU once as `multimem.st` and the switch delivers it to all
+ * ranks, 1/world of the egress of the form above.  The caller orders the ranks around it
+ * (a barrier before reading the outputs), as with peer stores. */
+int32_t kaio_b200_sum_partials_f32_multicast(const float* slots, size_t slots_len, uint32_t world,
+                                             uint32_t rows, uint32_t cols, void* multicast_out,
+                                             size_t out_len, uint32_t out_ld, uint32_t out_col0,
+                                             void* stream);
+
 /* ---- gated activation (between the up/gate and the down projection of an FFN block) ---- */
 
 /* The user kernel of examples/fused_silu_gate/src/main.rs:13-21:

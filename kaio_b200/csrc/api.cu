@@ -1374,12 +1374,11 @@ KAIO_API int32_t kaio_b200_matmul_int4_peer_partials(const kaio_f16* a, size_t a
                   op, "w4a16_tcgen05_peer_partials");
 }
 
-KAIO_API int32_t kaio_b200_sum_partials_f32(const float* slots, size_t slots_len, uint32_t world,
-                                            uint32_t rows, uint32_t cols, void* const* out_ptrs,
-                                            uint32_t num_out, size_t out_len, uint32_t out_ld,
-                                            uint32_t out_col0, void* stream)
+static int32_t run_sum_partials(const char* op, const float* slots, size_t slots_len, uint32_t world,
+                                uint32_t rows, uint32_t cols, void* const* out_ptrs, uint32_t num_out,
+                                size_t out_len, uint32_t out_ld, uint32_t out_col0, bool multicast,
+                                void* stream)
 {
-    const char* op = "sum_partials_f32";
     if (world == 0 || rows == 0 || cols == 0)
         return fail(KAIO_B200_ERR_INVALID_CONFIG, "%s dimensions must be non-zero", op);
     if (num_out == 0 || num_out > 8)
@@ -1412,8 +1411,27 @@ KAIO_API int32_t kaio_b200_sum_partials_f32(const float* slots, size_t slots_len
     if ((rc = get_ctx(&ctx)))
         return rc;
     return finish(launch_sum_partials(slots, world, rows, cols, outs, num_out, out_ld, out_col0,
-                                      static_cast<cudaStream_t>(stream)),
-                  op, "sum_partials_f32");
+                                      multicast, static_cast<cudaStream_t>(stream)),
+                  op, multicast ? "sum_partials_f32_multicast" : "sum_partials_f32");
+}
+
+KAIO_API int32_t kaio_b200_sum_partials_f32(const float* slots, size_t slots_len, uint32_t world,
+                                            uint32_t rows, uint32_t cols, void* const* out_ptrs,
+                                            uint32_t num_out, size_t out_len, uint32_t out_ld,
+                                            uint32_t out_col0, void* stream)
+{
+    return run_sum_partials("sum_partials_f32", slots, slots_len, world, rows, cols, out_ptrs, num_out,
+                            out_len, out_ld, out_col0, false, stream);
+}
+
+KAIO_API int32_t kaio_b200_sum_partials_f32_multicast(const float* slots, size_t slots_len,
+                                                      uint32_t world, uint32_t rows, uint32_t cols,
+                                                      void* multicast_out, size_t out_len,
+                                                      uint32_t out_ld, uint32_t out_col0, void* stream)
+{
+    void* outs[1] = {multicast_out};
+    return run_sum_partials("sum_partials_f32_multicast", slots, slots_len, world, rows, cols, outs, 1,
+                            out_len, out_ld, out_col0, true, stream);
 }
 
 // ---------------------------------------------------------------- allocation-free decode entry

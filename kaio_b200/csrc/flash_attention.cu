@@ -119,6 +119,18 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, ui
         : "memory");
 }
 
+#ifdef KAIO_TRACE
+// Development aid (never compiled into the shipped library): cycle stamps [cta][block < 20][8].
+__device__ unsigned long long* g_fa_trace = nullptr;
+#define FA_STAMP(j, slot)                                              \
+    do {                                                               \
+        if (trace_ptr && (j) < 20)                                     \
+            trace_ptr[(j) * 8 + (slot)] = clock64();                   \
+    } while (0)
+#else
+#define FA_STAMP(j, slot) do { } while (0)
+#endif
+
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
 {
@@ -140,6 +152,10 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
+#ifdef KAIO_TRACE
+    unsigned long long* const trace_ptr =
+        g_fa_trace ? g_fa_trace + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 160 : nullptr;
+#endif
 
     // heavy (late, causal) query blocks first
     const uint32_t num_qb = (p.seq_q + 2 * BQ - 1) / (2 * BQ);
@@ -263,6 +279,8 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
                         break;
                     }
                     tc_fence_after_sync();
+                    if (lane == 0)
+                        FA_STAMP(j, t == 0 ? 4 : 6);
                     // O_t += P_t V_j : 8 steps of 16 along kv; P in tensor memory (8 columns per
                     // step), V MN-major: 16 kv rows of 128 bytes per step, the two 64-column
                     // halves SUB_BYTES apart
@@ -298,6 +316,8 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
                     }
                     issue_qk(t, j + 1);
                 }
+                if (lane == 0)
+                    FA_STAMP(j, t == 0 ? 5 : 7);
             }
         }
     } else {
@@ -320,6 +340,8 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
                 break;
             }
             tc_fence_after_sync();
+            if (warp == 2 && lane == 0)
+                FA_STAMP(j, 0);
             const uint32_t col_base = j * BKV;
             // columns allowed for this row: j_abs < seq_k and (causal) j_abs <= row
             uint32_t col_lim = p.seq_k;
@@ -338,6 +360,8 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
             tmem_ld_32x32b_x32(s_tmem + 64, r2);
             tmem_ld_32x32b_x32(s_tmem + 96, r3);
             tmem_ld_wait();
+            if (warp == 2 && lane == 0)
+                FA_STAMP(j, 1);
             if (blk_mask) {
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
@@ -394,6 +418,8 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
             }
             // ---- pass 2: p = 2^(s * scale - m_ref), row sum, f16 pairs into tensor memory.  P
             // overwrites the first 64 columns of S, which are all in registers by now.
+            if (warp == 2 && lane == 0)
+                FA_STAMP(j, 2);
             float ls0 = 0.0f, ls1 = 0.0f, ls2 = 0.0f, ls3 = 0.0f;
             auto exp_chunk = [&](const uint32_t (&r)[32], uint32_t c) {
                 uint32_t pk[16];
@@ -420,6 +446,8 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
             exp_chunk(r3, 3);
             l_sum += (ls0 + ls1) + (ls2 + ls3);
             tmem_st_wait();
+            if (warp == 2 && lane == 0)
+                FA_STAMP(j, 3);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0)
@@ -487,6 +515,13 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
 }
 
 }  // namespace fa
+
+#ifdef KAIO_TRACE
+extern "C" __attribute__((visibility("default"))) int kaio_b200_debug_set_fa_trace(void* ptr)
+{
+    return (int)cudaMemcpyToSymbol(fa::g_fa_trace, &ptr, sizeof(ptr));
+}
+#endif
 
 bool flash_attention_ok(const AttnParams& p)
 {

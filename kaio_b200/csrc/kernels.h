@@ -135,7 +135,7 @@ cudaError_t launch_quantize_pack_s4(const float* w, uint32_t* packed, __half* sc
 // ---------------------------------------------------------------- sum of partial outputs
 cudaError_t launch_sum_partials(const float* slots, uint32_t world, uint32_t rows, uint32_t cols,
                                 float* const* outs, uint32_t num_out, uint64_t out_ld,
-                                uint32_t out_col0, cudaStream_t stream);
+                                uint32_t out_col0, bool multicast, cudaStream_t stream);
 
 // ---------------------------------------------------------------- gated activation
 cudaError_t launch_silu_gate_f32(const float* x, const float* gate, float* out, size_t n,

@@ -4,6 +4,9 @@
 // in ascending rank order (so every run and every rank produces the same bits) and stores the
 // sum to one or several destinations, which may again be peer memory (the all-gather half of a
 // two-step all-reduce).  A streaming pass: (world + copies) * 4 bytes per element.
+// With a multicast destination (an address of an NVLink multicast object that every rank's output
+// buffer is bound to) the sum leaves the GPU once, as multimem.st, and the switch delivers it to
+// every rank: (world + 1) * 4 bytes per element and 1/world of the egress.
 // KAIO is single-device; there is no reference counterpart.
 #include "kernels.h"
 
@@ -15,6 +18,8 @@ struct SumOut {
 
 // slots: [world][rows][cols] f32.  out_d[row * out_ld + out_col0 + c] = sum_s slots[s][row][c].
 // cols, out_ld, out_col0 are multiples of 4 and all bases 16-byte aligned.
+// MULTICAST: outs.ptrs[0] is a multicast address; one multimem.st per vector.
+template <bool MULTICAST>
 __global__ void __launch_bounds__(256)
 sum_partials_kernel(const float* __restrict__ slots, uint32_t world, uint32_t rows, uint32_t cols,
                     SumOut outs, uint32_t num_out, uint64_t out_ld, uint32_t out_col0)
@@ -36,14 +41,21 @@ sum_partials_kernel(const float* __restrict__ slots, uint32_t world, uint32_t ro
             acc.w += t.w;
         }
         const size_t o = (size_t)r * out_ld + out_col0 + (size_t)v * 4;
-        for (uint32_t d = 0; d < num_out; ++d)
-            *reinterpret_cast<float4*>(outs.ptrs[d] + o) = acc;
+        if constexpr (MULTICAST) {
+            asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                         :
+                         : "l"(outs.ptrs[0] + o), "f"(acc.x), "f"(acc.y), "f"(acc.z), "f"(acc.w)
+                         : "memory");
+        } else {
+            for (uint32_t d = 0; d < num_out; ++d)
+                *reinterpret_cast<float4*>(outs.ptrs[d] + o) = acc;
+        }
     }
 }
 
 cudaError_t launch_sum_partials(const float* slots, uint32_t world, uint32_t rows, uint32_t cols,
                                 float* const* outs, uint32_t num_out, uint64_t out_ld,
-                                uint32_t out_col0, cudaStream_t stream)
+                                uint32_t out_col0, bool multicast, cudaStream_t stream)
 {
     SumOut so = {};
     for (uint32_t d = 0; d < num_out && d < 8; ++d)
@@ -52,8 +64,12 @@ cudaError_t launch_sum_partials(const float* slots, uint32_t world, uint32_t row
     uint32_t gy = (148 * 8 + gx - 1) / gx;
     gy = gy > rows ? rows : gy;
     gy = gy < 1 ? 1 : (gy > 65535 ? 65535 : gy);
-    sum_partials_kernel<<<dim3(gx, gy, 1), 256, 0, stream>>>(slots, world, rows, cols, so, num_out,
-                                                             out_ld, out_col0);
+    if (multicast)
+        sum_partials_kernel<true><<<dim3(gx, gy, 1), 256, 0, stream>>>(slots, world, rows, cols, so,
+                                                                       1, out_ld, out_col0);
+    else
+        sum_partials_kernel<false><<<dim3(gx, gy, 1), 256, 0, stream>>>(slots, world, rows, cols, so,
+                                                                        num_out, out_ld, out_col0);
     return cudaGetLastError();
 }
 

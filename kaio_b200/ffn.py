@@ -25,6 +25,8 @@ The helpers at the top are layout logic and run on CPU tensors too.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -132,29 +134,59 @@ class FfnInt4:
         self.stage_ptrs = [int(p) for p in self.stage_h.buffer_ptrs]
         self.out_ptrs = [int(p) for p in self.out_h.buffer_ptrs]
         self.flip = 0
+        # Store-back of the two-step form through the NVLink multicast object torch binds the
+        # symmetric output buffers to, where the fabric offers one (0 otherwise): the summed block
+        # leaves this GPU once instead of once per peer.  KAIO_B200_MULTICAST=0 keeps peer stores.
+        self.out_mc = 0
+        if os.environ.get("KAIO_B200_MULTICAST", "1") != "0":
+            self.out_mc = int(getattr(self.out_h, "multicast_ptr", 0) or 0)
 
-    def run_fused(self, x: torch.Tensor, m: int) -> torch.Tensor:
+    def _store_back(self, dev, off: int, rows: int, r0: int = 0):
+        """Second step of the two-step form for ``rows`` rows starting at ``r0``: add this rank's
+        column block over the P staging slots at ``stage[off:]`` and deliver it to every rank."""
+        h, p = self.hidden, self.world
+        blk = h // p
+        slots = self.stage[off:off + rows * h]
+        if self.out_mc:
+            self.ops.sum_partials_f32_multicast(dev, slots, p, rows, blk, self.out_mc + r0 * h * 4, rows * h, h,
+                                                self.rank * blk)
+        else:
+            self.ops.sum_partials_f32(dev, slots, p, rows, blk, [q + r0 * h * 4 for q in self.out_ptrs], rows * h, h,
+                                      self.rank * blk)
+
+    def run_fused(self, x: torch.Tensor, m: int, mark=None) -> torch.Tensor:
         """gate|up, SiLU-gate, then the down projection whose epilogue stores into the ranks' staging
-        slots, the barrier, and the slot sum.  Returns the complete f32 ``[m, hidden]``."""
+        slots, the barrier, and the slot sum.  Returns the complete f32 ``[m, hidden]``.
+        ``mark(label)``, if given, is called after every launch (stage timing with events)."""
         if m > self.max_m:
             raise ValueError(f"m={m} exceeds max_m={self.max_m}")
+        mark = mark or (lambda label: None)
         ops, d, il, h, p = self.ops, self.device, self.i_loc, self.hidden, self.world
         ops.matmul_int4(d, x, self.w_gu, self.s_gu, self.gu, m, 2 * il, h, GROUP)
+        mark("gate_up")
         ops.silu_gate_f16(d, self.gu, self.gu.view(-1)[il:], self.act, m, il, x_ld=2 * il, gate_ld=2 * il)
+        mark("silu_gate")
         if m <= self.m_one:
             off = self.flip * self.one_elems
             self.flip ^= 1
             ops.matmul_int4_peer_partials(d, self.act, self.w_down, self.s_down, [q + off * 4 for q in self.stage_ptrs],
                                           p * m * h, p, self.rank, False, m, h, il, GROUP)
+            mark("down_peer_stores")
             self.stage_h.barrier()  # every rank's partial has landed in every rank's slots
+            mark("barrier")
             ops.sum_partials_f32(d, self.stage[off:off + p * m * h], p, m, h, [self.out.data_ptr()], m * h, h, 0)
+            mark("slot_sum")
             return self.out[: m * h].view(m, h)
-        off, blk = 2 * self.one_elems, h // p
+        off = 2 * self.one_elems
         ops.matmul_int4_peer_partials(d, self.act, self.w_down, self.s_down, [q + off * 4 for q in self.stage_ptrs],
                                       m * h, p, self.rank, True, m, h, il, GROUP)
+        mark("down_peer_stores")
         self.stage_h.barrier()  # column block r of every rank's partial has landed on rank r
-        ops.sum_partials_f32(d, self.stage[off:off + m * h], p, m, blk, self.out_ptrs, m * h, h, self.rank * blk)
+        mark("barrier")
+        self._store_back(d, off, m)
+        mark("slot_sum_store_back")
         self.out_h.barrier()  # every rank's summed block has landed in every rank's output
+        mark("closing_barrier")
         return self.out_sym[: m * h].view(m, h)
 
     def run_fused_pipelined(self, x: torch.Tensor, m: int, chunks: "list[int] | None" = None) -> torch.Tensor:
@@ -197,8 +229,7 @@ class FfnInt4:
             with torch.cuda.stream(self.side_stream):
                 self.side_stream.wait_event(ev)
                 self.stage_h.barrier()  # column block r of every rank's partial rows has landed on rank r
-                ops.sum_partials_f32(side_dev, self.stage[off:off + rows * h], p, rows, blk,
-                                     [q + r0 * h * 4 for q in self.out_ptrs], rows * h, h, self.rank * blk)
+                self._store_back(side_dev, off, rows, r0)
                 self.out_h.barrier()  # every rank's summed block of these rows has landed everywhere
             r0 += rows
         main.wait_stream(self.side_stream)

@@ -201,6 +201,14 @@ def sum_partials_f32(device, slots, world, rows, cols, out_ptrs, out_numel, out_
           C.cast(arr, C.c_void_p), len(out_ptrs), C.c_size_t(out_numel), out_ld, out_col0)
 
 
+def sum_partials_f32_multicast(device, slots, world, rows, cols, multicast_out, out_numel, out_ld, out_col0=0):
+    """Extension: the same sum stored once through ``multicast_out``, an address of an NVLink
+    multicast object every rank's output buffer is bound to (``multimem.st``; the switch delivers
+    the vector to all ranks)."""
+    _call(device, "kaio_b200_sum_partials_f32_multicast", *_buf(slots, torch.float32, "slots"), world, rows, cols,
+          C.c_void_p(int(multicast_out)), C.c_size_t(out_numel), out_ld, out_col0)
+
+
 # ------------------------------------------------------------------ fused QKV
 
 def qkv_project_int8(device, x, w_q, w_k, w_v, scale_q, scale_k, scale_v, q_out, k_out, v_out, m, n, k):

@@ -39,6 +39,12 @@ def _worker(rank, world, port, shapes, ret):
             want = ffn_oracle(orc, case, hidden, inter, m)
             weights = [case[n] for n in ("w_gate", "s_gate", "w_up", "s_up", "w_down", "s_down")]
             x = case["x"].cuda()
+            # a second input for the back-to-back runs below (the same weights)
+            case2 = dict(case)
+            case2["x"] = torch.from_numpy(
+                np.random.default_rng(m).standard_normal(case["x"].numel()).astype(np.float16)).reshape(case["x"].shape)
+            want2 = ffn_oracle(orc, case2, hidden, inter, m)
+            x2 = case2["x"].cuda()
             for reduce in ("all", "scatter", "overlap"):
                 chain = ffn.FfnInt4(ops, dev, hidden, inter, *weights, world=world, rank=rank, max_m=max(m, 16),
                                     reduce=reduce)
@@ -67,6 +73,23 @@ def _worker(rank, world, port, shapes, ret):
                 rel = np.max(np.abs(runs[0] - want) / np.maximum(np.abs(want), 1.0))
                 same = all(np.array_equal(runs[0], r) for r in runs[1:])
                 ok = ok and runs[0].shape == want.shape and bool(np.all(np.isfinite(runs[0]))) and rel < 1e-2 and same
+                dist.barrier()
+                # six runs enqueued back to back with no host synchronisation in between, on two
+                # alternating inputs: the staging buffers are reused while other ranks may still be
+                # reading the previous run's slots.  Every result is copied aside on the stream; one
+                # synchronise at the end; then each is checked against the oracle and, through an
+                # all-gather of the raw bits, for equality across the ranks.
+                kept = [chain.run(x if (i & 1) == 0 else x2, m).clone() for i in range(6)]
+                torch.cuda.synchronize()
+                for i, got_d in enumerate(kept):
+                    ref = want if (i & 1) == 0 else want2
+                    got = got_d.cpu().numpy()
+                    rel = np.max(np.abs(got - ref) / np.maximum(np.abs(ref), 1.0))
+                    ok = ok and bool(np.all(np.isfinite(got))) and rel < 1e-2
+                    ok = ok and bool(torch.equal(got_d.view(torch.int32), kept[i & 1].view(torch.int32)))
+                    bits = [torch.empty_like(got_d, dtype=torch.int32) for _ in range(world)]
+                    dist.all_gather(bits, got_d.view(torch.int32).contiguous())
+                    ok = ok and all(bool(torch.equal(bits[0], b)) for b in bits[1:])
                 dist.barrier()
             # the pipelined two-step form: the chain in two row chunks (gate|up as an f16 GEMM on
             # weights dequantised once), each chunk's barrier + slot sum + store-back on a second
