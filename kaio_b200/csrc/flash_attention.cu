@@ -17,13 +17,21 @@
 //                                   the first 64 columns of S_t), V from shared memory read
 //                                   MN-major (d contiguous), O_t in tensor memory
 //              issue order per block: PV_0(j), QK_0(j+1), PV_1(j), QK_1(j+1) -- while one tile's
-//              softmax runs, the tensor pipe works on the other tile.
+//              softmax runs, the tensor pipe works on the other tile, and serving the tiles in
+//              turn keeps them half a period apart (with one issuer per tile the two tiles
+//              fell into step: both in softmax, then both queueing for the tensor pipe).  P is
+//              handed over in two halves (kv 0-63, 64-127): the first four P V steps run while
+//              the softmax warps still exponentiate the second half.
 //   warps 2-5  softmax of tile 0, warps 6-9 softmax of tile 1: thread = query row.  tcgen05.ld of
-//              the score row, block max (four independent chains), running max with lazy rescale
-//              (O and the row sum are rescaled only when the max grows by more than 2^13),
-//              ex2(s * log2(e)/sqrt(d) - max), row sum, P packed to f16 and stored to tensor
-//              memory; at the end O / sum -> global.  Two warps per scheduler hide each other's
-//              dependent chains; a single softmax warp-group left the tensor pipe 27 % busy.
+//              the score row, block max (four independent chains), running reference with lazy
+//              rescale: P = 2^(s - ref) may grow to 2^15 before O and the row sum are rescaled,
+//              and a new reference is set 2^8 above the max seen, so a row's max can rise by
+//              2^23 before the next rescale; when any row of a warp must rescale, every row of
+//              the warp moves its reference up to its own running max (the pass over O costs
+//              the same for one row as for 32), which makes such passes rare.  ex2(s * log2(e)/sqrt(d) - ref), row sum, P packed to f16 and stored to
+//              tensor memory; at the end O / sum -> global.  Two warps per scheduler hide each
+//              other's dependent chains; a single softmax warp-group left the tensor pipe 27 %
+//              busy.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -47,6 +55,11 @@ constexpr uint32_t TMEM_O = 256;    // per tile: 128 columns (f32 output accumul
 
 constexpr uint32_t IDESC_QK = make_idesc(1, 0, 0, /*a K-major*/ 0, /*b K-major*/ 0, BQ, BKV);
 constexpr uint32_t IDESC_PV = make_idesc(1, 0, 0, /*a K-major*/ 0, /*b MN-major*/ 1, BQ, D);
+// lazy rescale: P = 2^(s - ref) <= 2^RESCALE_WINDOW (f16 holds 2^15); a new reference is
+// REF_MARGIN above the max seen so far (scores 2^-6 below the max still keep all f16 bits, and
+// what lies below is rounded to within 2^-17 of the largest term)
+constexpr float RESCALE_WINDOW = 15.0f;
+constexpr float REF_MARGIN = 8.0f;
 
 enum : uint32_t {
     SITE_Q_FULL = 1, SITE_KV_FULL = 2, SITE_KV_EMPTY = 3, SITE_S_FULL = 4, SITE_P_FULL = 5,
@@ -72,6 +85,24 @@ __device__ __forceinline__ float ex2_approx(float x)
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+
+// 2^x on the FMA pipe, for the share of the exponentials taken off the special-function unit
+// (16 results per clock per SM there; one of every four elements goes this way).  Round-to-nearest
+// split x = n + f through the 1.5 * 2^23 constant, degree-4 minimax polynomial for 2^f on
+// [-0.5, 0.5] (relative error 2.7e-6, far below the f16 rounding of P), n added to the exponent
+// field.  x <= 16 here; anything below -125 (masked scores are -inf) gives ~2^-125.
+__device__ __forceinline__ float ex2_poly(float x)
+{
+    x = fmaxf(x, -125.0f);
+    const float t = x + 12582912.0f;
+    const float f = x - (t - 12582912.0f);
+    float q = 9.574016556e-03f;
+    q = fmaf(q, f, 5.591819063e-02f);
+    q = fmaf(q, f, 2.402464896e-01f);
+    q = fmaf(q, f, 6.931217313e-01f);
+    q = fmaf(q, f, 9.999992847e-01f);
+    return __int_as_float(__float_as_int(q) + (__float_as_int(t) << 23));
 }
 
 __device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_t (&r)[16])
@@ -131,6 +162,7 @@ __device__ unsigned long long* g_fa_trace = nullptr;
 #define FA_STAMP(j, slot) do { } while (0)
 #endif
 
+// Three warps share a scheduler's 16 K registers: at most 168 per thread.
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
 {
@@ -145,9 +177,10 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
     auto kv_full = [&](uint32_t s) { return bar_base + 8u * (1 + s); };
     auto kv_empty = [&](uint32_t s) { return bar_base + 8u * (3 + s); };
     auto s_full = [&](uint32_t b) { return bar_base + 8u * (5 + b); };
-    auto p_full = [&](uint32_t b) { return bar_base + 8u * (7 + b); };
-    auto pv_done = [&](uint32_t b) { return bar_base + 8u * (9 + b); };
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 11);
+    auto p_lo = [&](uint32_t b) { return bar_base + 8u * (7 + b); };   // P of kv 0-63 stored
+    auto p_hi = [&](uint32_t b) { return bar_base + 8u * (9 + b); };   // P of kv 64-127 stored
+    auto pv_done = [&](uint32_t b) { return bar_base + 8u * (11 + b); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 13);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const uint32_t warp = threadIdx.x >> 5;
@@ -185,7 +218,8 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
         }
         for (uint32_t i = 0; i < 2; ++i) {
             mbar_init(s_full(i), 1);
-            mbar_init(p_full(i), 4);  // one arrive per softmax warp of the tile
+            mbar_init(p_lo(i), 4);  // one arrive per softmax warp of the tile
+            mbar_init(p_hi(i), 4);
             mbar_init(pv_done(i), 1);
         }
         *abort_flag = 0;
@@ -256,6 +290,27 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
             }
             __syncwarp();
         };
+        // O_t += P_t V_j, steps [k0, k0 + 4) of 16 along kv; P in tensor memory (8 columns per
+        // step), V MN-major: 16 kv rows of 128 bytes per step, the two 64-column halves
+        // SUB_BYTES apart
+        auto issue_pv = [&](uint32_t t, uint32_t j, uint32_t k0, bool last, bool last_reader) {
+            const uint32_t v_smem = kv_smem + (j & 1u) * STAGE_BYTES + KV_TILE_BYTES;
+            const uint32_t p_tmem = tmem_base + TMEM_S + t * BKV;
+            if (elect_one()) {
+#pragma unroll
+                for (uint32_t kk = k0; kk < k0 + BKV / 32; ++kk) {
+                    umma_f16_ts(tmem_base + TMEM_O + t * D, p_tmem + kk * 8,
+                                make_smem_desc_sw128(v_smem + kk * 2048, SUB_BYTES, 1024), IDESC_PV,
+                                (j | kk) != 0 ? 1u : 0u);
+                }
+                if (last) {
+                    umma_commit(pv_done(t));
+                    if (last_reader)
+                        umma_commit(kv_empty(j & 1u));  // K_j and V_j have been consumed
+                }
+            }
+            __syncwarp();
+        };
         bool ok = mbar_wait_bounded(q_full, 0, abort_flag, p.status, SITE_Q_FULL, KERNEL_FLASH_ATTN);
         if (ok && num_kv > 0) {
             ok = mbar_wait_bounded(kv_full(0), 0, abort_flag, p.status, SITE_KV_FULL,
@@ -273,32 +328,27 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
 #pragma unroll
             for (uint32_t t = 0; t < 2; ++t) {
                 if (j < nkv[t]) {
-                    if (!mbar_wait_bounded(p_full(t), j & 1u, abort_flag, p.status, SITE_P_FULL,
+                    // steps 0-3 go as soon as the first half of P is in
+                    if (lane == 0 && t == 0)
+                        FA_STAMP(j, 4);
+                    if (!mbar_wait_bounded(p_lo(t), j & 1u, abort_flag, p.status, SITE_P_FULL,
                                            KERNEL_FLASH_ATTN)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after_sync();
-                    if (lane == 0)
-                        FA_STAMP(j, t == 0 ? 4 : 6);
-                    // O_t += P_t V_j : 8 steps of 16 along kv; P in tensor memory (8 columns per
-                    // step), V MN-major: 16 kv rows of 128 bytes per step, the two 64-column
-                    // halves SUB_BYTES apart
-                    const uint32_t v_smem = kv_smem + (j & 1u) * STAGE_BYTES + KV_TILE_BYTES;
-                    const uint32_t p_tmem = tmem_base + TMEM_S + t * BKV;
-                    const bool last_reader = (t == 1) || (j >= nkv[1]);
-                    if (elect_one()) {
-#pragma unroll
-                        for (uint32_t kk = 0; kk < BKV / 16; ++kk) {
-                            umma_f16_ts(tmem_base + TMEM_O + t * D, p_tmem + kk * 8,
-                                        make_smem_desc_sw128(v_smem + kk * 2048, SUB_BYTES, 1024),
-                                        IDESC_PV, (j | kk) != 0 ? 1u : 0u);
-                        }
-                        umma_commit(pv_done(t));
-                        if (last_reader)
-                            umma_commit(kv_empty(j & 1u));  // K_j and V_j have been consumed
+                    if (lane == 0 && t == 0)
+                        FA_STAMP(j, 5);
+                    issue_pv(t, j, 0, false, false);
+                    if (!mbar_wait_bounded(p_hi(t), j & 1u, abort_flag, p.status, SITE_P_FULL,
+                                           KERNEL_FLASH_ATTN)) {
+                        ok = false;
+                        break;
                     }
-                    __syncwarp();
+                    tc_fence_after_sync();
+                    if (lane == 0 && t == 0)
+                        FA_STAMP(j, 6);
+                    issue_pv(t, j, BKV / 32, true, (t == 1) || (j >= nkv[1]));
                 }
                 // scores of the next block for this tile, issued behind its P V so the other
                 // tile's softmax overlaps them (in-order execution on the tensor pipe makes the
@@ -316,8 +366,8 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
                     }
                     issue_qk(t, j + 1);
                 }
-                if (lane == 0)
-                    FA_STAMP(j, t == 0 ? 5 : 7);
+                if (lane == 0 && t == 0)
+                    FA_STAMP(j, 7);
             }
         }
     } else {
@@ -327,10 +377,11 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
         const uint32_t lane_sel = (quarter * 32u) << 16;
         const uint32_t row_local = quarter * 32 + lane;
         const uint32_t row = q0 + t * BQ + row_local;  // query index inside this (batch, head)
-        const uint32_t my_kv = nkv[t];
+        const uint32_t my_kv = t ? nkv[1] : nkv[0];
         const uint32_t s_tmem = tmem_base + TMEM_S + t * BKV + lane_sel;
         const uint32_t o_tmem = tmem_base + TMEM_O + t * D + lane_sel;
-        float m_ref = 0.0f;  // max used in the exponent (log2 units)
+        float m_ref = 0.0f;  // reference subtracted in the exponent (log2 units)
+        float m_run = -INFINITY;  // running max of the scaled scores
         float l_sum = 0.0f;
         bool ok = true;
         for (uint32_t j = 0; j < my_kv; ++j) {
@@ -340,8 +391,6 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
                 break;
             }
             tc_fence_after_sync();
-            if (warp == 2 && lane == 0)
-                FA_STAMP(j, 0);
             const uint32_t col_base = j * BKV;
             // columns allowed for this row: j_abs < seq_k and (causal) j_abs <= row
             uint32_t col_lim = p.seq_k;
@@ -360,8 +409,6 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
             tmem_ld_32x32b_x32(s_tmem + 64, r2);
             tmem_ld_32x32b_x32(s_tmem + 96, r3);
             tmem_ld_wait();
-            if (warp == 2 && lane == 0)
-                FA_STAMP(j, 1);
             if (blk_mask) {
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
@@ -385,41 +432,26 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
                 mx3 = fmaxf(mx3, __uint_as_float(r3[i]));
             }
             const float m_blk = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
-            // ---- lazy rescale: keep the old reference unless the max grew by more than 2^13
-            // (P = 2^(s - m_ref) then stays below 2^13 = 8192, well inside f16, and keeps the
-            // f16 relative precision; the row sum and O are f32)
+            // ---- lazy rescale: keep the old reference while P = 2^(s - m_ref) stays inside f16
+            // (the row sum and O are f32)
             float alpha = 1.0f;
+            bool rescale = false;
             if (j == 0) {
-                m_ref = (m_blk == -INFINITY) ? 0.0f : m_blk;
-            } else if (m_blk > m_ref + 13.0f) {
-                alpha = ex2_approx(m_ref - m_blk);
-                m_ref = m_blk;
-            }
-            if (__any_sync(0xffffffffu, alpha != 1.0f)) {
-                // O_t was last written by the P V MMAs of block j-1
-                if (!mbar_wait_bounded(pv_done(t), (j - 1) & 1u, abort_flag, p.status, SITE_PV_DONE,
-                                       KERNEL_FLASH_ATTN)) {
-                    ok = false;
-                    break;
+                m_run = m_blk;
+                m_ref = (m_blk == -INFINITY) ? 0.0f : m_blk + REF_MARGIN;
+            } else {
+                m_run = fmaxf(m_run, m_blk);
+                rescale = __any_sync(0xffffffffu, m_blk > m_ref + RESCALE_WINDOW);
+                if (rescale && m_run + REF_MARGIN > m_ref) {
+                    // the pass over O is made for the whole warp: every row uses it to move its
+                    // reference up to its own running max
+                    alpha = ex2_approx(m_ref - (m_run + REF_MARGIN));
+                    m_ref = m_run + REF_MARGIN;
+                    l_sum *= alpha;
                 }
-                tc_fence_after_sync();
-                l_sum *= alpha;
-#pragma unroll 1
-                for (uint32_t c = 0; c < D / 32; ++c) {
-                    uint32_t r[32];
-                    tmem_ld_32x32b_x32(o_tmem + c * 32, r);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                    tmem_st_32x32b_x32(o_tmem + c * 32, r);
-                }
-                tmem_st_wait();
             }
             // ---- pass 2: p = 2^(s * scale - m_ref), row sum, f16 pairs into tensor memory.  P
             // overwrites the first 64 columns of S, which are all in registers by now.
-            if (warp == 2 && lane == 0)
-                FA_STAMP(j, 2);
             float ls0 = 0.0f, ls1 = 0.0f, ls2 = 0.0f, ls3 = 0.0f;
             auto exp_chunk = [&](const uint32_t (&r)[32], uint32_t c) {
                 uint32_t pk[16];
@@ -428,7 +460,7 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
                     const float p0 = ex2_approx(fmaf(__uint_as_float(r[i]), p.scale_log2, -m_ref));
                     const float p1 = ex2_approx(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -m_ref));
                     const float p2 = ex2_approx(fmaf(__uint_as_float(r[i + 2]), p.scale_log2, -m_ref));
-                    const float p3 = ex2_approx(fmaf(__uint_as_float(r[i + 3]), p.scale_log2, -m_ref));
+                    const float p3 = ex2_poly(fmaf(__uint_as_float(r[i + 3]), p.scale_log2, -m_ref));
                     ls0 += p0;
                     ls1 += p1;
                     ls2 += p2;
@@ -442,16 +474,78 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
             };
             exp_chunk(r0, 0);
             exp_chunk(r1, 1);
+            if (!rescale) {
+                // first half of P handed over: its P V steps run while the second half is computed
+                tmem_st_wait();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(p_lo(t));
+                    if (warp == 2)
+                        FA_STAMP(j, 0);
+                    if (warp == 6)
+                        FA_STAMP(j, 2);
+                }
+                // keep the second half's arithmetic behind the hand-over: without a dependence
+                // the compiler moves it in front of the store wait and the arrive comes late
+#pragma unroll
+                for (int i = 0; i < 32; i += 16) {
+                    asm volatile("" : "+r"(r2[i]), "+r"(r2[i + 1]), "+r"(r2[i + 2]), "+r"(r2[i + 3]),
+                                      "+r"(r2[i + 4]), "+r"(r2[i + 5]), "+r"(r2[i + 6]), "+r"(r2[i + 7]),
+                                      "+r"(r2[i + 8]), "+r"(r2[i + 9]), "+r"(r2[i + 10]), "+r"(r2[i + 11]),
+                                      "+r"(r2[i + 12]), "+r"(r2[i + 13]), "+r"(r2[i + 14]), "+r"(r2[i + 15])
+                                 :: "memory");
+                    asm volatile("" : "+r"(r3[i]), "+r"(r3[i + 1]), "+r"(r3[i + 2]), "+r"(r3[i + 3]),
+                                      "+r"(r3[i + 4]), "+r"(r3[i + 5]), "+r"(r3[i + 6]), "+r"(r3[i + 7]),
+                                      "+r"(r3[i + 8]), "+r"(r3[i + 9]), "+r"(r3[i + 10]), "+r"(r3[i + 11]),
+                                      "+r"(r3[i + 12]), "+r"(r3[i + 13]), "+r"(r3[i + 14]), "+r"(r3[i + 15])
+                                 :: "memory");
+                }
+            }
             exp_chunk(r2, 2);
             exp_chunk(r3, 3);
             l_sum += (ls0 + ls1) + (ls2 + ls3);
             tmem_st_wait();
-            if (warp == 2 && lane == 0)
-                FA_STAMP(j, 3);
+            if (rescale) {
+                // Some row of this warp moved its reference: O_t (last written by the P V of block
+                // j-1, complete since S_j was issued behind them) is scaled before any P V of this
+                // block may start, so this block hands both halves over at the end.  The score
+                // registers are free by now: four loads in flight.
+                if (!mbar_wait_bounded(pv_done(t), (j - 1) & 1u, abort_flag, p.status, SITE_PV_DONE,
+                                       KERNEL_FLASH_ATTN)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                tmem_ld_32x32b_x32(o_tmem + 0, r0);
+                tmem_ld_32x32b_x32(o_tmem + 32, r1);
+                tmem_ld_32x32b_x32(o_tmem + 64, r2);
+                tmem_ld_32x32b_x32(o_tmem + 96, r3);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    r0[i] = __float_as_uint(__uint_as_float(r0[i]) * alpha);
+                    r1[i] = __float_as_uint(__uint_as_float(r1[i]) * alpha);
+                    r2[i] = __float_as_uint(__uint_as_float(r2[i]) * alpha);
+                    r3[i] = __float_as_uint(__uint_as_float(r3[i]) * alpha);
+                }
+                tmem_st_32x32b_x32(o_tmem + 0, r0);
+                tmem_st_32x32b_x32(o_tmem + 32, r1);
+                tmem_st_32x32b_x32(o_tmem + 64, r2);
+                tmem_st_32x32b_x32(o_tmem + 96, r3);
+                tmem_st_wait();
+            }
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0)
-                mbar_arrive(p_full(t));
+            if (lane == 0) {
+                if (rescale)
+                    mbar_arrive(p_lo(t));
+                mbar_arrive(p_hi(t));
+                if (warp == 2)
+                    FA_STAMP(j, 1);
+                if (warp == 6)
+                    FA_STAMP(j, 3);
+            }
         }
         // ---- epilogue: O / l -> global
         if (ok && my_kv > 0)
