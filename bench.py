@@ -429,7 +429,7 @@ def sharded_summary(world, ffn, chain):
         ("three_launches", "ms_three_launches"), ("nccl_all_reduce", "ms_with_all_reduce"),
         ("overlapped_all_reduce", "ms_overlapped_all_reduce"), ("fused_all_reduce", "ms_fused_all_reduce"),
         ("fused_pipelined_all_reduce", "ms_fused_pipelined_all_reduce"),
-        ("reduce_scatter", "ms_with_reduce_scatter"))}
+        ("switch_all_reduce", "ms_switch_all_reduce"), ("reduce_scatter", "ms_with_reduce_scatter"))}
     out["chain_m4096_best_all_reduce_ms"] = r3(c4.get("ms_best_all_reduce"))
     for mm in (16, 256):
         cm = chain.get(f"m{mm}", {})
@@ -907,6 +907,16 @@ def bench_ffn_chain(torch, dist, ops, dev, rank, world, peaks):
         flag = torch.tensor([1 if fused_ok else 0], device="cuda")
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)  # every rank or none
         fused_ok = bool(flag.item())
+    switch_ok = fused_ok
+    if switch_ok:
+        try:  # the in-switch all-reduce needs NVLink multicast addresses for the symmetric buffers
+            chain._init_switch()
+        except Exception as exc:  # noqa: BLE001
+            switch_ok = False
+            print(f"in-switch all-reduce unavailable on rank {rank}: {exc!r}", file=sys.stderr, flush=True)
+        flag = torch.tensor([1 if switch_ok else 0], device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        switch_ok = bool(flag.item())
     del weights
     torch.cuda.empty_cache()
     il = chain.i_loc
@@ -994,15 +1004,20 @@ def bench_ffn_chain(torch, dist, ops, dev, rank, world, peaks):
                 fp_chunks = [[mm // 2, mm // 2], [mm // 4] * 4]
                 forms += [(lambda ch=ch: chain.run_fused_pipelined(x, mm, chunks=ch)) if fused_ok else with_all_reduce
                           for ch in fp_chunks]
+                sw_chunks = [[mm], [mm // 2, mm // 2]]
+                forms += [(lambda ch=ch: chain.run_switch(x, mm, chunks=ch)) if switch_ok else with_all_reduce
+                          for ch in sw_chunks]
                 first = [_time_ms(torch, f, iters) for f in forms]
                 second = [_time_ms(torch, f, iters) for f in reversed(forms)][::-1]
                 ts += [min(a, b) for a, b in zip(first, second)]
             else:
                 ts += [ts[3]] * 3 + [_time_ms(torch, lambda ch=ch: chain.run_overlapped(x, mm, chunks=ch), iters)
-                                     for ch in chunk_sets] + [ts[3]] * 2
+                                     for ch in chunk_sets] + [ts[3]] * 4
                 fp_chunks = [[mm], [mm]]
-            t_gu, t_act, t_down, t_local, t_ar, t_rs, t_fused, t_ov0, t_ov1, t_fp0, t_fp1 = \
+                sw_chunks = [[mm], [mm]]
+            t_gu, t_act, t_down, t_local, t_ar, t_rs, t_fused, t_ov0, t_ov1, t_fp0, t_fp1, t_sw0, t_sw1 = \
                 _max_over_ranks(torch, dist, world, ts)
+            t_sw, sw_best = (t_sw0, sw_chunks[0]) if t_sw0 <= t_sw1 else (t_sw1, sw_chunks[1])
             stage_ms = None
             if world > 1 and fused_ok:
                 # where the fused form's time goes: events between its launches, 5 runs, the mean per
@@ -1025,9 +1040,28 @@ def bench_ffn_chain(torch, dist, ops, dev, rank, world, peaks):
                 vals = _max_over_ranks(torch, dist, world, [sums[l] for l in labels])
                 stage_ms = {l: round(v, 4) for l, v in zip(labels, vals)}
                 stage_ms["store_back"] = "multicast" if chain.out_mc else "peer stores"
+            switch_stage_ms = None
+            if world > 1 and switch_ok:
+                labels, sums = [], {}
+                for it in range(2 + iters):
+                    evs = []
+
+                    def mark(label):
+                        ev = torch.cuda.Event(enable_timing=True)
+                        ev.record()
+                        evs.append((label, ev))
+                    mark("start")
+                    chain.run_switch(x, mm, mark=mark)
+                    torch.cuda.synchronize()
+                    if it >= 2:
+                        labels = [l for l, _ in evs[1:]]
+                        for (_, a), (l, b) in zip(evs[:-1], evs[1:]):
+                            sums[l] = sums.get(l, 0.0) + a.elapsed_time(b) / iters
+                vals = _max_over_ranks(torch, dist, world, [sums[l] for l in labels])
+                switch_stage_ms = {l: round(v, 4) for l, v in zip(labels, vals)}
             t_fp, fp_best = (t_fp0, fp_chunks[0]) if t_fp0 <= t_fp1 else (t_fp1, fp_chunks[1])
             t_ov, ov_chunks = (t_ov0, chunk_sets[0]) if t_ov0 <= t_ov1 else (t_ov1, chunk_sets[1])
-            best = min(t_ar, t_fused, t_ov, t_fp) if world > 1 else t_local
+            best = min(t_ar, t_fused, t_ov, t_fp, t_sw) if world > 1 else t_local
             act_bytes = 3 * mm * il * 2  # one rank's SiLU-gate pass: two f16 reads and one f16 write per element
             entry.update({
                 "ms_gate_up_gemm": t_gu, "ms_silu_gate": t_act, "ms_down_gemm": t_down, "ms_three_launches": t_local,
@@ -1036,6 +1070,9 @@ def bench_ffn_chain(torch, dist, ops, dev, rank, world, peaks):
                 "ms_overlapped_all_reduce": t_ov, "overlap_chunks": ov_chunks,
                 "ms_fused_pipelined_all_reduce": t_fp if (fused_ok and world > 1) else None,
                 "fused_pipelined_chunks": fp_best,
+                "ms_switch_all_reduce": t_sw if (switch_ok and world > 1) else None, "switch_chunks": sw_best,
+                "ms_switch_all_reduce_unchunked": t_sw0 if (switch_ok and world > 1) else None,
+                "switch_stage_ms": switch_stage_ms,
                 "ms_best_all_reduce": best,
                 "fused_form": "-" if not fused_ok else ("one step" if mm <= chain.m_one else "two steps"),
                 "tflops": flops / best / 1e9, "weight_stream_gbs": wbytes / best / 1e6,
@@ -1044,7 +1081,8 @@ def bench_ffn_chain(torch, dist, ops, dev, rank, world, peaks):
         if world > 1:
             chain.w_gu, chain.s_gu, chain.w_down, chain.s_down = sets[0]
             name = f"chain_m{mm}"
-            ok = _check_chain(torch, dist, ops, np, chain, x, mm, hidden, inter, rank, world, fused_ok, host_weights)
+            ok = _check_chain(torch, dist, ops, np, chain, x, mm, hidden, inter, rank, world, fused_ok, switch_ok,
+                              host_weights)
             checked.append(name)
             if not ok:
                 failed.append(name)
@@ -1057,17 +1095,20 @@ def bench_ffn_chain(torch, dist, ops, dev, rank, world, peaks):
                    "slots (peer memory), then a barrier and the slot sum; ms_fused_pipelined_all_reduce: the same "
                    "with the whole chain in row chunks (gate|up weights dequantised once), each chunk's barrier + "
                    "sum + store-back on a second stream behind the next chunk's launches; "
+                   "ms_switch_all_reduce: partials stay local, then multimem.ld_reduce + multimem.st through the "
+                   "NVSwitch per column block (switch_chunks: rows per pipelined chunk); "
                    "ms_overlapped_all_reduce: weights "
                    "dequantised once, rows in overlap_chunks, each chunk's NCCL all-reduce on a second stream "
                    "behind the next chunk's GEMMs")
     return res, {"checked": checked, "failed": failed}
 
 
-def _check_chain(torch, dist, ops, np, chain, x, mm, hidden, inter, rank, world, fused_ok, host_weights):
+def _check_chain(torch, dist, ops, np, chain, x, mm, hidden, inter, rank, world, fused_ok, switch_ok, host_weights):
     """Every reduction form of the chain against the stage-wise CPU oracle on two rows (rank 0,
     unsharded weights; bar: 1e-2 of max(|want|, the row's rms)), and the fused form's bits across
     the ranks."""
-    outs = {"nccl": None, "fused": None, "overlap": None, "fused_pipelined": None}
+    outs = {"nccl": None, "fused": None, "overlap": None, "fused_pipelined": None, "switch": None,
+            "switch_chunked": None}
     part = chain.local(x, mm)
     dist.all_reduce(part, op=dist.ReduceOp.SUM)
     outs["nccl"] = part.clone()
@@ -1077,18 +1118,24 @@ def _check_chain(torch, dist, ops, np, chain, x, mm, hidden, inter, rank, world,
         outs["overlap"] = chain.run_overlapped(x, mm).clone()
         if fused_ok and mm > chain.m_one:
             outs["fused_pipelined"] = chain.run_fused_pipelined(x, mm).clone()
+    if switch_ok:
+        outs["switch"] = chain.run_switch(x, mm).clone()
+        if mm > 512:
+            outs["switch_chunked"] = chain.run_switch(x, mm, chunks=[mm // 2, mm - mm // 2]).clone()
     torch.cuda.synchronize()
     why = []
     ok = ops.device_status(chain.device)[0] == 0
     if not ok:
         why.append("device status")
-    if outs["fused"] is not None:  # the fixed summation order gives every rank the same bits
-        digest = outs["fused"].contiguous().view(torch.int32).to(torch.int64).sum().reshape(1)
+    for name in ("fused", "switch"):  # one reducer per element: every rank holds the same bits
+        if outs[name] is None:
+            continue
+        digest = outs[name].contiguous().view(torch.int32).to(torch.int64).sum().reshape(1)
         all_d = torch.empty(world, dtype=torch.int64, device="cuda")
         dist.all_gather_into_tensor(all_d, digest)
         if not bool((all_d == all_d[0]).all().item()):
             ok = False
-            why.append("fused bits differ across ranks")
+            why.append(f"{name} bits differ across ranks")
     if rank == 0:
         from oracle import oracle as orc
         orc.build()

@@ -295,6 +295,18 @@ int32_t kaio_b200_sum_partials_f32_multicast(const float* slots, size_t slots_le
                                              size_t out_len, uint32_t out_ld, uint32_t out_col0,
                                              void* stream);
 
+/* All-reduce (sum) of an f32 [rows, ld] buffer that every rank holds at the same offset of a
+ * symmetric allocation bound to an NVLink multicast object.  multicast_in / multicast_out are the
+ * multicast addresses of the partial buffer and of the output buffer.  This rank reduces the column
+ * block [col0, col0 + cols) of all rows: `multimem.ld_reduce` adds the ranks' elements inside the
+ * switch, `multimem.st` delivers the sum to every rank.  Every rank calls it with its own block
+ * (rank r: col0 = r * ld / world), between two barriers of the caller's (partials complete
+ * before, outputs complete after).  One reducer per element: the same bits on every rank; the
+ * order of the in-switch additions is the hardware's. */
+int32_t kaio_b200_allreduce_multimem_f32(const void* multicast_in, void* multicast_out, size_t len,
+                                         uint32_t rows, uint32_t cols, uint32_t ld, uint32_t col0,
+                                         void* stream);
+
 /* ---- gated activation (between the up/gate and the down projection of an FFN block) ---- */
 
 /* The user kernel of examples/fused_silu_gate/src/main.rs:13-21:

@@ -1434,6 +1434,34 @@ KAIO_API int32_t kaio_b200_sum_partials_f32_multicast(const float* slots, size_t
                             out_len, out_ld, out_col0, true, stream);
 }
 
+KAIO_API int32_t kaio_b200_allreduce_multimem_f32(const void* multicast_in, void* multicast_out,
+                                                  size_t len, uint32_t rows, uint32_t cols,
+                                                  uint32_t ld, uint32_t col0, void* stream)
+{
+    const char* op = "allreduce_multimem_f32";
+    if (rows == 0 || cols == 0)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG, "%s dimensions must be non-zero", op);
+    if (cols % 4 != 0 || ld % 4 != 0 || col0 % 4 != 0 || ld < col0 + cols)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: cols, ld and col0 must be multiples of 4 and col0 + cols <= ld (got %u, %u, "
+                    "%u)", op, cols, ld, col0);
+    if (len < (size_t)(rows - 1) * ld + col0 + cols)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG, "%s: buffers too small: need %zu f32, got %zu", op,
+                    (size_t)(rows - 1) * ld + col0 + cols, len);
+    REQUIRE_PTR(multicast_in, op, "multicast_in");
+    REQUIRE_PTR(multicast_out, op, "multicast_out");
+    if ((uintptr_t)multicast_in % 16 != 0 || (uintptr_t)multicast_out % 16 != 0)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG, "%s: multicast addresses must be 16-byte aligned", op);
+    DeviceCtx* ctx;
+    int32_t rc;
+    if ((rc = get_ctx(&ctx)))
+        return rc;
+    return finish(launch_multimem_allreduce_f32(static_cast<const float*>(multicast_in),
+                                                static_cast<float*>(multicast_out), rows, cols, ld,
+                                                col0, static_cast<cudaStream_t>(stream)),
+                  op, "allreduce_multimem_f32");
+}
+
 // ---------------------------------------------------------------- allocation-free decode entry
 // Scratch of kaio_b200_matmul_int4_noalloc: split-K partial tiles, tile arrival counters and a
 // status block, in a fixed array that is part of the loaded module (every GPU that loads the

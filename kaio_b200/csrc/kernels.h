@@ -137,6 +137,10 @@ cudaError_t launch_sum_partials(const float* slots, uint32_t world, uint32_t row
                                 float* const* outs, uint32_t num_out, uint64_t out_ld,
                                 uint32_t out_col0, bool multicast, cudaStream_t stream);
 
+cudaError_t launch_multimem_allreduce_f32(const float* mc_in, float* mc_out, uint32_t rows,
+                                          uint32_t cols, uint64_t ld, uint32_t col0,
+                                          cudaStream_t stream);
+
 // ---------------------------------------------------------------- gated activation
 cudaError_t launch_silu_gate_f32(const float* x, const float* gate, float* out, size_t n,
                                  cudaStream_t stream);

@@ -53,6 +53,63 @@ sum_partials_kernel(const float* __restrict__ slots, uint32_t world, uint32_t ro
     }
 }
 
+// All-reduce of a [rows, ld] f32 buffer that every rank holds at the same offset of a symmetric
+// allocation bound to an NVLink multicast object: this rank reduces ITS column block
+// [col0, col0 + cols) -- multimem.ld_reduce pulls the element from every rank and adds inside the
+// switch, so one reduced copy crosses this GPU's link instead of world - 1 partial ones -- and
+// multimem.st delivers the sum to every rank's output.  One reducer per element: all ranks end
+// with the same bits.  Per rank and direction (world - 1) / world + 1 / world of the buffer
+// crosses NVLink; the peer-store form above moves 2 (world - 1) / world of it.
+__global__ void __launch_bounds__(256)
+multimem_allreduce_f32_kernel(const float* mc_in, float* mc_out, uint32_t rows, uint32_t cols,
+                              uint64_t ld, uint32_t col0)
+{
+    const uint32_t v = blockIdx.x * blockDim.x + threadIdx.x;
+    if (v >= cols / 4)
+        return;
+    // four rows in flight per thread: a reduction is a round trip through the switch
+    for (uint32_t r = blockIdx.y; r < rows; r += 4 * gridDim.y) {
+        float4 acc[4];
+#pragma unroll
+        for (uint32_t u = 0; u < 4; ++u) {
+            const uint32_t ru = r + u * gridDim.y;
+            if (ru < rows) {
+                const size_t o = (size_t)ru * ld + col0 + (size_t)v * 4;
+                asm volatile(
+                    "multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                    : "=f"(acc[u].x), "=f"(acc[u].y), "=f"(acc[u].z), "=f"(acc[u].w)
+                    : "l"(mc_in + o)
+                    : "memory");
+            }
+        }
+#pragma unroll
+        for (uint32_t u = 0; u < 4; ++u) {
+            const uint32_t ru = r + u * gridDim.y;
+            if (ru < rows) {
+                const size_t o = (size_t)ru * ld + col0 + (size_t)v * 4;
+                asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                             :
+                             : "l"(mc_out + o), "f"(acc[u].x), "f"(acc[u].y), "f"(acc[u].z),
+                               "f"(acc[u].w)
+                             : "memory");
+            }
+        }
+    }
+}
+
+cudaError_t launch_multimem_allreduce_f32(const float* mc_in, float* mc_out, uint32_t rows,
+                                          uint32_t cols, uint64_t ld, uint32_t col0,
+                                          cudaStream_t stream)
+{
+    const uint32_t gx = (cols / 4 + 255) / 256;
+    uint32_t gy = (148 * 8 + gx - 1) / gx;
+    gy = gy > rows ? rows : gy;
+    gy = gy < 1 ? 1 : (gy > 65535 ? 65535 : gy);
+    multimem_allreduce_f32_kernel<<<dim3(gx, gy, 1), 256, 0, stream>>>(mc_in, mc_out, rows, cols, ld,
+                                                                       col0);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_sum_partials(const float* slots, uint32_t world, uint32_t rows, uint32_t cols,
                                 float* const* outs, uint32_t num_out, uint64_t out_ld,
                                 uint32_t out_col0, bool multicast, cudaStream_t stream)

@@ -235,6 +235,80 @@ class FfnInt4:
         main.wait_stream(self.side_stream)
         return self.out_sym[: m * h].view(m, h)
 
+    # ---- all-reduce inside the NVSwitch (multimem.ld_reduce + multimem.st)
+
+    def _init_switch(self):
+        """Symmetric partial buffer for :meth:`run_switch`; needs the multicast addresses that torch
+        symmetric memory hands out where the fabric offers NVLink multicast."""
+        import torch.distributed._symmetric_memory as symm_mem
+        if not hasattr(self, "out_h"):
+            self._init_fused(self.out.device)
+        group = self.group if self.group is not None else dist.group.WORLD
+        self.part_sym = symm_mem.empty(self.max_m * self.hidden, dtype=torch.float32, device=self.out.device)
+        self.part_h = symm_mem.rendezvous(self.part_sym, group)
+        self.part_mc = int(getattr(self.part_h, "multicast_ptr", 0) or 0)
+        self.out_mc_switch = int(getattr(self.out_h, "multicast_ptr", 0) or 0)
+        if not self.part_mc or not self.out_mc_switch:
+            raise RuntimeError("no NVLink multicast address for the symmetric buffers on this fabric")
+        if not hasattr(self, "side_stream"):
+            self.side_stream = torch.cuda.Stream(device=self.out.device)
+
+    def run_switch(self, x: torch.Tensor, m: int, chunks: "list[int] | None" = None, mark=None) -> torch.Tensor:
+        """The chain with the all-reduce done by the NVSwitch: every rank writes its f32 partial
+        ``[m, hidden]`` into its own symmetric buffer, the ranks meet at a barrier, and rank ``r``
+        runs ``allreduce_multimem_f32`` on column block ``r`` -- ``multimem.ld_reduce`` adds the
+        eight partial elements inside the switch, ``multimem.st`` delivers the sum to every rank's
+        output -- so per rank and direction ``m * hidden * 4`` bytes cross NVLink instead of the
+        ``2 (P-1)/P`` times that of the peer-store form.  One reducer per element: the same bits on
+        every rank.  With ``chunks`` (row counts) the down projection runs chunk by chunk on
+        weights dequantised once, and chunk ``i``'s barrier + in-switch reduction run on a second
+        stream under chunk ``i+1``'s GEMM.  Returns the complete f32 ``[m, hidden]`` (symmetric
+        memory) on every rank."""
+        if m > self.max_m:
+            raise ValueError(f"m={m} exceeds max_m={self.max_m}")
+        if not hasattr(self, "part_mc"):
+            self._init_switch()
+        mark = mark or (lambda label: None)
+        ops, d, il, h, p = self.ops, self.device, self.i_loc, self.hidden, self.world
+        blk = h // p
+        chunks = chunks or [m]
+        if sum(chunks) != m or min(chunks) < 1:
+            raise ValueError(f"chunks {chunks} do not add up to m={m}")
+        ops.matmul_int4(d, x, self.w_gu, self.s_gu, self.gu, m, 2 * il, h, GROUP)
+        mark("gate_up")
+        ops.silu_gate_f16(d, self.gu, self.gu.view(-1)[il:], self.act, m, il, x_ld=2 * il, gate_ld=2 * il)
+        mark("silu_gate")
+        if len(chunks) == 1:
+            ops.matmul_int4(d, self.act, self.w_down, self.s_down, self.part_sym, m, h, il, GROUP)
+            mark("down")
+            self.part_h.barrier()  # every rank's partial is complete
+            mark("barrier")
+            ops.allreduce_multimem_f32(d, self.part_mc, self.out_mc_switch, m * h, m, blk, h, self.rank * blk)
+            mark("in_switch_all_reduce")
+            self.out_h.barrier()  # every block of the output has landed everywhere
+            mark("closing_barrier")
+            return self.out_sym[: m * h].view(m, h)
+        if not hasattr(self, "w_down_f16"):
+            self._init_overlap()
+        ops.dequantize_int4(d, self.w_down, self.s_down, self.w_down_f16, il, h, GROUP)
+        main = torch.cuda.current_stream()
+        side_dev = type(d)(d.ordinal, self.side_stream)
+        r0 = 0
+        for rows in chunks:
+            ops.matmul_tc(d, self.act[r0 * il:(r0 + rows) * il], self.w_down_f16,
+                          self.part_sym[r0 * h:(r0 + rows) * h], rows, h, il)
+            ev = torch.cuda.Event()
+            ev.record(main)
+            with torch.cuda.stream(self.side_stream):
+                self.side_stream.wait_event(ev)
+                self.part_h.barrier()
+                ops.allreduce_multimem_f32(side_dev, self.part_mc + r0 * h * 4, self.out_mc_switch + r0 * h * 4,
+                                           rows * h, rows, blk, h, self.rank * blk)
+                self.out_h.barrier()
+            r0 += rows
+        main.wait_stream(self.side_stream)
+        return self.out_sym[: m * h].view(m, h)
+
     # ---- all-reduce overlapped with the GEMMs (large M)
 
     @staticmethod

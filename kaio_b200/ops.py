@@ -209,6 +209,13 @@ def sum_partials_f32_multicast(device, slots, world, rows, cols, multicast_out, 
           C.c_void_p(int(multicast_out)), C.c_size_t(out_numel), out_ld, out_col0)
 
 
+def allreduce_multimem_f32(device, multicast_in, multicast_out, numel, rows, cols, ld, col0):
+    """Extension: this rank's column block ``[col0, col0 + cols)`` of an in-switch all-reduce
+    (``multimem.ld_reduce`` + ``multimem.st``) over multicast addresses of symmetric buffers."""
+    _call(device, "kaio_b200_allreduce_multimem_f32", C.c_void_p(int(multicast_in)), C.c_void_p(int(multicast_out)),
+          C.c_size_t(numel), rows, cols, ld, col0)
+
+
 # ------------------------------------------------------------------ fused QKV
 
 def qkv_project_int8(device, x, w_q, w_k, w_v, scale_q, scale_k, scale_v, q_out, k_out, v_out, m, n, k):

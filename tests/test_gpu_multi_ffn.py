@@ -104,6 +104,28 @@ def _worker(rank, world, port, shapes, ret):
             ok = ok and bool(np.all(np.isfinite(got))) and rel < 1e-2
             ok = ok and bool(torch.equal(piped[0].view(torch.int32), piped[1].view(torch.int32)))
             dist.barrier()
+            # the all-reduce inside the NVSwitch (multimem.ld_reduce + multimem.st), whole and in two
+            # row chunks, where the fabric hands out multicast addresses: the oracle's chain within
+            # the bar, and the same bits on every rank (one reducer per element)
+            try:
+                chain._init_switch()
+                have_switch = 1
+            except RuntimeError:
+                have_switch = 0
+            flag = torch.tensor([have_switch], device="cuda")
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if bool(flag.item()):
+                for chunks in (None, [m - m // 2, m // 2]):
+                    got_d = chain.run_switch(x, m, chunks=chunks).clone()
+                    torch.cuda.synchronize()
+                    got = got_d.cpu().numpy()
+                    rel = np.max(np.abs(got - want) / np.maximum(np.abs(want), 1.0))
+                    ok = ok and bool(np.all(np.isfinite(got))) and rel < 1e-2
+                    bits = [torch.empty_like(got_d, dtype=torch.int32) for _ in range(world)]
+                    dist.all_gather(bits, got_d.view(torch.int32).contiguous())
+                    ok = ok and all(bool(torch.equal(bits[0], b)) for b in bits[1:])
+                    dist.barrier()
+            ret[f"switch{rank}"] = bool(flag.item())
             assert ops.device_status(dev)[0] == 0
         ret[rank] = ok
     finally:
@@ -119,4 +141,5 @@ def test_ffn_chain_ranks(world):
     mgr = mp.Manager()
     ret = mgr.dict()
     mp.spawn(_worker, args=(world, _free_port(), shapes, ret), nprocs=world, join=True)
-    assert dict(ret) == {r: True for r in range(world)}
+    got = dict(ret)
+    assert {r: got[r] for r in range(world)} == {r: True for r in range(world)}
