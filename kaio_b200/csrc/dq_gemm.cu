@@ -432,22 +432,84 @@ dequant_s4_kernel(const DequantArgs args, uint32_t n, uint32_t k)
     }
 }
 
-// s8 [K,N] -> f16 [K,N] (exact).
+// The same conversion without the shared-memory transpose, for K % 32 == 0 and even N: a thread owns
+// two neighbouring columns and 32 k (one 16-byte load per column; the two halves of a 32-byte sector
+// are fetched by consecutive k chunks of the same warp), and for each k the warp writes 64 columns
+// as one full 128-byte line of half2.  Streams at about twice the rate of the tiled kernel, which
+// spends its time in two block barriers per 4096 weights.
+__global__ void __launch_bounds__(256)
+dequant_s4_stream_kernel(const DequantArgs args, uint32_t n, uint32_t k)
+{
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(args.w[blockIdx.z]);
+    const __half* scales = args.scales[blockIdx.z];
+    __half* out = args.out[blockIdx.z];
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint32_t col = blockIdx.x * 64 + lane * 2;
+    if (col >= n)
+        return;
+    const uint32_t k_words = k >> 3;
+    // 8 warps of a block take 8 consecutive 32-k chunks; blocks stride over K
+    for (uint32_t k0 = (blockIdx.y * 8 + warp) * 32; k0 < k; k0 += gridDim.y * 8 * 32) {
+        const uint4 a = *reinterpret_cast<const uint4*>(w + (k0 >> 3) + (size_t)col * k_words);
+        const uint4 b = *reinterpret_cast<const uint4*>(w + (k0 >> 3) + (size_t)(col + 1) * k_words);
+        const __half2 sc = *reinterpret_cast<const __half2*>(scales + (size_t)(k0 >> 7) * n + col);
+        const uint32_t wa[4] = {a.x, a.y, a.z, a.w}, wb[4] = {b.x, b.y, b.z, b.w};
+        __half* dst = out + (size_t)k0 * n + col;
+#pragma unroll
+        for (int wi = 0; wi < 4; ++wi) {
+#pragma unroll
+            for (int nib = 0; nib < 8; ++nib) {
+                const int32_t qa = ((int32_t)(wa[wi] << (28 - 4 * nib))) >> 28;
+                const int32_t qb = ((int32_t)(wb[wi] << (28 - 4 * nib))) >> 28;
+                const __half2 q = __halves2half2(__int2half_rn(qa), __int2half_rn(qb));
+                *reinterpret_cast<__half2*>(dst + (size_t)(wi * 8 + nib) * n) = __hmul2(q, sc);
+            }
+        }
+    }
+}
+
+static void launch_dequant_s4_any(const DequantArgs& da, uint32_t n, uint32_t k, int num_probs,
+                                  cudaStream_t stream)
+{
+    bool aligned = true;  // 16-byte loads of the packed words, 4-byte accesses of scales and output
+    for (int i = 0; i < num_probs; ++i)
+        aligned = aligned && (uintptr_t)da.w[i] % 16 == 0 && (uintptr_t)da.scales[i] % 4 == 0 &&
+                  (uintptr_t)da.out[i] % 4 == 0;
+    if (k % 32 == 0 && n % 2 == 0 && aligned) {
+        const uint32_t gx = (n + 63) / 64;
+        uint32_t gy = (k + 255) / 256;
+        // enough blocks to fill the GPU several times over, not more
+        const uint32_t want = (148u * 32u + gx - 1) / gx;
+        gy = gy < want ? gy : want;
+        dequant_s4_stream_kernel<<<dim3(gx, gy < 1 ? 1 : gy, num_probs), 256, 0, stream>>>(da, n, k);
+    } else {
+        dim3 grid((n + 63) / 64, (k + 63) / 64, num_probs);
+        dequant_s4_kernel<<<grid, 256, 0, stream>>>(da, n, k);
+    }
+}
+
+// s8 [K,N] -> f16 [K,N] (exact).  VEC = 16: one 16-byte load and two 16-byte stores per thread and
+// step (count % 16 == 0 and 16-byte aligned bases); VEC = 8: 8-byte loads for the rest.
+template <int VEC>
 __global__ void __launch_bounds__(256)
 dequant_s8_kernel(const DequantArgs args, size_t count)
 {
     const int8_t* w = reinterpret_cast<const int8_t*>(args.w[blockIdx.y]);
     __half* out = args.out[blockIdx.y];
-    const size_t stride = (size_t)gridDim.x * blockDim.x * 8;
-    for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < count; i += stride) {
-        // count % 8 == 0 and 8-byte aligned bases on this path
-        const int2 raw = *reinterpret_cast<const int2*>(w + i);
-        const int8_t* b = reinterpret_cast<const int8_t*>(&raw);
-        __half2 h[4];
+    const size_t stride = (size_t)gridDim.x * blockDim.x * VEC;
+    for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC; i < count; i += stride) {
+        alignas(16) int8_t b[VEC];
+        if constexpr (VEC == 16)
+            *reinterpret_cast<int4*>(b) = *reinterpret_cast<const int4*>(w + i);
+        else
+            *reinterpret_cast<int2*>(b) = *reinterpret_cast<const int2*>(w + i);
+        __half2 h[VEC / 2];
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
+        for (int j = 0; j < VEC / 2; ++j)
             h[j] = __halves2half2(__int2half_rn((int)b[2 * j]), __int2half_rn((int)b[2 * j + 1]));
-        *reinterpret_cast<uint4*>(out + i) = *reinterpret_cast<uint4*>(h);
+#pragma unroll
+        for (int j = 0; j < VEC / 8; ++j)
+            reinterpret_cast<uint4*>(out + i)[j] = reinterpret_cast<uint4*>(h)[j];
     }
 }
 
@@ -517,8 +579,7 @@ cudaError_t launch_dequant_s4(const uint32_t* w_packed, const __half* scales, __
     da.w[0] = w_packed;
     da.scales[0] = scales;
     da.out[0] = out;
-    dim3 grid((n + 63) / 64, (k + 63) / 64, 1);
-    dequant_s4_kernel<<<grid, 256, 0, stream>>>(da, n, k);
+    launch_dequant_s4_any(da, n, k, 1, stream);
     return cudaGetLastError();
 }
 
@@ -539,12 +600,18 @@ cudaError_t launch_dq_gemm(const DeviceCtx& ctx, int wfmt, const __half* x, cons
         for (int i = 0; i < num_probs; ++i)  // the weights are the f16 operand already
             da.out[i] = const_cast<__half*>(reinterpret_cast<const __half*>(probs[i].w));
     } else if (wfmt == WFMT_S4_PACKED) {
-        dim3 grid((n + 63) / 64, (k + 63) / 64, num_probs);
-        dequant_s4_kernel<<<grid, 256, 0, stream>>>(da, n, k);
+        launch_dequant_s4_any(da, n, k, num_probs, stream);
     } else {
-        const size_t count = (size_t)k * n;
-        dim3 grid((unsigned)((count / 8 + 255) / 256 < 4096 ? (count / 8 + 255) / 256 : 4096), num_probs);
-        dequant_s8_kernel<<<grid, 256, 0, stream>>>(da, count);
+        const size_t count = (size_t)k * n;  // count % 8 == 0 and 8-byte aligned bases on this path
+        bool wide = count % 16 == 0;
+        for (int i = 0; i < num_probs; ++i)
+            wide = wide && (uintptr_t)da.w[i] % 16 == 0 && (uintptr_t)da.out[i] % 16 == 0;
+        const size_t vecs = count / (wide ? 16 : 8);
+        dim3 grid((unsigned)((vecs + 255) / 256 < 8192 ? (vecs + 255) / 256 : 8192), num_probs);
+        if (wide)
+            dequant_s8_kernel<16><<<grid, 256, 0, stream>>>(da, count);
+        else
+            dequant_s8_kernel<8><<<grid, 256, 0, stream>>>(da, count);
     }
     cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess)
