@@ -430,7 +430,9 @@ def sharded_summary(world, ffn, chain):
     out = {"n_gpus": world}
     c4 = chain.get("m4096", {})
     out["chain_m4096_ms"] = {k: r3(c4.get(v)) for k, v in (
-        ("three_launches", "ms_three_launches"), ("nccl_all_reduce", "ms_with_all_reduce"),
+        ("three_launches", "ms_three_launches"), ("two_launches_silu_epilogue", "ms_two_launches_silu_epilogue"),
+        ("fused_all_reduce_silu_epilogue", "ms_fused_all_reduce_silu_epilogue"),
+        ("nccl_all_reduce", "ms_with_all_reduce"),
         ("overlapped_all_reduce", "ms_overlapped_all_reduce"), ("fused_all_reduce", "ms_fused_all_reduce"),
         ("fused_pipelined_all_reduce", "ms_fused_pipelined_all_reduce"),
         ("switch_all_reduce", "ms_switch_all_reduce"), ("reduce_scatter", "ms_with_reduce_scatter"))}
@@ -1022,6 +1024,25 @@ def bench_ffn_chain(torch, dist, ops, dev, rank, world, peaks):
             t_gu, t_act, t_down, t_local, t_ar, t_rs, t_fused, t_ov0, t_ov1, t_fp0, t_fp1, t_sw0, t_sw1 = \
                 _max_over_ranks(torch, dist, world, ts)
             t_sw, sw_best = (t_sw0, sw_chunks[0]) if t_sw0 <= t_sw1 else (t_sw1, sw_chunks[1])
+            # gate|up and the SiLU-gate as one launch (activation in the GEMM's epilogue): the local
+            # chain and, at N > 1, the fused all-reduce form on top of it
+            # (timed in alternation with the three-launch form, two rounds, min of each: at M = 4096 the
+            # GPU drifts along its power cap, so forms timed minutes apart do not compare)
+            chain.enable_fused_silu()
+            pair_a, pair_b = [], []
+            for _ in range(2):
+                chain.enable_fused_silu(False)
+                pair_a.append(_time_ms(torch, lambda: chain.local(x, mm), iters))
+                chain.enable_fused_silu(True)
+                pair_b.append(_time_ms(torch, lambda: chain.local(x, mm), iters))
+            fs = [min(pair_b), min(pair_a)]
+            if world > 1 and fused_ok:
+                fs.append(_time_ms(torch, lambda: chain.run_fused(x, mm), iters))
+            chain.enable_fused_silu(False)
+            fs = _max_over_ranks(torch, dist, world, fs)
+            t_local_same = fs[1]
+            fs = [fs[0]] + fs[2:]
+            t_local_fs, t_fused_fs = fs[0], (fs[1] if len(fs) > 1 else None)
             stage_ms = None
             if world > 1 and fused_ok:
                 # where the fused form's time goes: events between its launches, 5 runs, the mean per
@@ -1065,10 +1086,14 @@ def bench_ffn_chain(torch, dist, ops, dev, rank, world, peaks):
                 switch_stage_ms = {l: round(v, 4) for l, v in zip(labels, vals)}
             t_fp, fp_best = (t_fp0, fp_chunks[0]) if t_fp0 <= t_fp1 else (t_fp1, fp_chunks[1])
             t_ov, ov_chunks = (t_ov0, chunk_sets[0]) if t_ov0 <= t_ov1 else (t_ov1, chunk_sets[1])
-            best = min(t_ar, t_fused, t_ov, t_fp, t_sw) if world > 1 else t_local
+            best = min(t_ar, t_fused, t_ov, t_fp, t_sw) if world > 1 else min(t_local, t_local_fs)
+            if t_fused_fs is not None:
+                best = min(best, t_fused_fs)
             act_bytes = 3 * mm * il * 2  # one rank's SiLU-gate pass: two f16 reads and one f16 write per element
             entry.update({
                 "ms_gate_up_gemm": t_gu, "ms_silu_gate": t_act, "ms_down_gemm": t_down, "ms_three_launches": t_local,
+                "ms_two_launches_silu_epilogue": t_local_fs, "ms_three_launches_same_window": t_local_same,
+                "ms_fused_all_reduce_silu_epilogue": t_fused_fs,
                 "ms_with_all_reduce": t_ar, "ms_with_reduce_scatter": t_rs,
                 "ms_fused_all_reduce": t_fused if fused_ok else None, "fused_stage_ms": stage_ms,
                 "ms_overlapped_all_reduce": t_ov, "overlap_chunks": ov_chunks,
@@ -1099,6 +1124,8 @@ def bench_ffn_chain(torch, dist, ops, dev, rank, world, peaks):
                    "slots (peer memory), then a barrier and the slot sum; ms_fused_pipelined_all_reduce: the same "
                    "with the whole chain in row chunks (gate|up weights dequantised once), each chunk's barrier + "
                    "sum + store-back on a second stream behind the next chunk's launches; "
+                   "ms_two_launches_silu_epilogue: gate|up with the SiLU-gate in its epilogue (column-interleaved "
+                   "weights), then down; ms_fused_all_reduce_silu_epilogue: the fused all-reduce form on top of it; "
                    "ms_switch_all_reduce: partials stay local, then multimem.ld_reduce + multimem.st through the "
                    "NVSwitch per column block (switch_chunks: rows per pipelined chunk); "
                    "ms_overlapped_all_reduce: weights "
@@ -1111,8 +1138,8 @@ def _check_chain(torch, dist, ops, np, chain, x, mm, hidden, inter, rank, world,
     """Every reduction form of the chain against the stage-wise CPU oracle on two rows (rank 0,
     unsharded weights; bar: 1e-2 of max(|want|, the row's rms)), and the fused form's bits across
     the ranks."""
-    outs = {"nccl": None, "fused": None, "overlap": None, "fused_pipelined": None, "switch": None,
-            "switch_chunked": None}
+    outs = {"nccl": None, "fused": None, "overlap": None, "fused_pipelined": None, "fused_silu_epilogue": None,
+            "switch": None, "switch_chunked": None}
     part = chain.local(x, mm)
     dist.all_reduce(part, op=dist.ReduceOp.SUM)
     outs["nccl"] = part.clone()
@@ -1122,6 +1149,10 @@ def _check_chain(torch, dist, ops, np, chain, x, mm, hidden, inter, rank, world,
         outs["overlap"] = chain.run_overlapped(x, mm).clone()
         if fused_ok and mm > chain.m_one:
             outs["fused_pipelined"] = chain.run_fused_pipelined(x, mm).clone()
+    if fused_ok and mm > 512:
+        chain.enable_fused_silu()
+        outs["fused_silu_epilogue"] = chain.run_fused(x, mm).clone()
+        chain.enable_fused_silu(False)
     if switch_ok:
         outs["switch"] = chain.run_switch(x, mm).clone()
         if mm > 512:

@@ -242,6 +242,20 @@ int32_t kaio_b200_attention_mha_f16(const kaio_f16* q, size_t q_len, const kaio_
                                     uint32_t seq_k, uint32_t head_dim, uint32_t row_stride,
                                     int32_t causal, void* stream);
 
+/* EXT: the gate|up projection of a feed-forward block with the SiLU-gate in the GEMM's epilogue.
+ * b_packed / scales describe W4A16 weights [k, 2*cols] in kaio_b200_matmul_int4's layout whose
+ * COLUMNS ALTERNATE IN BLOCKS OF 64: block 2b holds columns [64b, 64b+64) of W_gate, block 2b+1
+ * the same columns of W_up (cols % 64 == 0).  act f16 [m, cols] = silu(x W_gate) * (x W_up), both
+ * projections rounded to f16 first: bit for bit what kaio_b200_matmul_int4_f16out followed by
+ * kaio_b200_silu_gate_f16 gives.  For m > 512 the [m, 2*cols] projection never reaches memory;
+ * smaller m run the small-M W4A16 kernels into gu_scratch (f16 [m, 2*cols], 16-byte aligned,
+ * required there, ignored otherwise) and apply the activation in a second launch. */
+int32_t kaio_b200_matmul_int4_silu_gate(const kaio_f16* x, size_t x_len, const uint32_t* b_packed,
+                                        size_t b_len, const kaio_f16* scales, size_t scales_len,
+                                        kaio_f16* act, size_t act_len, kaio_f16* gu_scratch,
+                                        size_t gu_len, uint32_t m, uint32_t cols, uint32_t k,
+                                        uint32_t group_size, void* stream);
+
 /* ---- quantisers (the step in front of the GEMMs; host code in the reference's examples) ---- */
 
 /* GPU form of `derive_scale` + `quantize` applied per row

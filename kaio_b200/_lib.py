@@ -50,6 +50,8 @@ SIGNATURES = {
     "kaio_b200_sum_partials_f32": [_VP, _SZ, _U32, _U32, _U32, _VP, _U32, _SZ, _U32, _U32, _VP],
     "kaio_b200_sum_partials_f32_multicast": [_VP, _SZ, _U32, _U32, _U32, _VP, _SZ, _U32, _U32, _VP],
     "kaio_b200_allreduce_multimem_f32": [_VP, _VP, _SZ, _U32, _U32, _U32, _U32, _VP],
+    "kaio_b200_matmul_int4_silu_gate": [_VP, _SZ, _VP, _SZ, _VP, _SZ, _VP, _SZ, _VP, _SZ, _U32, _U32, _U32, _U32,
+                                        _VP],
     "kaio_b200_silu_gate_f32": [_VP, _SZ, _VP, _SZ, _VP, _SZ, _U32, _VP],
     "kaio_b200_silu_gate_f16": [_VP, _SZ, _VP, _SZ, _VP, _SZ, _U32, _U32, _U32, _U32, _U32, _VP],
     "kaio_b200_device_status": [_VP, C.POINTER(_U32)],

@@ -1126,6 +1126,69 @@ KAIO_API int32_t kaio_b200_silu_gate_f16(const kaio_f16* x, size_t x_len, const 
                   op, "silu_gate_f16");
 }
 
+KAIO_API int32_t kaio_b200_matmul_int4_silu_gate(const kaio_f16* x, size_t x_len,
+                                                 const uint32_t* b_packed, size_t b_len,
+                                                 const kaio_f16* scales, size_t scales_len,
+                                                 kaio_f16* act, size_t act_len, kaio_f16* gu_scratch,
+                                                 size_t gu_len, uint32_t m, uint32_t cols,
+                                                 uint32_t k, uint32_t group_size, void* stream)
+{
+    const char* op = "matmul_int4_silu_gate";
+    if (cols == 0 || cols % 64 != 0)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: cols must be a non-zero multiple of 64, the interleave block (got %u)", op,
+                    cols);
+    const uint32_t n = 2 * cols;
+    // the interleaved projection is an ordinary W4A16 product [m, 2*cols]
+    int32_t rc = validate_int4("f16", x_len, b_len, scales_len, (size_t)m * n, m, n, k, group_size);
+    if (rc)
+        return rc;
+    if (act_len < (size_t)m * cols)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG, "%s: act buffer too small: need %zu f16, got %zu", op,
+                    (size_t)m * cols, act_len);
+    REQUIRE_PTR(x, op, "X");
+    REQUIRE_PTR(b_packed, op, "B packed");
+    REQUIRE_PTR(scales, op, "scales");
+    REQUIRE_PTR(act, op, "act");
+    DeviceCtx* ctx;
+    if ((rc = get_ctx(&ctx, act)))
+        return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    DqProblem pr;
+    pr.w = b_packed;
+    pr.scales = reinterpret_cast<const __half*>(scales);
+    pr.col_scale = nullptr;
+    pr.scale = 1.0f;
+    pr.out = act;
+    const __half* xh = reinterpret_cast<const __half*>(x);
+    // Large M: the paired f16 GEMM applies the activation in its epilogue (the interleaved
+    // [m, 2*cols] projection never reaches memory).  The small-M kernels keep their own epilogues:
+    // they write the interleaved projection to the caller's scratch and a second launch applies
+    // the activation -- the same bits either way.
+    const bool small_m = w4a16_decode_ok(xh, &pr, 1, m, n, k) ||
+                         (m <= fused_max_m() && w4a16_fused_ok(xh, &pr, 1, m, n, k));
+    if (!small_m && m > 128 && (uintptr_t)act % 16 == 0 &&
+        dq_gemm_fast_path_ok(WFMT_S4_PACKED, xh, &pr, 1, true, m, n, k)) {
+        StreamScratch* sc = nullptr;
+        if ((rc = ensure_dq_workspace(ctx, s, dq_gemm_workspace_bytes(1, n, k), &sc)))
+            return rc;
+        return finish(launch_dq_gemm(*ctx, WFMT_S4_PACKED, xh, &pr, 1, true, false, m, n, k,
+                                     sc->dq_workspace, s, nullptr, true),
+                      op, "w4a16_tcgen05_silu_gate");
+    }
+    if (gu_scratch == nullptr || gu_len < (size_t)m * n || (uintptr_t)gu_scratch % 16 != 0 ||
+        (uintptr_t)act % 16 != 0)
+        return fail(KAIO_B200_ERR_INVALID_CONFIG,
+                    "%s: this shape needs a 16-byte aligned scratch of %zu f16 for the interleaved "
+                    "projection (got %zu) and a 16-byte aligned act", op, (size_t)m * n, gu_len);
+    if ((rc = run_int4(x, x_len, b_packed, b_len, scales, scales_len, gu_scratch, gu_len, true, m, n, k,
+                       group_size, stream)))
+        return rc;
+    return finish(launch_silu_gate_f16_interleaved(reinterpret_cast<const __half*>(gu_scratch),
+                                                   reinterpret_cast<__half*>(act), m, cols, n, cols, s),
+                  op, "w4a16_then_silu_gate");
+}
+
 KAIO_API int32_t kaio_b200_quantize_pack_int4(const float* w, size_t w_len, uint32_t* packed,
                                               size_t packed_len, kaio_f16* scales,
                                               size_t scales_len, uint32_t k, uint32_t n,

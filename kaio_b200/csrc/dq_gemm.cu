@@ -26,6 +26,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "silu.cuh"
 
 namespace kaio {
 namespace f16g {
@@ -73,6 +74,8 @@ struct Params {
     uint32_t scatter_cols;  // > 0: a block goes only to map col0 / scatter_cols (see OutputCopies)
     uint32_t m, n, k;
     int post_scale;
+    int silu_gate;  // f16 out only: column blocks of 64 alternate between two projections a, b;
+                    // the epilogue stores silu(f16(a)) * f16(b) as [m, n/2]
     uint32_t* status;
 };
 
@@ -292,6 +295,46 @@ f16_gemm_kernel(const __grid_constant__ TensorMaps maps, const Params p)
                 if (col0 >= p.n)
                     break;  // warp-uniform
                 uint32_t stg[32];  // one 128-byte output row
+                if (OUT_F16 && p.silu_gate) {
+                    // blocks c (projection a) and c+1 (projection b) make one output block
+                    if (c & 1u)
+                        continue;
+#pragma unroll
+                    for (uint32_t half = 0; half < 2; ++half) {
+                        uint32_t ra[32], rb[32];
+                        tmem_ld_32x32b_x32(taddr + c * 64 + half * 32, ra);
+                        tmem_ld_32x32b_x32(taddr + (c + 1) * 64 + half * 32, rb);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; j += 2) {
+                            // both projections are rounded to f16 first: the bits of the f16-out
+                            // GEMM followed by the stand-alone pass
+                            const __half2 ha = __floats2half2_rn(__uint_as_float(ra[j]),
+                                                                 __uint_as_float(ra[j + 1]));
+                            const __half2 hb = __floats2half2_rn(__uint_as_float(rb[j]),
+                                                                 __uint_as_float(rb[j + 1]));
+                            stg[half * 16 + (j >> 1)] =
+                                silu_gate_h2(*reinterpret_cast<const uint32_t*>(&ha),
+                                             *reinterpret_cast<const uint32_t*>(&hb));
+                        }
+                    }
+                    if (lane == 0)
+                        tma_store_wait_read<1>();
+                    __syncwarp();
+                    const uint32_t stg_off = (ewarp * 2 + ((c >> 1) & 1u)) * STG_BYTES;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        *reinterpret_cast<uint4*>(stg_gen + stg_off + sw128_offset(lane, j)) =
+                            make_uint4(stg[4 * j], stg[4 * j + 1], stg[4 * j + 2], stg[4 * j + 3]);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(omap, stg_base + stg_off, (int32_t)(col0 >> 1),
+                                     (int32_t)(m0 + quarter * 32));
+                        tma_store_commit();
+                    }
+                    continue;
+                }
 #pragma unroll
                 for (uint32_t half = 0; half < COLS_PER_BLOCK / 32; ++half) {
                     uint32_t r[32];
@@ -586,7 +629,7 @@ cudaError_t launch_dequant_s4(const uint32_t* w_packed, const __half* scales, __
 cudaError_t launch_dq_gemm(const DeviceCtx& ctx, int wfmt, const __half* x, const DqProblem* probs,
                            int num_probs, bool out_f16, bool post_scale, uint32_t m, uint32_t n,
                            uint32_t k, void* dq_workspace, cudaStream_t stream,
-                           const OutputCopies* copies)
+                           const OutputCopies* copies, bool silu_gate)
 {
     using namespace f16g;
     const size_t per = dq_gemm_workspace_bytes(1, n, k);
@@ -648,7 +691,11 @@ cudaError_t launch_dq_gemm(const DeviceCtx& ctx, int wfmt, const __half* x, cons
             ld = n;
         }
         // in the scatter form a destination holds one block of scatter_cols columns
-        const uint64_t width = (copies && copies->scatter_cols) ? copies->scatter_cols : n;
+        uint64_t width = (copies && copies->scatter_cols) ? copies->scatter_cols : n;
+        if (silu_gate) {  // the activation is half as wide as the two interleaved projections
+            width = n / 2;
+            ld = n / 2;
+        }
         if (out_f16)
             err = encode_tensor_map_2d(&maps.out[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, width,
                                        m, ld * 2, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -670,6 +717,7 @@ cudaError_t launch_dq_gemm(const DeviceCtx& ctx, int wfmt, const __half* x, cons
     p.n = n;
     p.k = k;
     p.post_scale = post_scale ? 1 : 0;
+    p.silu_gate = silu_gate ? 1 : 0;
     p.status = ctx.status;
     if (pair)
         return out_f16 ? launch_f16_gemm<true, true>(ctx, maps, p, stream)

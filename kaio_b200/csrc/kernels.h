@@ -121,7 +121,10 @@ cudaError_t launch_dequant_s4(const uint32_t* w_packed, const __half* scales, __
 cudaError_t launch_dq_gemm(const DeviceCtx& ctx, int wfmt, const __half* x, const DqProblem* probs,
                            int num_probs, bool out_f16, bool post_scale, uint32_t m, uint32_t n,
                            uint32_t k, void* dq_workspace, cudaStream_t stream,
-                           const OutputCopies* copies = nullptr);
+                           const OutputCopies* copies = nullptr, bool silu_gate = false);
+// silu_gate (one problem, f16 out, n % 128 == 0): the weight columns alternate in blocks of 64
+// between two projections; the epilogue rounds both to f16, applies out = silu(a) * b and stores
+// [m, n/2] (probs[0].out).
 
 // ---------------------------------------------------------------- quantisers
 cudaError_t launch_quantize_rows_int8(const float* x, int8_t* q, float* scale, uint32_t m,
@@ -147,6 +150,9 @@ cudaError_t launch_silu_gate_f32(const float* x, const float* gate, float* out, 
 cudaError_t launch_silu_gate_f16(const __half* x, const __half* gate, __half* out, uint32_t rows,
                                  uint32_t cols, uint32_t x_ld, uint32_t gate_ld, uint32_t out_ld,
                                  cudaStream_t stream);
+cudaError_t launch_silu_gate_f16_interleaved(const __half* gu, __half* out, uint32_t rows,
+                                             uint32_t cols, uint32_t gu_ld, uint32_t out_ld,
+                                             cudaStream_t stream);
 
 // ---------------------------------------------------------------- self-test of the bounded wait
 cudaError_t launch_selftest_bounded_wait(const DeviceCtx& ctx, uint32_t budget_us,

@@ -6,6 +6,7 @@
 // two inputs may be the halves of one [rows, 2*cols] projection output).
 // Both are streaming passes bound by HBM: 12 bytes per element (f32), 6 bytes (f16).
 #include "kernels.h"
+#include "silu.cuh"
 
 namespace kaio {
 
@@ -46,23 +47,6 @@ silu_gate_f32_kernel(const float* __restrict__ x, const float* __restrict__ gate
         for (; i < count; i += stride)
             out[i] = silu_gate1(__ldg(x + i), __ldg(gate + i));
     }
-}
-
-// The f16 form rounds its result to 11 significant bits, so the hardware approximations
-// (ex2.approx inside __expf, rcp.approx inside __fdividef; a few f32 units in the last place)
-// are invisible after the rounding except on rare ties; with the IEEE divide and expf the pass
-// is bound by instruction issue, not by HBM.
-__device__ __forceinline__ float silu_gate1_fast(float x, float g)
-{
-    return __fdividef(x, 1.0f + __expf(-x)) * g;
-}
-
-__device__ __forceinline__ uint32_t silu_gate_h2(uint32_t xw, uint32_t gw)
-{
-    const float2 xf = __half22float2(*reinterpret_cast<const __half2*>(&xw));
-    const float2 gf = __half22float2(*reinterpret_cast<const __half2*>(&gw));
-    const __half2 r = __floats2half2_rn(silu_gate1_fast(xf.x, gf.x), silu_gate1_fast(xf.y, gf.y));
-    return *reinterpret_cast<const uint32_t*>(&r);
 }
 
 __device__ __forceinline__ uint4 silu_gate_h8(const uint4& a, const uint4& b)
@@ -107,6 +91,25 @@ silu_gate_f16_kernel(const __half* __restrict__ x, const __half* __restrict__ ga
         for (; r < rows; r += rs)
             out[(size_t)r * out_ld + c] = __float2half_rn(silu_gate1_fast(
                 __half2float(x[(size_t)r * x_ld + c]), __half2float(gate[(size_t)r * gate_ld + c])));
+    }
+}
+
+// The same pass on a projection whose columns alternate in blocks of 64 between the two inputs
+// (block 2b = x columns [64b, 64b+64), block 2b+1 = the gate columns of the same range): the
+// layout the fused gate|up GEMM takes its weights in.  cols % 64 == 0, 16-byte aligned rows.
+__global__ void __launch_bounds__(256)
+silu_gate_f16_interleaved_kernel(const __half* __restrict__ gu, __half* __restrict__ out,
+                                 uint32_t rows, uint32_t cols, uint32_t gu_ld, uint32_t out_ld)
+{
+    const uint32_t v = blockIdx.x * blockDim.x + threadIdx.x;
+    if (v >= cols / 8)
+        return;
+    const uint32_t c = v * 8;
+    const uint32_t src = (c >> 6) * 128 + (c & 63u);
+    for (uint32_t r = blockIdx.y; r < rows; r += gridDim.y) {
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(gu + (size_t)r * gu_ld + src));
+        const uint4 b = __ldg(reinterpret_cast<const uint4*>(gu + (size_t)r * gu_ld + src + 64));
+        *reinterpret_cast<uint4*>(out + (size_t)r * out_ld + c) = silu_gate_h8(a, b);
     }
 }
 
@@ -158,6 +161,15 @@ cudaError_t launch_silu_gate_f16(const __half* x, const __half* gate, __half* ou
     else
         silu_gate_f16_kernel<1><<<grid_2d(rows, cols), 256, 0, stream>>>(
             x, gate, out, rows, cols, x_ld, gate_ld, out_ld);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_silu_gate_f16_interleaved(const __half* gu, __half* out, uint32_t rows,
+                                             uint32_t cols, uint32_t gu_ld, uint32_t out_ld,
+                                             cudaStream_t stream)
+{
+    silu_gate_f16_interleaved_kernel<<<grid_2d(rows, cols / 8), 256, 0, stream>>>(gu, out, rows, cols,
+                                                                                 gu_ld, out_ld);
     return cudaGetLastError();
 }
 

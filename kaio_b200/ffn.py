@@ -70,6 +70,28 @@ def concat_gate_up(w_gate: torch.Tensor, s_gate: torch.Tensor, w_up: torch.Tenso
     return packed, scales.contiguous().view(-1)
 
 
+def interleave_index(n: int, block: int = 64) -> torch.Tensor:
+    """Column order of the fused gate|up + SiLU-gate GEMM: position ``p`` of the interleaved
+    ``[K, 2n]`` weight takes column ``index[p]`` of the concatenated ``[gate | up]`` weight -- blocks
+    of ``block`` gate columns alternate with the same columns of up."""
+    if n % block != 0:
+        raise ValueError(f"n={n} must be a multiple of the interleave block {block}")
+    p = torch.arange(2 * n)
+    b, within = p // (2 * block), p % (2 * block)
+    return torch.where(within < block, b * block + within, n + b * block + within - block)
+
+
+def interleave_gate_up(w_gu: torch.Tensor, s_gu: torch.Tensor, k: int, n: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """The concatenated ``[K, 2n]`` gate|up weight of :func:`concat_gate_up` re-ordered for
+    ``matmul_int4_silu_gate`` (packed columns are contiguous runs of ``K/8`` words; scales are
+    ``[K/128, 2n]``)."""
+    idx = interleave_index(n).to(w_gu.device)
+    packed = w_gu.view(-1)[: 2 * n * (k // 8)].view(2 * n, k // 8)[idx].contiguous().view(-1)
+    g = k // GROUP
+    scales = s_gu.view(-1)[: g * 2 * n].view(g, 2 * n)[:, idx].contiguous().view(-1)
+    return packed, scales
+
+
 class FfnInt4:
     """One rank's share of the W4A16 feed-forward block.
 
@@ -106,8 +128,31 @@ class FfnInt4:
         self.out = torch.empty(max_m * hidden, dtype=torch.float32, device=dev)
         self.rows = torch.empty((max_m // world) * hidden, dtype=torch.float32, device=dev) \
             if (world > 1 and reduce == "scatter") else None
+        self.fuse_silu = False
         if world > 1 and reduce == "fused":
             self._init_fused(dev)
+
+    def enable_fused_silu(self, on: bool = True):
+        """Run gate|up and the SiLU-gate as ONE launch (``matmul_int4_silu_gate``: the activation in
+        the GEMM's epilogue for m > 512, so the ``[m, 2I]`` projection never reaches memory) in
+        :meth:`local`, :meth:`run_fused` and :meth:`run_switch`.  Keeps a second, column-interleaved
+        copy of the gate|up shard.  The bits do not change."""
+        if on and not hasattr(self, "w_gu_il"):
+            self.w_gu_il, self.s_gu_il = interleave_gate_up(self.w_gu, self.s_gu, self.hidden, self.i_loc)
+        self.fuse_silu = bool(on)
+
+    def _gate_up_act(self, x: torch.Tensor, m: int, mark):
+        """``act[m, I_loc] = silu(x W_gate) * (x W_up)`` in ``self.act``: one launch or two."""
+        ops, d, il, h = self.ops, self.device, self.i_loc, self.hidden
+        if self.fuse_silu:
+            ops.matmul_int4_silu_gate(d, x, self.w_gu_il, self.s_gu_il, self.act, self.gu, m, il, h, GROUP)
+            mark("gate_up_silu")
+            return
+        ops.matmul_int4(d, x, self.w_gu, self.s_gu, self.gu, m, 2 * il, h, GROUP)
+        mark("gate_up")
+        # row r of gu = [gate(r, 0..il) | up(r, 0..il)]
+        ops.silu_gate_f16(d, self.gu, self.gu.view(-1)[il:], self.act, m, il, x_ld=2 * il, gate_ld=2 * il)
+        mark("silu_gate")
 
     # ---- reduction fused into the down projection (peer stores + barrier + slot sum)
 
@@ -162,10 +207,7 @@ class FfnInt4:
             raise ValueError(f"m={m} exceeds max_m={self.max_m}")
         mark = mark or (lambda label: None)
         ops, d, il, h, p = self.ops, self.device, self.i_loc, self.hidden, self.world
-        ops.matmul_int4(d, x, self.w_gu, self.s_gu, self.gu, m, 2 * il, h, GROUP)
-        mark("gate_up")
-        ops.silu_gate_f16(d, self.gu, self.gu.view(-1)[il:], self.act, m, il, x_ld=2 * il, gate_ld=2 * il)
-        mark("silu_gate")
+        self._gate_up_act(x, m, mark)
         if m <= self.m_one:
             off = self.flip * self.one_elems
             self.flip ^= 1
@@ -274,10 +316,7 @@ class FfnInt4:
         chunks = chunks or [m]
         if sum(chunks) != m or min(chunks) < 1:
             raise ValueError(f"chunks {chunks} do not add up to m={m}")
-        ops.matmul_int4(d, x, self.w_gu, self.s_gu, self.gu, m, 2 * il, h, GROUP)
-        mark("gate_up")
-        ops.silu_gate_f16(d, self.gu, self.gu.view(-1)[il:], self.act, m, il, x_ld=2 * il, gate_ld=2 * il)
-        mark("silu_gate")
+        self._gate_up_act(x, m, mark)
         if len(chunks) == 1:
             ops.matmul_int4(d, self.act, self.w_down, self.s_down, self.part_sym, m, h, il, GROUP)
             mark("down")
@@ -377,9 +416,7 @@ class FfnInt4:
         if m > self.max_m:
             raise ValueError(f"m={m} exceeds max_m={self.max_m}")
         ops, d, il = self.ops, self.device, self.i_loc
-        ops.matmul_int4(d, x, self.w_gu, self.s_gu, self.gu, m, 2 * il, self.hidden, GROUP)
-        # row r of gu = [gate(r, 0..il) | up(r, 0..il)]
-        ops.silu_gate_f16(d, self.gu, self.gu.view(-1)[il:], self.act, m, il, x_ld=2 * il, gate_ld=2 * il)
+        self._gate_up_act(x, m, lambda label: None)
         ops.matmul_int4(d, self.act, self.w_down, self.s_down, self.out, m, self.hidden, il, GROUP)
         return self.out[: m * self.hidden].view(m, self.hidden)
 

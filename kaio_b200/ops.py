@@ -209,6 +209,19 @@ def sum_partials_f32_multicast(device, slots, world, rows, cols, multicast_out, 
           C.c_void_p(int(multicast_out)), C.c_size_t(out_numel), out_ld, out_col0)
 
 
+def matmul_int4_silu_gate(device, x, b_packed, scales, act, gu_scratch, m, cols, k, group_size=GROUP_SIZE):
+    """Extension: ``act[m, cols] = silu(x W_gate) * (x W_up)`` from W4A16 weights ``[k, 2*cols]`` whose
+    columns alternate in blocks of 64 between ``W_gate`` and ``W_up`` (see
+    :func:`kaio_b200.ffn.interleave_gate_up`); the activation runs in the GEMM's epilogue for m > 512."""
+    if gu_scratch is None:
+        scratch = (C.c_void_p(None), C.c_size_t(0))
+    else:
+        scratch = _buf(gu_scratch, torch.float16, "gu_scratch")
+    _call(device, "kaio_b200_matmul_int4_silu_gate", *_buf(x, torch.float16, "x"),
+          *_buf(b_packed, torch.int32, "b_packed"), *_buf(scales, torch.float16, "scales"),
+          *_buf(act, torch.float16, "act"), *scratch, m, cols, k, group_size)
+
+
 def allreduce_multimem_f32(device, multicast_in, multicast_out, numel, rows, cols, ld, col0):
     """Extension: this rank's column block ``[col0, col0 + cols)`` of an in-switch all-reduce
     (``multimem.ld_reduce`` + ``multimem.st``) over multicast addresses of symmetric buffers."""

@@ -90,6 +90,28 @@ def test_concat_gate_up_is_the_packing_of_the_concatenated_matrix(oracle):
     assert torch.equal(scales.view(k // 128, 2 * n), torch.cat([sg.view(-1, n), su.view(-1, n)], dim=1))
 
 
+def test_interleave_gate_up_is_the_packing_of_the_interleaved_matrix(oracle):
+    """Blocks of 64 gate columns alternate with the same columns of up: the layout of the fused
+    gate|up + SiLU-gate GEMM."""
+    k, n = 256, 128
+    wg = oracle.lcg_s4(3, k * n).reshape(k, n)
+    wu = oracle.lcg_s4(4, k * n).reshape(k, n)
+    sg = torch.arange((k // 128) * n, dtype=torch.float32).to(torch.float16)
+    su = (torch.arange((k // 128) * n, dtype=torch.float32) + 1000).to(torch.float16)
+    w_gu, s_gu = ffn.concat_gate_up(torch.from_numpy(oracle.pack_s4(wg, k, n).view(np.int32)), sg,
+                                    torch.from_numpy(oracle.pack_s4(wu, k, n).view(np.int32)), su, k, n)
+    packed, scales = ffn.interleave_gate_up(w_gu, s_gu, k, n)
+    dense = np.concatenate([np.concatenate([wg[:, b:b + 64], wu[:, b:b + 64]], axis=1) for b in range(0, n, 64)], axis=1)
+    assert np.array_equal(packed.numpy(), oracle.pack_s4(np.ascontiguousarray(dense), k, 2 * n).view(np.int32))
+    sgm, sum_ = sg.view(-1, n), su.view(-1, n)
+    want_s = torch.cat([torch.cat([sgm[:, b:b + 64], sum_[:, b:b + 64]], dim=1) for b in range(0, n, 64)], dim=1)
+    assert torch.equal(scales.view(k // 128, 2 * n), want_s)
+    idx = ffn.interleave_index(n)
+    assert sorted(idx.tolist()) == list(range(2 * n))
+    with pytest.raises(ValueError):
+        ffn.interleave_index(96)
+
+
 # ---------------------------------------------------------------- the chain over gloo
 
 class OracleOps:

@@ -220,3 +220,45 @@ def test_chunked_chain_equals_the_whole_chain(oracle):
     want = ffn_oracle(oracle, case, hidden, inter, m)
     assert max_rel(parts.cpu().numpy(), want) < 1e-2
     assert ffn.FfnInt4.default_chunks(4096) == [2048, 1280, 768] and ffn.FfnInt4.default_chunks(512) == [512]
+
+
+@pytest.mark.parametrize("hidden,inter,m", [(256, 512, 16), (512, 1024, 300), (512, 1024, 640), (1024, 2048, 1500)])
+def test_silu_gate_in_the_gemm_epilogue_gives_the_same_bits(oracle, hidden, inter, m):
+    """``matmul_int4_silu_gate`` (activation in the GEMM epilogue above m = 512, two launches through
+    the caller's scratch below) against the two separate ops it replaces: the same bits in the
+    activation and at the end of the chain; the chain stays within the oracle's bar."""
+    case = make_ffn_case(oracle, hidden, inter, m, seed=7 * hidden + m)
+    weights = [case[n] for n in ("w_gate", "s_gate", "w_up", "s_up", "w_down", "s_down")]
+    chain = ffn.FfnInt4(ops, device(), hidden, inter, *weights, max_m=max(m, 16))
+    x = case["x"].cuda()
+    plain = chain.run(x, m).clone()
+    act_plain = chain.act[: m * inter].clone()
+    chain.enable_fused_silu()
+    chain.act.zero_()
+    fused = chain.run(x, m).clone()
+    torch.cuda.synchronize()
+    assert ops.device_status(device())[0] == 0
+    assert torch.equal(chain.act[: m * inter].view(torch.int16), act_plain.view(torch.int16))
+    assert torch.equal(fused.view(torch.int32), plain.view(torch.int32))
+    assert max_rel(host(fused), ffn_oracle(oracle, case, hidden, inter, m)) < 1e-2
+    # the entry point itself: above 512 rows one launch and no scratch
+    act = torch.zeros(m * inter, device="cuda", dtype=torch.float16)
+    ops.matmul_int4_silu_gate(device(), x, chain.w_gu_il, chain.s_gu_il, act, None if m > 512 else chain.gu,
+                              m, inter, hidden)
+    assert ops.last_variant() == ("w4a16_tcgen05_silu_gate" if m > 512 else "w4a16_then_silu_gate")
+    assert torch.equal(act.view(torch.int16), act_plain.view(torch.int16))
+
+
+def test_silu_gate_gemm_argument_errors():
+    d = device()
+    k, cols, m = 128, 64, 4
+    x = torch.zeros(m * k, device="cuda", dtype=torch.float16)
+    w = torch.zeros((k // 8) * 2 * cols, device="cuda", dtype=torch.int32)
+    s = torch.zeros(2 * cols, device="cuda", dtype=torch.float16)
+    act = torch.zeros(m * cols, device="cuda", dtype=torch.float16)
+    with pytest.raises(InvalidConfig, match="multiple of 64"):
+        ops.matmul_int4_silu_gate(d, x, w, s, act, None, m, 32, k)
+    with pytest.raises(InvalidConfig, match="act buffer too small"):
+        ops.matmul_int4_silu_gate(d, x, w, s, act[:8], None, m, cols, k)
+    with pytest.raises(InvalidConfig, match="needs a 16-byte aligned scratch"):
+        ops.matmul_int4_silu_gate(d, x, w, s, act, None, m, cols, k)
