@@ -1391,6 +1391,9 @@ KAIO_API int32_t kaio_b200_matmul_int4_peer_partials(const kaio_f16* a, size_t a
     copies.count = world;
     copies.ld = cols;
     copies.scatter_cols = scatter ? cols : 0u;
+    // start the walk at the next rank's block: the ranks then store to different owners at any
+    // one time, and this rank's own block (local stores) comes last
+    copies.start_col = scatter ? ((rank + 1) % world) * cols : 0u;
     for (uint32_t r = 0; r < world; ++r) {
         if (slot_ptrs[r] == nullptr || (uintptr_t)slot_ptrs[r] % 16 != 0)
             return fail(KAIO_B200_ERR_INVALID_CONFIG,

@@ -73,6 +73,7 @@ struct Params {
     uint32_t copies;  // each output block is stored to `copies` tensor maps (out[prob*copies + r])
     uint32_t scatter_cols;  // > 0: a block goes only to map col0 / scatter_cols (see OutputCopies)
     uint32_t m, n, k;
+    uint32_t nt_rot;  // the walk over the column tiles starts at tile nt_rot (see OutputCopies)
     int post_scale;
     int silu_gate;  // f16 out only: column blocks of 64 alternate between two projections a, b;
                     // the epilogue stores silu(f16(a)) * f16(b) as [m, n/2]
@@ -165,7 +166,10 @@ f16_gemm_kernel(const __grid_constant__ TensorMaps maps, const Params p)
         const uint32_t gm = (tiles_m - g * RASTER_GM) < RASTER_GM ? (tiles_m - g * RASTER_GM) : RASTER_GM;
         const uint32_t nt = rem / gm, mi = rem - nt * gm;
         m0 = (g * RASTER_GM + mi) * C::BM + rank * BM_CTA;
-        n0 = nt * BN;
+        uint32_t ntr = nt + p.nt_rot;
+        if (ntr >= tiles_n)
+            ntr -= tiles_n;
+        n0 = ntr * BN;
     };
 
     if (warp == 0) {
@@ -717,6 +721,7 @@ cudaError_t launch_dq_gemm(const DeviceCtx& ctx, int wfmt, const __half* x, cons
     p.n = n;
     p.k = k;
     p.post_scale = post_scale ? 1 : 0;
+    p.nt_rot = copies ? (copies->start_col / BN) % ((n + BN - 1) / BN) : 0u;
     p.silu_gate = silu_gate ? 1 : 0;
     p.status = ctx.status;
     if (pair)

@@ -111,6 +111,12 @@ struct OutputCopies {
     // > 0: column c is stored only to destination c / scatter_cols, at column c % scatter_cols
     // (each destination receives one block of columns: the reduce-scatter form).
     uint32_t scatter_cols;
+    // Column at which this caller starts its walk over the output (the paired f16 GEMM honours it;
+    // the small-M kernels ignore it).  In the scatter form every rank works through the same
+    // tiles: started at the same column they would all store to the same owner at the same time
+    // and that owner's NVLink ingress would set the pace; started one block apart, each owner
+    // receives from one or two ranks at a time.  The tiles and their results do not change.
+    uint32_t start_col;
 };
 
 size_t dq_gemm_workspace_bytes(int num_probs, uint32_t n, uint32_t k);
