@@ -787,6 +787,7 @@ def bench_ffn70b(torch, dist, ops, sharding, dev, rank, world):
             variant = ops.last_variant()
             t_all = _time_ms(torch, both, iters) if world > 1 else t_gemm
             t_fused = t_all
+            fused_variant = None
             if world > 1:
                 # one kernel per rank: the epilogue stores into every rank's buffer (peer memory)
                 fused = sharding.FusedGatherGemm(ops, dev, mm, n, k, world, rank)
@@ -796,13 +797,14 @@ def bench_ffn70b(torch, dist, ops, sharding, dev, rank, world):
                     fused.run(a, w, sc)
 
                 t_fused = _time_ms(torch, run_fused, iters)
-                if mm <= 256:
-                    name = f"cfg5_k{k}_n{n}_m{mm}"
-                    ok = _check_gather(torch, dist, ops, np, dev, rank, world, fused, gather, a, c, sets[0],
-                                       mm, n, k)
-                    checked.append(name)
-                    if not ok:
-                        failed.append(name)
+                fused_variant = ops.last_variant()
+                # checked at every M: the multicast epilogue serves only the large ones
+                name = f"cfg5_k{k}_n{n}_m{mm}"
+                ok = _check_gather(torch, dist, ops, np, dev, rank, world, fused, gather, a, c, sets[0],
+                                   mm, n, k)
+                checked.append(name)
+                if not ok:
+                    failed.append(name)
                 del fused
             t_gemm, t_all, t_fused = _max_over_ranks(torch, dist, world, [t_gemm, t_all, t_fused])
             best = min(t_all, t_fused)
@@ -811,7 +813,8 @@ def bench_ffn70b(torch, dist, ops, sharding, dev, rank, world):
             res[f"k{k}_n{n}_m{mm}"] = {
                 "ms_gemm": t_gemm, "ms_gemm_plus_gather": t_all, "ms_fused_peer_store": t_fused,
                 "tflops": flops / best / 1e9, "weight_stream_gbs": nbytes / best / 1e6,
-                "weight_sets_cycled": rotate, "variant": variant}
+                "weight_sets_cycled": rotate, "variant": variant,
+                "fused_variant": fused_variant if world > 1 else None}
             del a, c, gather
         del sets
         torch.cuda.empty_cache()

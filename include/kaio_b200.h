@@ -158,6 +158,17 @@ int32_t kaio_b200_matmul_int4_allgather(const kaio_f16* a, size_t a_len,
                                         uint32_t rank, uint32_t m, uint32_t n_total, uint32_t k,
                                         uint32_t group_size, void* stream);
 
+/* The same with the rows above m = 512 written through an NVLink multicast object: multicast_out
+ * is the multicast address of the [m, n_total] output that every rank's buffer is bound to (e.g.
+ * the multicast pointer of a torch symmetric-memory allocation).  The paired GEMM then stores each
+ * output block once as `multimem.st` and the switch delivers it to all ranks (1/world of the
+ * egress).  Smaller m use out_ptrs as above, which therefore stay required. */
+int32_t kaio_b200_matmul_int4_allgather_multicast(
+    const kaio_f16* a, size_t a_len, const uint32_t* b_packed_shard, size_t b_len,
+    const kaio_f16* scales_shard, size_t scales_len, void* const* out_ptrs, size_t out_len,
+    void* multicast_out, uint32_t world, uint32_t rank, uint32_t m, uint32_t n_total, uint32_t k,
+    uint32_t group_size, void* stream);
+
 /* Extension (no reference counterpart; KAIO is single-device): the all-gather of a column-parallel
  * GEMM's output through NCCL.  Every rank passes its [m, n_total / world] shard (row-major,
  * elem_bytes = 2 for f16 or 4 for f32) and receives the row-major [m, n_total] matrix in `out`.

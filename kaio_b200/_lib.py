@@ -30,6 +30,8 @@ SIGNATURES = {
     "kaio_b200_matmul_int4_noalloc": [_VP, _SZ, _VP, _SZ, _VP, _SZ, _VP, _SZ, _U32, _U32, _U32, _U32, _VP],
     "kaio_b200_matmul_int4_allgather": [_VP, _SZ, _VP, _SZ, _VP, _SZ, _VP, _SZ, _U32, _U32, _U32, _U32, _U32,
                                         _U32, _VP],
+    "kaio_b200_matmul_int4_allgather_multicast": [_VP, _SZ, _VP, _SZ, _VP, _SZ, _VP, _SZ, _VP, _U32, _U32, _U32,
+                                                  _U32, _U32, _U32, _VP],
     "kaio_b200_allgather_cols": [_VP, _SZ, _VP, _SZ, _U32, _U32, _U32, _U32, _VP, _VP],
     "kaio_b200_matmul_int4_f16out": [_VP, _SZ, _VP, _SZ, _VP, _SZ, _VP, _SZ, _U32, _U32, _U32, _U32, _VP],
     "kaio_b200_qkv_project_int8": [_VP, _SZ, _VP, _SZ, _VP, _SZ, _VP, _SZ, _F32, _F32, _F32,

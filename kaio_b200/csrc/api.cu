@@ -1227,15 +1227,13 @@ KAIO_API int32_t kaio_b200_quantize_pack_int4(const float* w, size_t w_len, uint
 }
 
 // ---------------------------------------------------------------- sharded W4A16 + all-gather
-KAIO_API int32_t kaio_b200_matmul_int4_allgather(const kaio_f16* a, size_t a_len,
-                                                 const uint32_t* b_packed_shard, size_t b_len,
-                                                 const kaio_f16* scales_shard, size_t scales_len,
-                                                 void* const* out_ptrs, size_t out_len,
-                                                 uint32_t world, uint32_t rank, uint32_t m,
-                                                 uint32_t n_total, uint32_t k, uint32_t group_size,
-                                                 void* stream)
+static int32_t run_int4_allgather(const char* op, const kaio_f16* a, size_t a_len,
+                                  const uint32_t* b_packed_shard, size_t b_len,
+                                  const kaio_f16* scales_shard, size_t scales_len,
+                                  void* const* out_ptrs, size_t out_len, void* multicast_out,
+                                  uint32_t world, uint32_t rank, uint32_t m, uint32_t n_total,
+                                  uint32_t k, uint32_t group_size, void* stream)
 {
-    const char* op = "matmul_int4_allgather";
     if (world == 0 || world > 8 || rank >= world)
         return fail(KAIO_B200_ERR_INVALID_CONFIG, "%s: world must be 1..8 and rank < world (got %u, %u)",
                     op, world, rank);
@@ -1264,6 +1262,11 @@ KAIO_API int32_t kaio_b200_matmul_int4_allgather(const kaio_f16* a, size_t a_len
             return fail(KAIO_B200_ERR_INVALID_CONFIG,
                         "%s: output pointer %u is null or not 16-byte aligned", op, r);
         copies.ptrs[r] = reinterpret_cast<kaio_f16*>(out_ptrs[r]) + (size_t)rank * n_loc;
+    }
+    if (multicast_out != nullptr) {
+        if ((uintptr_t)multicast_out % 16 != 0)
+            return fail(KAIO_B200_ERR_INVALID_CONFIG, "%s: multicast address is not 16-byte aligned", op);
+        copies.multicast = reinterpret_cast<kaio_f16*>(multicast_out) + (size_t)rank * n_loc;
     }
     DeviceCtx* ctx;
     if ((rc = get_ctx(&ctx)))
@@ -1301,7 +1304,32 @@ KAIO_API int32_t kaio_b200_matmul_int4_allgather(const kaio_f16* a, size_t a_len
         return rc;
     return finish(launch_dq_gemm(*ctx, WFMT_S4_PACKED, x, &pr, 1, true, false, m, n_loc, k,
                                  sc->dq_workspace, s, &copies),
-                  op, "w4a16_tcgen05_allgather");
+                  op, multicast_out ? "w4a16_tcgen05_allgather_multicast" : "w4a16_tcgen05_allgather");
+}
+
+KAIO_API int32_t kaio_b200_matmul_int4_allgather(const kaio_f16* a, size_t a_len,
+                                                 const uint32_t* b_packed_shard, size_t b_len,
+                                                 const kaio_f16* scales_shard, size_t scales_len,
+                                                 void* const* out_ptrs, size_t out_len,
+                                                 uint32_t world, uint32_t rank, uint32_t m,
+                                                 uint32_t n_total, uint32_t k, uint32_t group_size,
+                                                 void* stream)
+{
+    return run_int4_allgather("matmul_int4_allgather", a, a_len, b_packed_shard, b_len, scales_shard,
+                              scales_len, out_ptrs, out_len, nullptr, world, rank, m, n_total, k,
+                              group_size, stream);
+}
+
+KAIO_API int32_t kaio_b200_matmul_int4_allgather_multicast(
+    const kaio_f16* a, size_t a_len, const uint32_t* b_packed_shard, size_t b_len,
+    const kaio_f16* scales_shard, size_t scales_len, void* const* out_ptrs, size_t out_len,
+    void* multicast_out, uint32_t world, uint32_t rank, uint32_t m, uint32_t n_total, uint32_t k,
+    uint32_t group_size, void* stream)
+{
+    const char* op = "matmul_int4_allgather_multicast";
+    REQUIRE_PTR(multicast_out, op, "multicast_out");
+    return run_int4_allgather(op, a, a_len, b_packed_shard, b_len, scales_shard, scales_len, out_ptrs,
+                              out_len, multicast_out, world, rank, m, n_total, k, group_size, stream);
 }
 
 // ---------------------------------------------------------------- NCCL all-gather of column shards

@@ -74,6 +74,8 @@ struct Params {
     uint32_t scatter_cols;  // > 0: a block goes only to map col0 / scatter_cols (see OutputCopies)
     uint32_t m, n, k;
     uint32_t nt_rot;  // the walk over the column tiles starts at tile nt_rot (see OutputCopies)
+    void* mc_out;     // non-null: multicast address of the output (see OutputCopies::multicast)
+    uint64_t mc_ld;   // its row stride in elements
     int post_scale;
     int silu_gate;  // f16 out only: column blocks of 64 alternate between two projections a, b;
                     // the epilogue stores silu(f16(a)) * f16(b) as [m, n/2]
@@ -388,7 +390,31 @@ f16_gemm_kernel(const __grid_constant__ TensorMaps maps, const Params p)
                         make_uint4(stg[4 * j], stg[4 * j + 1], stg[4 * j + 2], stg[4 * j + 3]);
                 fence_proxy_async_smem();
                 __syncwarp();
-                if (lane == 0) {
+                if (p.mc_out != nullptr) {
+                    // all destinations at once: the staged block goes out as 16-byte multimem
+                    // stores (8 lanes = one 128-byte row, 4 rows per instruction) and the switch
+                    // copies it into every rank's buffer
+                    constexpr uint32_t ELEM = OUT_F16 ? 2 : 4;
+                    uint8_t* const mc = reinterpret_cast<uint8_t*>(p.mc_out);
+#pragma unroll
+                    for (uint32_t it = 0; it < 8; ++it) {
+                        const uint32_t row = it * 4 + (lane >> 3), chunk = lane & 7u;
+                        const uint32_t grow = m0 + quarter * 32 + row;
+                        const uint32_t gcol = col0 + chunk * (16 / ELEM);
+                        if (grow < p.m && gcol < p.n) {
+                            const uint4 v = *reinterpret_cast<const uint4*>(
+                                stg_gen + stg_off + sw128_offset(row, chunk));
+                            asm volatile(
+                                "multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                                :
+                                : "l"(mc + ((size_t)grow * p.mc_ld + gcol) * ELEM),
+                                  "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)),
+                                  "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+                                : "memory");
+                        }
+                    }
+                    __syncwarp();  // the block has been read out before the buffer is staged again
+                } else if (lane == 0) {
                     // one store per destination: with the sharded all-gather the destinations are
                     // the [M, N] buffers of every rank (peer memory), so the transfer overlaps the
                     // GEMM tile by tile
@@ -722,6 +748,8 @@ cudaError_t launch_dq_gemm(const DeviceCtx& ctx, int wfmt, const __half* x, cons
     p.k = k;
     p.post_scale = post_scale ? 1 : 0;
     p.nt_rot = copies ? (copies->start_col / BN) % ((n + BN - 1) / BN) : 0u;
+    p.mc_out = (copies && !copies->scatter_cols && !silu_gate) ? copies->multicast : nullptr;
+    p.mc_ld = copies ? copies->ld : 0;
     p.silu_gate = silu_gate ? 1 : 0;
     p.status = ctx.status;
     if (pair)

@@ -117,6 +117,11 @@ struct OutputCopies {
     // and that owner's NVLink ingress would set the pace; started one block apart, each owner
     // receives from one or two ranks at a time.  The tiles and their results do not change.
     uint32_t start_col;
+    // Non-null: an address of an NVLink multicast object that all destinations' buffers are bound
+    // to (already offset to this caller's first column, row stride ld).  The paired f16 GEMM then
+    // writes every output block ONCE with multimem.st and the switch delivers it to all ranks
+    // (1/count of the egress); ptrs[] stay valid for the kernels that do not take this path.
+    void* multicast;
 };
 
 size_t dq_gemm_workspace_bytes(int num_probs, uint32_t n, uint32_t k);

@@ -169,6 +169,18 @@ def matmul_int4_allgather(device, a, b_packed_shard, scales_shard, out_ptrs, out
           C.cast(arr, C.c_void_p), C.c_size_t(out_numel), world, rank, m, n_total, k, group_size)
 
 
+def matmul_int4_allgather_multicast(device, a, b_packed_shard, scales_shard, out_ptrs, out_numel, multicast_out,
+                                    world, rank, m, n_total, k, group_size=GROUP_SIZE):
+    """Extension: :func:`matmul_int4_allgather` whose large-``m`` kernel writes each output block once
+    through ``multicast_out``, the NVLink multicast address of the ``[m, n_total]`` output
+    (``multimem.st``; the switch delivers it to every rank)."""
+    arr = (C.c_void_p * world)(*[C.c_void_p(int(p)) for p in out_ptrs])
+    _call(device, "kaio_b200_matmul_int4_allgather_multicast", *_buf(a, torch.float16, "a"),
+          *_buf(b_packed_shard, torch.int32, "b_packed_shard"), *_buf(scales_shard, torch.float16, "scales_shard"),
+          C.cast(arr, C.c_void_p), C.c_size_t(out_numel), C.c_void_p(int(multicast_out)), world, rank, m, n_total,
+          k, group_size)
+
+
 def allgather_cols(device, shard, out, m, n_total, world, nccl_comm):
     """Extension: NCCL all-gather of ``[m, n_total/world]`` column shards into the row-major
     ``[m, n_total]`` ``out`` on every rank, through the C ABI.  ``nccl_comm`` is the raw

@@ -12,6 +12,8 @@ GPUs).
 """
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -102,9 +104,19 @@ class FusedGatherGemm:
         self.handle = symm_mem.rendezvous(self.flat, group if group is not None else dist.group.WORLD)
         self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
         self.out = self.flat.view(m, n)
+        # Where torch binds the symmetric buffers to an NVLink multicast object the large-m kernel
+        # writes each output block once through it (KAIO_B200_MULTICAST=0 keeps per-rank stores).
+        self.multicast = 0
+        if os.environ.get("KAIO_B200_MULTICAST", "1") != "0":
+            self.multicast = int(getattr(self.handle, "multicast_ptr", 0) or 0)
 
     def run(self, a, w_packed_shard, scales_shard):
-        self.ops.matmul_int4_allgather(self.device, a, w_packed_shard, scales_shard, self.ptrs,
-                                       self.m * self.n, self.world, self.rank, self.m, self.n, self.k)
+        if self.multicast:
+            self.ops.matmul_int4_allgather_multicast(self.device, a, w_packed_shard, scales_shard, self.ptrs,
+                                                     self.m * self.n, self.multicast, self.world, self.rank,
+                                                     self.m, self.n, self.k)
+        else:
+            self.ops.matmul_int4_allgather(self.device, a, w_packed_shard, scales_shard, self.ptrs,
+                                           self.m * self.n, self.world, self.rank, self.m, self.n, self.k)
         self.handle.barrier()  # every rank's stores have landed before anyone reads
         return self.out

@@ -75,7 +75,9 @@ def test_fused_gather_two_ranks():
         pytest.skip("needs 2 GPUs")
     import torch.multiprocessing as mp
     world = 2
-    shapes = [(16, 1024, 512), (300, 2048, 1024)]
+    # the last two run the paired GEMM (m > 512), whose epilogue writes through the NVLink multicast
+    # object where there is one; ragged rows and a shard width that is not a multiple of the tile
+    shapes = [(16, 1024, 512), (300, 2048, 1024), (640, 2048, 1024), (700, 2080, 512)]
     mgr = mp.Manager()
     ret = mgr.dict()
     mp.spawn(_worker, args=(world, _free_port(), shapes, ret), nprocs=world, join=True)
