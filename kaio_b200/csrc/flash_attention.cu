@@ -87,22 +87,39 @@ __device__ __forceinline__ float ex2_approx(float x)
     return y;
 }
 
-// 2^x on the FMA pipe, for the share of the exponentials taken off the special-function unit
-// (16 results per clock per SM there; one of every four elements goes this way).  Round-to-nearest
-// split x = n + f through the 1.5 * 2^23 constant, degree-4 minimax polynomial for 2^f on
-// [-0.5, 0.5] (relative error 2.7e-6, far below the f16 rounding of P), n added to the exponent
-// field.  x <= 16 here; anything below -125 (masked scores are -inf) gives ~2^-125.
-__device__ __forceinline__ float ex2_poly(float x)
+// Packed f32 pairs (sm_100: one instruction, two f32 operations) and the three-input max: the
+// softmax warps are bound by instruction issue, not by a pipe.
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi)
 {
-    x = fmaxf(x, -125.0f);
-    const float t = x + 12582912.0f;
-    const float f = x - (t - 12582912.0f);
-    float q = 9.574016556e-03f;
-    q = fmaf(q, f, 5.591819063e-02f);
-    q = fmaf(q, f, 2.402464896e-01f);
-    q = fmaf(q, f, 6.931217313e-01f);
-    q = fmaf(q, f, 9.999992847e-01f);
-    return __int_as_float(__float_as_int(q) + (__float_as_int(t) << 23));
+    uint64_t v;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
+    return v;
+}
+
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi)
+{
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c)
+{
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b)
+{
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
+__device__ __forceinline__ float max3_f32(float a, float b, float c)
+{
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
 }
 
 __device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_t (&r)[16])
@@ -425,11 +442,11 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
             // ---- pass 1: block maximum of the raw scores (the scale is positive: scale after)
             float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {  // four independent chains
-                mx0 = fmaxf(mx0, __uint_as_float(r0[i]));
-                mx1 = fmaxf(mx1, __uint_as_float(r1[i]));
-                mx2 = fmaxf(mx2, __uint_as_float(r2[i]));
-                mx3 = fmaxf(mx3, __uint_as_float(r3[i]));
+            for (int i = 0; i < 32; i += 2) {  // four independent chains, two scores per instruction
+                mx0 = max3_f32(mx0, __uint_as_float(r0[i]), __uint_as_float(r0[i + 1]));
+                mx1 = max3_f32(mx1, __uint_as_float(r1[i]), __uint_as_float(r1[i + 1]));
+                mx2 = max3_f32(mx2, __uint_as_float(r2[i]), __uint_as_float(r2[i + 1]));
+                mx3 = max3_f32(mx3, __uint_as_float(r3[i]), __uint_as_float(r3[i + 1]));
             }
             const float m_blk = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
             // ---- lazy rescale: keep the old reference while P = 2^(s - m_ref) stays inside f16
@@ -452,19 +469,23 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
             }
             // ---- pass 2: p = 2^(s * scale - m_ref), row sum, f16 pairs into tensor memory.  P
             // overwrites the first 64 columns of S, which are all in registers by now.
-            float ls0 = 0.0f, ls1 = 0.0f, ls2 = 0.0f, ls3 = 0.0f;
+            // two scores per FMA and per add (packed f32x2); the exponentials stay scalar (MUFU)
+            uint64_t lsa = 0, lsb = 0;  // packed row-sum accumulators (two chains)
+            const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2);
+            const uint64_t nref2 = pack_f32x2(-m_ref, -m_ref);
             auto exp_chunk = [&](const uint32_t (&r)[32], uint32_t c) {
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 4) {
-                    const float p0 = ex2_approx(fmaf(__uint_as_float(r[i]), p.scale_log2, -m_ref));
-                    const float p1 = ex2_approx(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -m_ref));
-                    const float p2 = ex2_approx(fmaf(__uint_as_float(r[i + 2]), p.scale_log2, -m_ref));
-                    const float p3 = ex2_poly(fmaf(__uint_as_float(r[i + 3]), p.scale_log2, -m_ref));
-                    ls0 += p0;
-                    ls1 += p1;
-                    ls2 += p2;
-                    ls3 += p3;
+                    float x0, x1, x2, x3;
+                    unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])),
+                                           scale2, nref2), x0, x1);
+                    unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])),
+                                           scale2, nref2), x2, x3);
+                    const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+                    const float p2 = ex2_approx(x2), p3 = ex2_approx(x3);
+                    lsa = add_f32x2(lsa, pack_f32x2(p0, p1));
+                    lsb = add_f32x2(lsb, pack_f32x2(p2, p3));
                     const __half2 h01 = __floats2half2_rn(p0, p1);
                     const __half2 h23 = __floats2half2_rn(p2, p3);
                     pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&h01);
@@ -504,7 +525,12 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
             }
             exp_chunk(r2, 2);
             exp_chunk(r3, 3);
-            l_sum += (ls0 + ls1) + (ls2 + ls3);
+            {
+                float a0, a1, b0, b1;
+                unpack_f32x2(lsa, a0, a1);
+                unpack_f32x2(lsb, b0, b1);
+                l_sum += (a0 + a1) + (b0 + b1);
+            }
             tmem_st_wait();
             if (rescale) {
                 // Some row of this warp moved its reference: O_t (last written by the P V of block
