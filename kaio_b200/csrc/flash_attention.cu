@@ -7,7 +7,11 @@
 // in shared memory, seq_k <= 384) and adds the batched multi-head form that reads Q/K/V in place
 // from [batch*seq, heads*128] projection outputs.
 //
-// One CTA per (batch, head, 256 query rows) = two query tiles of 128 rows, 320 threads:
+// Persistent: one CTA per SM walks the work items (batch, head, 256 query rows), heaviest first;
+// Q loads, the fill of the K/V ring and the first scores of the next item overlap the softmax tail
+// and the output of the current one, and tensor memory and barriers are set up once.  (One CTA per
+// item spent about a quarter of its time in launch, set-up, pipeline fill and output.)
+// An item = two query tiles of 128 rows; 320 threads:
 //   warp 0     TMA producer: Q once (four [128][64] boxes), then K and V blocks ([128 kv][128 d] as
 //              two 64-column boxes each) through a 2-stage ring; 128-byte swizzle.
 //   warp 1     MMA issuer (converged warp, elected lane), for tile t in {0, 1}:
@@ -79,6 +83,41 @@ struct Params {
 struct TensorMaps {
     CUtensorMap q, k, v;
 };
+
+// One work item = (batch, head, 256 query rows).  Items are numbered heaviest first (causal: the
+// last query block of every (batch, head), then the one before, ...), and CTA c takes items c,
+// c + gridDim.x, ...: every CTA gets one item of each weight class.
+struct Item {
+    uint32_t b, h, q0;
+    uint32_t nkv0, nkv1;  // KV blocks each query tile attends to (0 for a tile beyond seq_q)
+    uint32_t num_kv;
+};
+
+__device__ __forceinline__ Item make_item(const Params& p, uint32_t it)
+{
+    const uint32_t num_qb = (p.seq_q + 2 * BQ - 1) / (2 * BQ);
+    const uint32_t bh_count = p.batch * p.heads;
+    const uint32_t tier = it / bh_count, bh = it - tier * bh_count;
+    Item im;
+    im.b = bh / p.heads;
+    im.h = bh - im.b * p.heads;
+    im.q0 = (num_qb - 1 - tier) * 2 * BQ;
+    uint32_t nkv[2];
+#pragma unroll
+    for (uint32_t t = 0; t < 2; ++t) {
+        const uint32_t tq0 = im.q0 + t * BQ;
+        uint32_t kv_end = p.seq_k;
+        if (p.causal) {
+            const uint32_t lim = tq0 + BQ;  // columns j <= i < tq0 + BQ
+            kv_end = lim < kv_end ? lim : kv_end;
+        }
+        nkv[t] = tq0 < p.seq_q ? (kv_end + BKV - 1) / BKV : 0u;
+    }
+    im.nkv0 = nkv[0];
+    im.nkv1 = nkv[1];
+    im.num_kv = nkv[0] > nkv[1] ? nkv[0] : nkv[1];
+    return im;
+}
 
 __device__ __forceinline__ float ex2_approx(float x)
 {
@@ -167,17 +206,6 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, ui
         : "memory");
 }
 
-#ifdef KAIO_TRACE
-// Development aid (never compiled into the shipped library): cycle stamps [cta][block < 20][8].
-__device__ unsigned long long* g_fa_trace = nullptr;
-#define FA_STAMP(j, slot)                                              \
-    do {                                                               \
-        if (trace_ptr && (j) < 20)                                     \
-            trace_ptr[(j) * 8 + (slot)] = clock64();                   \
-    } while (0)
-#else
-#define FA_STAMP(j, slot) do { } while (0)
-#endif
 
 // Three warps share a scheduler's 16 K registers: at most 168 per thread.
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -197,38 +225,28 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
     auto p_lo = [&](uint32_t b) { return bar_base + 8u * (7 + b); };   // P of kv 0-63 stored
     auto p_hi = [&](uint32_t b) { return bar_base + 8u * (9 + b); };   // P of kv 64-127 stored
     auto pv_done = [&](uint32_t b) { return bar_base + 8u * (11 + b); };
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 13);
+    const uint32_t q_empty = bar_base + 8u * 13;  // the item's last Q K^T has read Q
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 14);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
-#ifdef KAIO_TRACE
-    unsigned long long* const trace_ptr =
-        g_fa_trace ? g_fa_trace + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 160 : nullptr;
-#endif
 
-    // heavy (late, causal) query blocks first
-    const uint32_t num_qb = (p.seq_q + 2 * BQ - 1) / (2 * BQ);
-    const uint32_t qb = num_qb - 1 - blockIdx.x;
-    const uint32_t bh = blockIdx.y;
-    const uint32_t b = bh / p.heads, h = bh % p.heads;
-    const uint32_t q0 = qb * 2 * BQ;
-    // KV blocks each query tile attends to (0 for a tile that lies beyond seq_q)
-    uint32_t nkv[2];
-#pragma unroll
-    for (uint32_t t = 0; t < 2; ++t) {
-        const uint32_t tq0 = q0 + t * BQ;
-        uint32_t kv_end = p.seq_k;
-        if (p.causal) {
-            const uint32_t lim = tq0 + BQ;  // columns j <= i < tq0 + BQ
-            kv_end = lim < kv_end ? lim : kv_end;
-        }
-        nkv[t] = tq0 < p.seq_q ? (kv_end + BKV - 1) / BKV : 0u;
-    }
-    const uint32_t num_kv = nkv[0] > nkv[1] ? nkv[0] : nkv[1];
+    // Persistent CTA: all barrier phases run on through the items (counters, not item-local
+    // indices, give the parities); K/V of the next item stream in behind the current one's, its Q
+    // lands while the softmax warps finish and write out the current item.
+    const uint32_t total_items = ((p.seq_q + 2 * BQ - 1) / (2 * BQ)) * p.batch * p.heads;
+    // Round r hands item r * G + c to CTA c in even rounds and to CTA G - 1 - c in odd ones: with the
+    // items sorted by weight the CTAs' totals stay within ~1 % of each other (plain round robin:
+    // 6 % at config 4), as good as a greedy assignment.
+    auto item_of = [&](uint32_t round) {
+        const uint32_t c = (round & 1u) ? gridDim.x - 1 - blockIdx.x : blockIdx.x;
+        return round * gridDim.x + c;
+    };
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
+        mbar_init(q_empty, 1);
         for (uint32_t s = 0; s < KV_STAGES; ++s) {
             mbar_init(kv_full(s), 1);
             mbar_init(kv_empty(s), 1);
@@ -256,43 +274,59 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
-        const int32_t col0 = (int32_t)(h * D);
-        const int32_t q_row = (int32_t)(b * p.seq_q + q0);
-        if (elect_one()) {
-            mbar_expect_tx(q_full, Q_BYTES);
-#pragma unroll
-            for (int t = 0; t < 2; ++t) {
-                tma_load_2d(q_smem + t * Q_TILE_BYTES, &maps.q, q_full, col0, q_row + t * BQ);
-                tma_load_2d(q_smem + t * Q_TILE_BYTES + SUB_BYTES, &maps.q, q_full, col0 + 64,
-                            q_row + t * BQ);
-            }
-        }
-        __syncwarp();
-        for (uint32_t j = 0; j < num_kv; ++j) {
-            const uint32_t s = j & 1u, ph = (j >> 1) & 1u;
-            if (!mbar_wait_bounded(kv_empty(s), ph ^ 1u, abort_flag, p.status, SITE_KV_EMPTY,
+        uint32_t kvc = 0;  // KV blocks loaded so far (all items): stage kvc & 1, use kvc >> 1
+        bool ok = true;
+        for (uint32_t round = 0; ok && round * gridDim.x < total_items; ++round) {
+            const uint32_t it = item_of(round);
+            if (it >= total_items)
+                continue;  // the last round is not full
+            const uint32_t n_item = round;  // every earlier round held an item for this CTA
+            const Item im = make_item(p, it);
+            const int32_t col0 = (int32_t)(im.h * D);
+            const int32_t q_row = (int32_t)(im.b * p.seq_q + im.q0);
+            // Q is single-buffered: the previous item's last Q K^T must have read it
+            if (!mbar_wait_bounded(q_empty, (n_item & 1u) ^ 1u, abort_flag, p.status, SITE_Q_FULL,
                                    KERNEL_FLASH_ATTN))
                 break;
             if (elect_one()) {
-                const uint32_t stage = kv_smem + s * STAGE_BYTES;
-                const int32_t kv_row = (int32_t)(b * p.seq_k + j * BKV);
-                mbar_expect_tx(kv_full(s), STAGE_BYTES);
-                tma_load_2d(stage, &maps.k, kv_full(s), col0, kv_row);
-                tma_load_2d(stage + SUB_BYTES, &maps.k, kv_full(s), col0 + 64, kv_row);
-                tma_load_2d(stage + KV_TILE_BYTES, &maps.v, kv_full(s), col0, kv_row);
-                tma_load_2d(stage + KV_TILE_BYTES + SUB_BYTES, &maps.v, kv_full(s), col0 + 64,
-                            kv_row);
+                mbar_expect_tx(q_full, Q_BYTES);
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+                    tma_load_2d(q_smem + t * Q_TILE_BYTES, &maps.q, q_full, col0, q_row + t * BQ);
+                    tma_load_2d(q_smem + t * Q_TILE_BYTES + SUB_BYTES, &maps.q, q_full, col0 + 64,
+                                q_row + t * BQ);
+                }
             }
             __syncwarp();
+            for (uint32_t j = 0; j < im.num_kv; ++j, ++kvc) {
+                const uint32_t s = kvc & 1u, ph = (kvc >> 1) & 1u;
+                if (!mbar_wait_bounded(kv_empty(s), ph ^ 1u, abort_flag, p.status, SITE_KV_EMPTY,
+                                       KERNEL_FLASH_ATTN)) {
+                    ok = false;
+                    break;
+                }
+                if (elect_one()) {
+                    const uint32_t stage = kv_smem + s * STAGE_BYTES;
+                    const int32_t kv_row = (int32_t)(im.b * p.seq_k + j * BKV);
+                    mbar_expect_tx(kv_full(s), STAGE_BYTES);
+                    tma_load_2d(stage, &maps.k, kv_full(s), col0, kv_row);
+                    tma_load_2d(stage + SUB_BYTES, &maps.k, kv_full(s), col0 + 64, kv_row);
+                    tma_load_2d(stage + KV_TILE_BYTES, &maps.v, kv_full(s), col0, kv_row);
+                    tma_load_2d(stage + KV_TILE_BYTES + SUB_BYTES, &maps.v, kv_full(s), col0 + 64,
+                                kv_row);
+                }
+                __syncwarp();
+            }
         }
         if (*abort_flag)
             for (uint32_t spin = 0; spin < 2000; ++spin)
                 __nanosleep(100);
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        auto issue_qk = [&](uint32_t t, uint32_t j) {
-            // S_t = Q_t K_j^T : 8 steps of 16 along d; sub-tile d/64, 32 bytes inside the row
-            const uint32_t stage = kv_smem + (j & 1u) * STAGE_BYTES;
+        // g = running number of the KV block (all items): it selects the stage
+        auto issue_qk = [&](uint32_t t, uint32_t g) {
+            // S_t = Q_t K^T : 8 steps of 16 along d; sub-tile d/64, 32 bytes inside the row
+            const uint32_t stage = kv_smem + (g & 1u) * STAGE_BYTES;
             const uint32_t qt = q_smem + t * Q_TILE_BYTES;
             const uint32_t d_tmem = tmem_base + TMEM_S + t * BKV;
             if (elect_one()) {
@@ -307,11 +341,12 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
             }
             __syncwarp();
         };
-        // O_t += P_t V_j, steps [k0, k0 + 4) of 16 along kv; P in tensor memory (8 columns per
+        // O_t += P_t V, steps [k0, k0 + 4) of 16 along kv; P in tensor memory (8 columns per
         // step), V MN-major: 16 kv rows of 128 bytes per step, the two 64-column halves
-        // SUB_BYTES apart
-        auto issue_pv = [&](uint32_t t, uint32_t j, uint32_t k0, bool last, bool last_reader) {
-            const uint32_t v_smem = kv_smem + (j & 1u) * STAGE_BYTES + KV_TILE_BYTES;
+        // SUB_BYTES apart.  j = block inside the item (its first P V overwrites O_t).
+        auto issue_pv = [&](uint32_t t, uint32_t j, uint32_t g, uint32_t k0, bool last,
+                            bool last_reader) {
+            const uint32_t v_smem = kv_smem + (g & 1u) * STAGE_BYTES + KV_TILE_BYTES;
             const uint32_t p_tmem = tmem_base + TMEM_S + t * BKV;
             if (elect_one()) {
 #pragma unroll
@@ -323,69 +358,87 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
                 if (last) {
                     umma_commit(pv_done(t));
                     if (last_reader)
-                        umma_commit(kv_empty(j & 1u));  // K_j and V_j have been consumed
+                        umma_commit(kv_empty(g & 1u));  // this K and V block have been consumed
                 }
             }
             __syncwarp();
         };
-        bool ok = mbar_wait_bounded(q_full, 0, abort_flag, p.status, SITE_Q_FULL, KERNEL_FLASH_ATTN);
-        if (ok && num_kv > 0) {
-            ok = mbar_wait_bounded(kv_full(0), 0, abort_flag, p.status, SITE_KV_FULL,
+        uint32_t kvc = 0;           // KV blocks of the items before this one
+        uint32_t done[2] = {0, 0};  // blocks each tile's softmax has handed over so far
+        bool ok = true;
+        for (uint32_t round = 0; ok && round * gridDim.x < total_items; ++round) {
+            const uint32_t it = item_of(round);
+            if (it >= total_items)
+                continue;  // the last round is not full
+            const uint32_t n_item = round;  // every earlier round held an item for this CTA
+            const Item im = make_item(p, it);
+            const uint32_t nkv[2] = {im.nkv0, im.nkv1};
+            ok = mbar_wait_bounded(q_full, n_item & 1u, abort_flag, p.status, SITE_Q_FULL,
                                    KERNEL_FLASH_ATTN);
-            if (ok) {
-                tc_fence_after_sync();
-                if (nkv[0] > 0)
-                    issue_qk(0, 0);
-                if (nkv[1] > 0)
-                    issue_qk(1, 0);
-            }
-        }
-        for (uint32_t j = 0; ok && j < num_kv; ++j) {
-            bool next_ready = false;
-#pragma unroll
-            for (uint32_t t = 0; t < 2; ++t) {
-                if (j < nkv[t]) {
-                    // steps 0-3 go as soon as the first half of P is in
-                    if (lane == 0 && t == 0)
-                        FA_STAMP(j, 4);
-                    if (!mbar_wait_bounded(p_lo(t), j & 1u, abort_flag, p.status, SITE_P_FULL,
-                                           KERNEL_FLASH_ATTN)) {
-                        ok = false;
-                        break;
-                    }
+            if (ok && im.num_kv > 0) {
+                ok = mbar_wait_bounded(kv_full(kvc & 1u), (kvc >> 1) & 1u, abort_flag, p.status,
+                                       SITE_KV_FULL, KERNEL_FLASH_ATTN);
+                if (ok) {
                     tc_fence_after_sync();
-                    if (lane == 0 && t == 0)
-                        FA_STAMP(j, 5);
-                    issue_pv(t, j, 0, false, false);
-                    if (!mbar_wait_bounded(p_hi(t), j & 1u, abort_flag, p.status, SITE_P_FULL,
-                                           KERNEL_FLASH_ATTN)) {
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after_sync();
-                    if (lane == 0 && t == 0)
-                        FA_STAMP(j, 6);
-                    issue_pv(t, j, BKV / 32, true, (t == 1) || (j >= nkv[1]));
+                    if (nkv[0] > 0)
+                        issue_qk(0, kvc);
+                    if (nkv[1] > 0)
+                        issue_qk(1, kvc);
                 }
-                // scores of the next block for this tile, issued behind its P V so the other
-                // tile's softmax overlaps them (in-order execution on the tensor pipe makes the
-                // overwrite of P_t by S_t safe)
-                if (j + 1 < nkv[t]) {
-                    if (!next_ready) {
-                        if (!mbar_wait_bounded(kv_full((j + 1) & 1u), ((j + 1) >> 1) & 1u,
-                                               abort_flag, p.status, SITE_KV_FULL,
-                                               KERNEL_FLASH_ATTN)) {
+            }
+            if (ok && im.num_kv <= 1) {
+                if (elect_one())
+                    umma_commit(q_empty);  // no further Q K^T in this item
+                __syncwarp();
+            }
+            for (uint32_t j = 0; ok && j < im.num_kv; ++j) {
+                const uint32_t g = kvc + j;
+                bool next_ready = false;
+#pragma unroll
+                for (uint32_t t = 0; t < 2; ++t) {
+                    if (j < nkv[t]) {
+                        // steps 0-3 go as soon as the first half of P is in
+                        if (!mbar_wait_bounded(p_lo(t), done[t] & 1u, abort_flag, p.status,
+                                               SITE_P_FULL, KERNEL_FLASH_ATTN)) {
                             ok = false;
                             break;
                         }
                         tc_fence_after_sync();
-                        next_ready = true;
+                        issue_pv(t, j, g, 0, false, false);
+                        if (!mbar_wait_bounded(p_hi(t), done[t] & 1u, abort_flag, p.status,
+                                               SITE_P_FULL, KERNEL_FLASH_ATTN)) {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after_sync();
+                        issue_pv(t, j, g, BKV / 32, true, (t == 1) || (j >= nkv[1]));
+                        ++done[t];
                     }
-                    issue_qk(t, j + 1);
+                    // scores of the next block for this tile, issued behind its P V so the other
+                    // tile's softmax overlaps them (in-order execution on the tensor pipe makes
+                    // the overwrite of P_t by S_t safe)
+                    if (j + 1 < nkv[t]) {
+                        if (!next_ready) {
+                            if (!mbar_wait_bounded(kv_full((g + 1) & 1u), ((g + 1) >> 1) & 1u,
+                                                   abort_flag, p.status, SITE_KV_FULL,
+                                                   KERNEL_FLASH_ATTN)) {
+                                ok = false;
+                                break;
+                            }
+                            tc_fence_after_sync();
+                            next_ready = true;
+                        }
+                        issue_qk(t, g + 1);
+                    }
                 }
-                if (lane == 0 && t == 0)
-                    FA_STAMP(j, 7);
+                // the item's last Q K^T were issued in the step before the last one
+                if (ok && j + 2 == im.num_kv) {
+                    if (elect_one())
+                        umma_commit(q_empty);
+                    __syncwarp();
+                }
             }
+            kvc += im.num_kv;
         }
     } else {
         // ------------------------------------------------------------ softmax + epilogue
@@ -393,16 +446,23 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
         const uint32_t quarter = warp & 3u;
         const uint32_t lane_sel = (quarter * 32u) << 16;
         const uint32_t row_local = quarter * 32 + lane;
-        const uint32_t row = q0 + t * BQ + row_local;  // query index inside this (batch, head)
-        const uint32_t my_kv = t ? nkv[1] : nkv[0];
         const uint32_t s_tmem = tmem_base + TMEM_S + t * BKV + lane_sel;
         const uint32_t o_tmem = tmem_base + TMEM_O + t * D + lane_sel;
+        uint32_t cnt = 0;  // blocks of this tile processed so far (all items): barrier parities
+        bool ok = true;
+        for (uint32_t round = 0; ok && round * gridDim.x < total_items; ++round) {
+        const uint32_t it = item_of(round);
+        if (it >= total_items)
+            continue;  // the last round is not full
+        const Item im = make_item(p, it);
+        const uint32_t b = im.b, h = im.h, q0 = im.q0;
+        const uint32_t row = q0 + t * BQ + row_local;  // query index inside this (batch, head)
+        const uint32_t my_kv = t ? im.nkv1 : im.nkv0;
         float m_ref = 0.0f;  // reference subtracted in the exponent (log2 units)
         float m_run = -INFINITY;  // running max of the scaled scores
         float l_sum = 0.0f;
-        bool ok = true;
-        for (uint32_t j = 0; j < my_kv; ++j) {
-            if (!mbar_wait_bounded(s_full(t), j & 1u, abort_flag, p.status, SITE_S_FULL,
+        for (uint32_t j = 0; j < my_kv; ++j, ++cnt) {
+            if (!mbar_wait_bounded(s_full(t), cnt & 1u, abort_flag, p.status, SITE_S_FULL,
                                    KERNEL_FLASH_ATTN)) {
                 ok = false;
                 break;
@@ -502,10 +562,6 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
                 __syncwarp();
                 if (lane == 0) {
                     mbar_arrive(p_lo(t));
-                    if (warp == 2)
-                        FA_STAMP(j, 0);
-                    if (warp == 6)
-                        FA_STAMP(j, 2);
                 }
                 // keep the second half's arithmetic behind the hand-over: without a dependence
                 // the compiler moves it in front of the store wait and the arrive comes late
@@ -537,7 +593,7 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
                 // j-1, complete since S_j was issued behind them) is scaled before any P V of this
                 // block may start, so this block hands both halves over at the end.  The score
                 // registers are free by now: four loads in flight.
-                if (!mbar_wait_bounded(pv_done(t), (j - 1) & 1u, abort_flag, p.status, SITE_PV_DONE,
+                if (!mbar_wait_bounded(pv_done(t), (cnt - 1) & 1u, abort_flag, p.status, SITE_PV_DONE,
                                        KERNEL_FLASH_ATTN)) {
                     ok = false;
                     break;
@@ -567,15 +623,11 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
                 if (rescale)
                     mbar_arrive(p_lo(t));
                 mbar_arrive(p_hi(t));
-                if (warp == 2)
-                    FA_STAMP(j, 1);
-                if (warp == 6)
-                    FA_STAMP(j, 3);
             }
         }
         // ---- epilogue: O / l -> global
         if (ok && my_kv > 0)
-            ok = mbar_wait_bounded(pv_done(t), (my_kv - 1) & 1u, abort_flag, p.status, SITE_PV_DONE,
+            ok = mbar_wait_bounded(pv_done(t), (cnt - 1) & 1u, abort_flag, p.status, SITE_PV_DONE,
                                    KERNEL_FLASH_ATTN);
         if (ok && q0 + t * BQ < p.seq_q) {
             tc_fence_after_sync();
@@ -623,6 +675,9 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
                 }
             }
         }
+        // the reads of O_t are complete before this warp arrives for the next item's first block
+        tc_fence_before_sync();
+        }  // items
     }
 
     // ---------------------------------------------------------------- teardown
@@ -636,12 +691,6 @@ flash_attention_kernel(const __grid_constant__ TensorMaps maps, const Params p)
 
 }  // namespace fa
 
-#ifdef KAIO_TRACE
-extern "C" __attribute__((visibility("default"))) int kaio_b200_debug_set_fa_trace(void* ptr)
-{
-    return (int)cudaMemcpyToSymbol(fa::g_fa_trace, &ptr, sizeof(ptr));
-}
-#endif
 
 bool flash_attention_ok(const AttnParams& p)
 {
@@ -709,8 +758,10 @@ cudaError_t launch_flash_attention(const DeviceCtx& ctx, const AttnParams& ap, c
             return err;
         attr_set[ctx.device] = true;
     }
-    dim3 grid((ap.seq_q + 2 * BQ - 1) / (2 * BQ), ap.batch * ap.heads);
-    flash_attention_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(maps, p);
+    // persistent: one CTA per SM walks the (batch, head, 256-row query block) items
+    const uint32_t items = ((ap.seq_q + 2 * BQ - 1) / (2 * BQ)) * ap.batch * ap.heads;
+    const uint32_t ctas = items < (uint32_t)ctx.num_sms ? items : (uint32_t)ctx.num_sms;
+    flash_attention_kernel<<<dim3(ctas), NUM_THREADS, SMEM_BYTES, stream>>>(maps, p);
     return cudaGetLastError();
 }
 
