@@ -85,12 +85,13 @@ struct TensorMaps {
 };
 
 // One work item = (batch, head, 256 query rows).  The (batch, head) pairs are taken in groups of
-// gridDim.x / 2 -- about as many as keep their K and V (1 MB each at seq 2048) in the L2 together --
-// and inside a group the items are numbered heaviest first (causal: the last query block of every
-// pair, then the one before, ...).  A group is a whole number of rounds of the grid, so the snake
-// assignment (see item_of) gives every CTA the same total per group, and the eight query blocks of a
-// pair run within a few rounds of each other: K and V come from DRAM about once (numbered heaviest
-// first over ALL pairs they were fetched three times).
+// gridDim.x / 4 -- few enough that their K and V (1 MB per pair at seq 2048) stay in the L2
+// together -- and inside a group the items are numbered heaviest first (causal: the last query block
+// of every pair, then the one before, ...).  With eight query blocks per pair a group is two whole
+// rounds of the grid, so the snake assignment (see item_of) gives every CTA the same total per
+// group, and the query blocks of a pair run within two rounds of each other: K and V come from
+// DRAM about once (numbered heaviest first over ALL pairs they were fetched three times: 1.27 GB
+// instead of 0.40 GB at config 4, and 326 us instead of 300).
 struct Item {
     uint32_t b, h, q0;
     uint32_t nkv0, nkv1;  // KV blocks each query tile attends to (0 for a tile beyond seq_q)
@@ -101,7 +102,7 @@ __device__ __forceinline__ Item make_item(const Params& p, uint32_t it)
 {
     const uint32_t num_qb = (p.seq_q + 2 * BQ - 1) / (2 * BQ);
     const uint32_t bh_count = p.batch * p.heads;
-    const uint32_t gsz = gridDim.x >= 2 ? gridDim.x / 2 : 1u;  // pairs per group
+    const uint32_t gsz = gridDim.x >= 4 ? gridDim.x / 4 : 1u;  // pairs per group
     const uint32_t groups = (bh_count + gsz - 1) / gsz;
     uint32_t grp = it / (gsz * num_qb);
     grp = grp < groups - 1 ? grp : groups - 1;
