@@ -561,28 +561,24 @@ static void launch_dequant_s4_any(const DequantArgs& da, uint32_t n, uint32_t k,
     }
 }
 
-// s8 [K,N] -> f16 [K,N] (exact).  VEC = 16: one 16-byte load and two 16-byte stores per thread and
-// step (count % 16 == 0 and 16-byte aligned bases); VEC = 8: 8-byte loads for the rest.
-template <int VEC>
+// s8 [K,N] -> f16 [K,N] (exact).  One 8-byte load and one 16-byte store per thread and step: every
+// store instruction of a warp covers 512 contiguous bytes.  (A 16-byte load with two 16-byte stores
+// per thread was measured slower: each store instruction then fills only half of every sector.)
 __global__ void __launch_bounds__(256)
 dequant_s8_kernel(const DequantArgs args, size_t count)
 {
     const int8_t* w = reinterpret_cast<const int8_t*>(args.w[blockIdx.y]);
     __half* out = args.out[blockIdx.y];
-    const size_t stride = (size_t)gridDim.x * blockDim.x * VEC;
-    for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC; i < count; i += stride) {
-        alignas(16) int8_t b[VEC];
-        if constexpr (VEC == 16)
-            *reinterpret_cast<int4*>(b) = *reinterpret_cast<const int4*>(w + i);
-        else
-            *reinterpret_cast<int2*>(b) = *reinterpret_cast<const int2*>(w + i);
-        __half2 h[VEC / 2];
+    const size_t stride = (size_t)gridDim.x * blockDim.x * 8;
+    for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < count; i += stride) {
+        // count % 8 == 0 and 8-byte aligned bases on this path
+        const int2 raw = *reinterpret_cast<const int2*>(w + i);
+        const int8_t* b = reinterpret_cast<const int8_t*>(&raw);
+        __half2 h[4];
 #pragma unroll
-        for (int j = 0; j < VEC / 2; ++j)
+        for (int j = 0; j < 4; ++j)
             h[j] = __halves2half2(__int2half_rn((int)b[2 * j]), __int2half_rn((int)b[2 * j + 1]));
-#pragma unroll
-        for (int j = 0; j < VEC / 8; ++j)
-            reinterpret_cast<uint4*>(out + i)[j] = reinterpret_cast<uint4*>(h)[j];
+        *reinterpret_cast<uint4*>(out + i) = *reinterpret_cast<uint4*>(h);
     }
 }
 
@@ -675,16 +671,9 @@ cudaError_t launch_dq_gemm(const DeviceCtx& ctx, int wfmt, const __half* x, cons
     } else if (wfmt == WFMT_S4_PACKED) {
         launch_dequant_s4_any(da, n, k, num_probs, stream);
     } else {
-        const size_t count = (size_t)k * n;  // count % 8 == 0 and 8-byte aligned bases on this path
-        bool wide = count % 16 == 0;
-        for (int i = 0; i < num_probs; ++i)
-            wide = wide && (uintptr_t)da.w[i] % 16 == 0 && (uintptr_t)da.out[i] % 16 == 0;
-        const size_t vecs = count / (wide ? 16 : 8);
-        dim3 grid((unsigned)((vecs + 255) / 256 < 8192 ? (vecs + 255) / 256 : 8192), num_probs);
-        if (wide)
-            dequant_s8_kernel<16><<<grid, 256, 0, stream>>>(da, count);
-        else
-            dequant_s8_kernel<8><<<grid, 256, 0, stream>>>(da, count);
+        const size_t count = (size_t)k * n;
+        dim3 grid((unsigned)((count / 8 + 255) / 256 < 4096 ? (count / 8 + 255) / 256 : 4096), num_probs);
+        dequant_s8_kernel<<<grid, 256, 0, stream>>>(da, count);
     }
     cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess)
