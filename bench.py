@@ -393,7 +393,7 @@ def main():
                    "wall_s_timed_loop": t_wall1 - t_wall0},
     }
     # the compact multi-GPU objects come right behind the contract keys: a reader that keeps only the
-    # first few KB of the line still has them (the last key repeats the parity verdict for one that
+    # first few KB of the line still has them (the last key repeats the parity result for one that
     # keeps only the end)
     if parity is not None:
         line["multi_parity"] = parity
