@@ -7,10 +7,10 @@
 // in shared memory, seq_k <= 384) and adds the batched multi-head form that reads Q/K/V in place
 // from [batch*seq, heads*128] projection outputs.
 //
-// Persistent: one CTA per SM walks the work items (batch, head, 256 query rows), heaviest first;
-// Q loads, the fill of the K/V ring and the first scores of the next item overlap the softmax tail
-// and the output of the current one, and tensor memory and barriers are set up once.  (One CTA per
-// item spent about a quarter of its time in launch, set-up, pipeline fill and output.)
+// Persistent: one CTA per SM walks the work items (batch, head, 256 query rows), heaviest first
+// inside groups of (batch, head) pairs whose K and V fit the L2 together (see make_item); Q loads,
+// the fill of the K/V ring and the first scores of the next item overlap the softmax tail and the
+// output of the current one, and tensor memory and barriers are set up once.
 // An item = two query tiles of 128 rows; 320 threads:
 //   warp 0     TMA producer: Q once (four [128][64] boxes), then K and V blocks ([128 kv][128 d] as
 //              two 64-column boxes each) through a 2-stage ring; 128-byte swizzle.
@@ -32,17 +32,19 @@
 //              and a new reference is set 2^8 above the max seen, so a row's max can rise by
 //              2^23 before the next rescale; when any row of a warp must rescale, every row of
 //              the warp moves its reference up to its own running max (the pass over O costs
-//              the same for one row as for 32), which makes such passes rare.  ex2(s * log2(e)/sqrt(d) - ref), row sum, P packed to f16 and stored to
-//              tensor memory; at the end O / sum -> global.  Two warps per scheduler hide each
-//              other's dependent chains; a single softmax warp-group left the tensor pipe 27 %
-//              busy.
+//              the same for one row as for 32), which makes such passes rare.
+//              ex2(s * log2(e)/sqrt(d) - ref) with the scale-and-subtract and the row sum as
+//              packed f32x2 instructions (the warps are bound by instruction issue), P packed
+//              to f16 and stored to tensor memory; at the end O / sum -> global.  Two warps per
+//              scheduler hide each other's dependent chains; a single softmax warp-group left
+//              the tensor pipe 27 % busy.
 #include "common.cuh"
 #include "kernels.h"
 
 namespace kaio {
 namespace fa {
 
-constexpr int BQ = 128;   // query rows per CTA
+constexpr int BQ = 128;   // query rows per tile (two tiles per work item)
 constexpr int BKV = 128;  // key/value rows per block
 constexpr int D = 128;    // head dim
 constexpr int KV_STAGES = 2;
